@@ -1,0 +1,289 @@
+// Row-wise kernels of the decoder: embedding gather, residual sum + RMSNorm,
+// position rotation fused with the paged key/value write, and SiLU(gate)*up.
+//
+// Conventions: the residual stream is float32 in both engines (the residual sum
+// is a 32-bit sum); activations between kernels are T (bfloat16 or float);
+// norm weights, biases and rotation frequencies are float32.
+#include "common.cuh"
+
+namespace distie {
+
+// ---------------------------------------------------------------------------
+// Embedding: residual[t, :] = table[ids[t], :] as float32.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ table,
+                             float* __restrict__ residual, int hidden, int vocab, int* __restrict__ error) {
+  const int t = blockIdx.x;
+  int id = ids[t];
+  if (id < 0 || id >= vocab) {
+    if (threadIdx.x == 0 && error) atomicExch(error, 1);
+    id = 0;  // never read outside the table
+  }
+  const T* row = table + (size_t)id * hidden;
+  float* out = residual + (size_t)t * hidden;
+  if ((hidden & 7) == 0) {
+    for (int i = threadIdx.x * 8; i < hidden; i += blockDim.x * 8) {
+      float v[8];
+      load8(row + i, v);
+      store8(out + i, v);
+    }
+  } else {
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[i] = to_float(row[i]);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// residual += delta (float32 sum, written back), then
+//   out = weight * cast_T(residual * rsqrt(mean(residual^2) + eps))
+// The normalised value is rounded to T before the weight multiplies it, as the
+// reference does.  With `rows_index` the kernel normalises only the listed rows
+// (used before the output head) and leaves the residual untouched.
+// One block per output row.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void add_rmsnorm_kernel(const T* __restrict__ delta, float* __restrict__ residual,
+                                   const float* __restrict__ weight, T* __restrict__ out,
+                                   const int* __restrict__ rows_index, int hidden, float eps) {
+  __shared__ float scratch[32];
+  const int out_row = blockIdx.x;
+  const int row = rows_index ? rows_index[out_row] : out_row;
+  float* res = residual + (size_t)row * hidden;
+  const T* del = delta ? delta + (size_t)row * hidden : nullptr;
+  T* dst = out + (size_t)out_row * hidden;
+  const bool write_back = (delta != nullptr) && (rows_index == nullptr);
+
+  float sumsq = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float v = res[i];
+    if (del) v += to_float(del[i]);
+    if (write_back) res[i] = v;
+    sumsq += v * v;
+  }
+  const float total = block_sum(sumsq, scratch);
+  const float rstd = rsqrtf(total / (float)hidden + eps);
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float v = res[i];
+    if (del && !write_back) v += to_float(del[i]);
+    const float normed = to_float(from_float<T>(v * rstd));
+    dst[i] = from_float<T>(weight[i] * normed);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Rotation of q and k (rotate-half or interleaved pairs, over the first
+// `rotary_dim` dims of each head) in float32, fused with the write of the new
+// key and value rows into their pages.
+//
+//   qkv      [T, row_stride]: q heads, then k heads, then v heads, each head_dim wide
+//   k_cache  [pages, kv_heads, page_size, head_dim] of this layer's slot (v likewise)
+//   slot of token t = block_table[seat(t), pos / page_size], row pos % page_size
+//
+// q is rotated in place; k (rotated) and v go straight to the cache; nothing else
+// is written.  Without `inv_freq` nothing is rotated; with `write_cache == 0`
+// only q is handled.  One block per token.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
+                                     const int* __restrict__ token_seq, const int* __restrict__ seq_seat,
+                                     const int* __restrict__ block_table, int table_width,
+                                     const float* __restrict__ inv_freq, T* __restrict__ k_cache,
+                                     T* __restrict__ v_cache, int row_stride, int num_heads, int num_kv_heads,
+                                     int head_dim, int rotary_dim, int interleaved, int page_size, int num_pages,
+                                     int write_cache, int* __restrict__ error) {
+  extern __shared__ float trig[];  // cos[rotary_dim/2], sin[rotary_dim/2]
+  const int t = blockIdx.x;
+  const int pos = positions[t];
+  const int half = rotary_dim >> 1;
+  if (inv_freq) {
+    for (int j = threadIdx.x; j < half; j += blockDim.x) {
+      float s, c;
+      sincosf((float)pos * inv_freq[j], &s, &c);
+      trig[j] = c;
+      trig[half + j] = s;
+    }
+  }
+  __syncthreads();
+
+  T* row = qkv + (size_t)t * row_stride;
+  T* k_dst = nullptr;
+  T* v_dst = nullptr;
+  if (write_cache) {
+    const int seat = seq_seat[token_seq[t]];
+    const int column = pos / page_size;
+    const int page = (pos >= 0 && column < table_width) ? block_table[(size_t)seat * table_width + column] : -1;
+    if (page < 0 || page >= num_pages) {
+      if (threadIdx.x == 0 && error) atomicExch(error, 2);
+      write_cache = 0;  // never write outside the slab
+    } else {
+      const size_t base = ((size_t)page * num_kv_heads * page_size + (pos % page_size)) * head_dim;
+      k_dst = k_cache + base;
+      v_dst = v_cache + base;
+    }
+  }
+  const size_t cache_head_stride = (size_t)page_size * head_dim;
+
+  // q and k heads: pairs (j, j + half) or (2j, 2j + 1) inside the rotary dims.
+  const int rot_heads = num_heads + num_kv_heads;
+  const int pairs_per_head = head_dim >> 1;
+  for (int idx = threadIdx.x; idx < rot_heads * pairs_per_head; idx += blockDim.x) {
+    const int head = idx / pairs_per_head;
+    const int j = idx % pairs_per_head;
+    const bool is_k = head >= num_heads;
+    if (is_k && !write_cache) continue;
+    T* src = row + (size_t)head * head_dim;
+    int i0, i1;
+    float c = 1.f, s = 0.f;
+    if (j < half) {
+      if (interleaved) { i0 = 2 * j; i1 = 2 * j + 1; } else { i0 = j; i1 = j + half; }
+      if (inv_freq) { c = trig[j]; s = trig[half + j]; }
+    } else {  // dims beyond rotary_dim pass through, two at a time
+      i0 = rotary_dim + 2 * (j - half);
+      i1 = i0 + 1;
+    }
+    const float x0 = to_float(src[i0]), x1 = to_float(src[i1]);
+    const float y0 = x0 * c - x1 * s;
+    const float y1 = x1 * c + x0 * s;
+    if (is_k) {
+      T* dst = k_dst + (size_t)(head - num_heads) * cache_head_stride;
+      dst[i0] = from_float<T>(y0);
+      dst[i1] = from_float<T>(y1);
+    } else {
+      src[i0] = from_float<T>(y0);
+      src[i1] = from_float<T>(y1);
+    }
+  }
+  if (write_cache) {
+    const T* v_src = row + (size_t)(num_heads + num_kv_heads) * head_dim;
+    for (int idx = threadIdx.x; idx < num_kv_heads * head_dim; idx += blockDim.x) {
+      const int head = idx / head_dim, i = idx % head_dim;
+      v_dst[(size_t)head * cache_head_stride + i] = v_src[idx];
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// out[t, i] = silu(gate_up[t, i]) * gate_up[t, inter + i], computed in float32.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, size_t total) {
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = idx / inter;
+    const int i = (int)(idx % inter);
+    const float g = to_float(gate_up[t * 2 * inter + i]);
+    const float u = to_float(gate_up[t * 2 * inter + inter + i]);
+    out[idx] = from_float<T>(g / (1.f + expf(-g)) * u);
+  }
+}
+
+// out (T) [rows, cols] = cast(in (float32) + bias[col]): the epilogue of a product whose
+// float32 result gets its bias added before the one rounding to T.
+template <typename T>
+__global__ void bias_cast_kernel(const float* __restrict__ in, const float* __restrict__ bias, T* __restrict__ out,
+                                 int cols, size_t total) {
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (size_t)gridDim.x * blockDim.x) {
+    float v = in[idx];
+    if (bias) v += bias[idx % cols];
+    out[idx] = from_float<T>(v);
+  }
+}
+
+}  // namespace distie
+
+using namespace distie;
+
+extern "C" int distie_embed(const int* ids, const void* table, float* residual, int tokens, int hidden, int vocab,
+                            int table_dtype, int* error, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (hidden < 1 || vocab < 1) return DISTIE_ERR_ARG;
+  const int threads = hidden >= 2048 ? 256 : 128;
+  if (table_dtype == DISTIE_BF16)
+    embed_kernel<<<tokens, threads, 0, stream>>>(ids, (const __nv_bfloat16*)table, residual, hidden, vocab, error);
+  else if (table_dtype == DISTIE_F32)
+    embed_kernel<<<tokens, threads, 0, stream>>>(ids, (const float*)table, residual, hidden, vocab, error);
+  else
+    return DISTIE_ERR_UNSUPPORTED;
+  DISTIE_LAUNCH_CHECK();
+  return 0;
+}
+
+extern "C" int distie_add_rmsnorm(const void* delta, float* residual, const float* weight, void* out,
+                                  const int* rows_index, int rows, int hidden, float eps, int dtype,
+                                  cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (hidden < 1) return DISTIE_ERR_ARG;
+  const int threads = hidden >= 4096 ? 512 : (hidden >= 1024 ? 256 : 128);
+  if (dtype == DISTIE_BF16)
+    add_rmsnorm_kernel<<<rows, threads, 0, stream>>>((const __nv_bfloat16*)delta, residual, weight,
+                                                     (__nv_bfloat16*)out, rows_index, hidden, eps);
+  else if (dtype == DISTIE_F32)
+    add_rmsnorm_kernel<<<rows, threads, 0, stream>>>((const float*)delta, residual, weight, (float*)out,
+                                                     rows_index, hidden, eps);
+  else
+    return DISTIE_ERR_UNSUPPORTED;
+  DISTIE_LAUNCH_CHECK();
+  return 0;
+}
+
+extern "C" int distie_rope_kv_write(void* qkv, const int* positions, const int* token_seq, const int* seq_seat,
+                                    const int* block_table, int table_width, const float* inv_freq, void* k_cache,
+                                    void* v_cache, int tokens, int row_stride, int num_heads, int num_kv_heads,
+                                    int head_dim, int rotary_dim, int interleaved, int page_size, int num_pages,
+                                    int write_cache, int dtype, int* error, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (head_dim < 2 || (head_dim & 1) || rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1) ||
+      num_heads < 1 || num_kv_heads < 1 || page_size < 1 || table_width < 1)
+    return DISTIE_ERR_ARG;
+  const int threads = 128;
+  const size_t shared = (size_t)rotary_dim * sizeof(float);
+  if (dtype == DISTIE_BF16)
+    rope_kv_write_kernel<<<tokens, threads, shared, stream>>>(
+        (__nv_bfloat16*)qkv, positions, token_seq, seq_seat, block_table, table_width, inv_freq,
+        (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, row_stride, num_heads, num_kv_heads, head_dim, rotary_dim,
+        interleaved, page_size, num_pages, write_cache, error);
+  else if (dtype == DISTIE_F32)
+    rope_kv_write_kernel<<<tokens, threads, shared, stream>>>(
+        (float*)qkv, positions, token_seq, seq_seat, block_table, table_width, inv_freq, (float*)k_cache,
+        (float*)v_cache, row_stride, num_heads, num_kv_heads, head_dim, rotary_dim, interleaved, page_size, num_pages,
+        write_cache, error);
+  else
+    return DISTIE_ERR_UNSUPPORTED;
+  DISTIE_LAUNCH_CHECK();
+  return 0;
+}
+
+extern "C" int distie_swiglu(const void* gate_up, void* out, int tokens, int inter, int dtype, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (inter < 1) return DISTIE_ERR_ARG;
+  const size_t total = (size_t)tokens * inter;
+  const int threads = 256;
+  const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
+  if (dtype == DISTIE_BF16)
+    swiglu_kernel<<<blocks, threads, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, total);
+  else if (dtype == DISTIE_F32)
+    swiglu_kernel<<<blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, inter, total);
+  else
+    return DISTIE_ERR_UNSUPPORTED;
+  DISTIE_LAUNCH_CHECK();
+  return 0;
+}
+
+extern "C" int distie_bias_cast(const float* in, const float* bias, void* out, long long rows, int cols, int dtype,
+                                cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (cols < 1) return DISTIE_ERR_ARG;
+  const size_t total = (size_t)rows * cols;
+  const int threads = 256;
+  const size_t want = (total + threads - 1) / threads;
+  const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+  if (dtype == DISTIE_BF16)
+    bias_cast_kernel<<<blocks, threads, 0, stream>>>(in, bias, (__nv_bfloat16*)out, cols, total);
+  else if (dtype == DISTIE_F32)
+    bias_cast_kernel<<<blocks, threads, 0, stream>>>(in, bias, (float*)out, cols, total);
+  else
+    return DISTIE_ERR_UNSUPPORTED;
+  DISTIE_LAUNCH_CHECK();
+  return 0;
+}

@@ -1,0 +1,201 @@
+"""The step function: a batch of (request, its next tokens) in, logits at the wanted places out.
+
+``ModelRunner.step(entries)`` runs only the tokens it is given, as one batch,
+against what earlier steps left in the cache, and returns float32 logits
+``[wanted, vocab]`` on the device.  Trace replay and generation both go through
+it; generation adds sampling on the device (``run_plan``).
+
+Steps in which every request decodes one token are replayed from CUDA graphs, one
+per batch-size bucket, like the reference's (worker/src/inference/qwen2/
+batch_decode.py:1-17): the batch is rounded up to a bucket (1, 2, 4, 8, then steps
+of 8), padding rows decode token 0 at position 0 of the padding seat, whose block
+table names a spare page the pool never hands out.  Everything a captured step
+reads sits in fixed device buffers that are refilled before each replay.
+"""
+
+from __future__ import annotations
+
+import bisect
+import logging
+from typing import Sequence
+
+import numpy as np
+import torch
+
+from ..sampling.sampler import Sampler, uniform
+from .batch import BatchEntry, StepLayout, StepStaging, lay_out, views
+
+_log = logging.getLogger(__name__)
+
+
+def decode_buckets(max_batch: int) -> tuple[int, ...]:
+    """Powers of two up to 8, then steps of 8, then ``max_batch`` (batch_decode.py:42-49)."""
+    if max_batch < 1:
+        raise ValueError("max_batch must be >= 1")
+    sizes = {b for b in (1, 2, 4, 8) if b < max_batch}
+    sizes.update(range(16, max_batch, 8))
+    sizes.add(max_batch)
+    return tuple(sorted(sizes))
+
+
+class _Bucket:
+    def __init__(self, size: int, device: torch.device) -> None:
+        self.size = size
+        # token_ids | positions | token_seq | seq_seat | logit_rows, each `size` long
+        self.ints = torch.zeros(5 * size, dtype=torch.int32, device=device)
+        self.floats = torch.zeros(2 * size, dtype=torch.float32, device=device)  # temperatures | uniforms
+        self.tokens = torch.zeros(size, dtype=torch.int32, device=device)
+        self.logits: torch.Tensor | None = None
+        self.graph: torch.cuda.CUDAGraph | None = None
+        pin = device.type == "cuda"
+        self.host_ints = torch.zeros(5 * size, dtype=torch.int32, pin_memory=pin)
+        self.host_floats = torch.zeros(2 * size, dtype=torch.float32, pin_memory=pin)
+        self.layout = StepLayout([], size, size, size, size, 0, np.zeros(0, dtype=np.int32))
+
+
+class ModelRunner:
+    def __init__(self, model, cache, max_step_tokens: int, max_seqs: int, decode_graphs: bool = True) -> None:
+        self.model = model
+        self.cache = cache
+        self.kernels = model.kernels
+        self.device = self.kernels.device
+        self.sampler = Sampler(self.kernels)
+        self.max_step_tokens = max_step_tokens
+        self.max_seqs = max_seqs
+        self.staging = StepStaging(4 * max_step_tokens + max_seqs, self.device)
+        self._floats_host = [
+            torch.zeros(2 * max_seqs, dtype=torch.float32, pin_memory=self.device.type == "cuda") for _ in range(2)
+        ]
+        self._floats_turn = 0
+        self._floats_device = torch.zeros(2 * max_seqs, dtype=torch.float32, device=self.device)
+        graph_safe = all(getattr(block, "graph_safe", True) for block in model.blocks)
+        self.use_graphs = bool(decode_graphs) and self.device.type == "cuda" and graph_safe
+        self._sizes = decode_buckets(max_seqs)
+        self._buckets: dict[int, _Bucket] = {}
+        self._graph_pool = None
+        self.graph_replays = 0
+        self.steps = 0
+
+    # -- the step function ----------------------------------------------------
+    @torch.inference_mode()
+    def step(self, entries: Sequence[BatchEntry]) -> torch.Tensor | None:
+        layout = lay_out(entries, self.model.vocab_size)
+        if layout.num_tokens > self.max_step_tokens or layout.num_seqs > self.max_seqs:
+            raise ValueError(
+                f"step of {layout.num_tokens} tokens / {layout.num_seqs} requests exceeds the runner's "
+                f"limits ({self.max_step_tokens} / {self.max_seqs})"
+            )
+        self.cache.upload_tables([s.seat for s in layout.seqs])
+        step, rows = self.staging.upload(layout)
+        self.steps += 1
+        return self.model.forward(step, layout.seqs, self.cache, rows if layout.num_rows else None)
+
+    def finish_step(self) -> None:
+        """After the step's results reached the host: surface device-side checks."""
+        self.kernels.check_errors()
+
+    # -- generation: plan in, one token per sampling item out -----------------
+    @torch.inference_mode()
+    def run_plan(self, plan) -> list[int]:
+        items = plan.items
+        if not items:
+            raise ValueError("empty step plan")
+        sampling = [item for item in items if item.samples]
+        if self.use_graphs and len(items) <= self._sizes[-1] and all(len(i.token_ids) == 1 for i in items):
+            try:
+                return self._graph_step(items)
+            except Exception:  # the eager step rewrites the same slots, so running it instead is safe
+                _log.exception("decode graph failed; every step stays eager from now on")
+                self.use_graphs = False
+        entries = [
+            BatchEntry(i.seq.seat, i.token_ids, i.past_len, (len(i.token_ids) - 1,) if i.samples else ())
+            for i in items
+        ]
+        logits = self.step(entries)
+        if not sampling:
+            self.finish_step()
+            return []
+        temps, uniforms = self._sampling_numbers(sampling)
+        tokens = self.sampler.pick(logits, temps, uniforms).tolist()
+        self.finish_step()
+        return tokens
+
+    def _sampling_numbers(self, sampling):
+        if all(item.seq.temperature <= 0 for item in sampling):
+            return None, None
+        n = len(sampling)
+        host = self._floats_host[self._floats_turn]
+        self._floats_turn ^= 1
+        array = host.numpy()
+        for row, item in enumerate(sampling):
+            array[row] = max(0.0, float(item.seq.temperature))
+            array[n + row] = uniform(item.seq.seed, len(item.seq.output_ids))
+        self._floats_device[: 2 * n].copy_(host[: 2 * n], non_blocking=True)
+        return self._floats_device[:n], self._floats_device[n : 2 * n]
+
+    # -- decode graphs ------------------------------------------------------
+    def bucket_for(self, rows: int) -> int:
+        if rows < 1 or rows > self._sizes[-1]:
+            raise ValueError(f"decode batch of {rows} rows outside 1..{self._sizes[-1]}")
+        return self._sizes[bisect.bisect_left(self._sizes, rows)]
+
+    def _graph_step(self, items) -> list[int]:
+        rows = len(items)
+        size = self.bucket_for(rows)
+        bucket = self._buckets.get(size)
+        if bucket is None:
+            bucket = _Bucket(size, self.device)
+            self._buckets[size] = bucket
+        ints = bucket.host_ints.numpy()
+        floats = bucket.host_floats.numpy()
+        ids, positions, token_seq = ints[:size], ints[size : 2 * size], ints[2 * size : 3 * size]
+        seats, logit_rows = ints[3 * size : 4 * size], ints[4 * size :]
+        ids[:] = 0
+        positions[:] = 0
+        seats[:] = self.cache.pad_seat
+        token_seq[:] = np.arange(size, dtype=np.int32)
+        logit_rows[:] = np.arange(size, dtype=np.int32)
+        floats[:] = 0.0
+        for row, item in enumerate(items):
+            ids[row] = item.token_ids[0]
+            positions[row] = item.past_len
+            seats[row] = item.seq.seat
+            floats[row] = max(0.0, float(item.seq.temperature))
+            floats[size + row] = uniform(item.seq.seed, len(item.seq.output_ids))
+        self.cache.upload_tables([item.seq.seat for item in items])
+        bucket.ints.copy_(bucket.host_ints, non_blocking=True)
+        bucket.floats.copy_(bucket.host_floats, non_blocking=True)
+        if bucket.graph is None:
+            self._capture(bucket)
+        else:
+            bucket.graph.replay()
+            self.graph_replays += 1
+        self.steps += 1
+        tokens = bucket.tokens[:rows].tolist()
+        self.finish_step()
+        return [token for token, item in zip(tokens, items) if item.samples]
+
+    def _forward_bucket(self, bucket: _Bucket) -> None:
+        layout = bucket.layout
+        layout.max_kv_len = self.cache.max_tokens_per_request  # a fixed bound: the graph must not depend on lengths
+        step, rows = views(bucket.ints, layout)
+        bucket.logits = self.model.forward(step, (), self.cache, rows)
+        size = bucket.size
+        self.sampler.pick(bucket.logits, bucket.floats[:size], bucket.floats[size:], bucket.tokens)
+
+    def _capture(self, bucket: _Bucket) -> None:
+        # Warm up on a side stream (library workspaces, lazy kernel loading), then capture.
+        side = torch.cuda.Stream(device=self.device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            self._forward_bucket(bucket)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize(self.device)
+        if self._graph_pool is None:
+            self._graph_pool = torch.cuda.graph_pool_handle()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, pool=self._graph_pool):
+            self._forward_bucket(bucket)
+        bucket.graph = graph
+        graph.replay()
+        _log.info("decode graph captured bucket=%s", bucket.size)

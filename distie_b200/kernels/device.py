@@ -1,0 +1,200 @@
+"""The two kernel sets of the product: bfloat16 (serving) and float32 (true 32-bit).
+
+Both drive the same hand-written launchers with a dtype code; they differ in the
+element type of activations, weights and cache, and in the matrix products:
+
+* bfloat16: products with float32 accumulation.  Plain ``x @ W.T`` goes to the
+  library (cuBLAS through ``torch.mm``), as the reference's engine does for every
+  product (worker/src/inference/qwen2/model.py:216-236); skinny and fused
+  products use this package's own kernels where they are registered.
+* float32: ``torch.mm`` with TF32 switched off, i.e. FMA-only float32 products;
+  accurate ``expf``/``sincosf``/``rsqrtf`` in every kernel.
+
+There is no CPU path here and no fallback: a missing library raises.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from . import library
+from .interface import KernelSet, KvSlot, RotaryTable, StepTensors
+from .library import KernelError, check, function
+
+_CODE = {torch.float32: 0, torch.bfloat16: 1}
+_DECODE_HEAD_DIMS = (16, 32, 64, 128, 256)
+
+_ERROR_TEXT = {
+    1: "a token id outside the vocabulary reached the embedding",
+    2: "a new token's page is missing from its block table (cache write)",
+    3: "a block table does not cover the keys a token attends to",
+    4: "a block table does not cover the keys a decoded token attends to",
+}
+
+
+class DeviceKernels(KernelSet):
+    def __init__(self, dtype: torch.dtype, device: torch.device | str = "cuda:0") -> None:
+        if dtype not in _CODE:
+            raise KernelError(f"no kernel set for dtype {dtype}; the engine runs bfloat16 or float32")
+        self.dtype = dtype
+        self.device = torch.device(device)
+        if self.device.type != "cuda" or not torch.cuda.is_available():
+            raise KernelError("distie_b200 runs on a CUDA device (sm_100a) only; no GPU is visible")
+        major, minor = torch.cuda.get_device_capability(self.device)
+        if major != 10:
+            raise KernelError(f"kernels are built for sm_100a; device reports sm_{major}{minor}")
+        self.code = _CODE[dtype]
+        if dtype == torch.float32:
+            # True 32-bit products: no TF32, no reduced-precision reductions.
+            torch.backends.cuda.matmul.allow_tf32 = False
+            torch.backends.cudnn.allow_tf32 = False
+            torch.set_float32_matmul_precision("highest")
+        library.load_unit("base")
+        self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
+        self.error_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.launches = 0  # own kernels launched (library products are not counted)
+
+    # -- helpers ------------------------------------------------------------
+    @staticmethod
+    def _stream() -> int:
+        return torch.cuda.current_stream().cuda_stream
+
+    def check_errors(self) -> None:
+        code = int(self.error_flag.item())
+        if code:
+            self.error_flag.zero_()
+            raise KernelError(f"device-side check failed: {_ERROR_TEXT.get(code, code)}")
+
+    # -- operations -----------------------------------------------------------
+    def embed(self, step: StepTensors, table: torch.Tensor, residual: torch.Tensor) -> None:
+        hidden = table.shape[1]
+        check(
+            function("distie_embed")(
+                step.token_ids.data_ptr(), table.data_ptr(), residual.data_ptr(), step.num_tokens, hidden,
+                table.shape[0], _CODE[table.dtype], self.error_flag.data_ptr(), self._stream(),
+            ),
+            "embed",
+        )
+        self.launches += 1
+
+    def add_rmsnorm(self, delta, residual, weight, eps, out, rows_index=None) -> None:
+        rows = out.shape[0]
+        check(
+            function("distie_add_rmsnorm")(
+                delta.data_ptr() if delta is not None else None, residual.data_ptr(), weight.data_ptr(),
+                out.data_ptr(), rows_index.data_ptr() if rows_index is not None else None, rows,
+                residual.shape[1], float(eps), self.code, self._stream(),
+            ),
+            "add_rmsnorm",
+        )
+        self.launches += 1
+
+    def linear(self, x, weight, bias=None, out_dtype=None):
+        out_dtype = out_dtype or self.dtype
+        if weight.dtype == torch.float32:
+            # float32 engine, or a matrix the checkpoint stores in 32-bit: a true float32 product.
+            x32 = x if x.dtype == torch.float32 else x.float()
+            y = torch.addmm(bias, x32, weight.t()) if bias is not None else torch.mm(x32, weight.t())
+            return y if out_dtype == torch.float32 else self._bias_cast(y, None, out_dtype)
+        if bias is None and out_dtype == self.dtype:
+            return torch.mm(x, weight.t())
+        y32 = torch.mm(x, weight.t(), out_dtype=torch.float32)
+        if out_dtype == torch.float32:
+            return y32 if bias is None else y32.add_(bias)
+        return self._bias_cast(y32, bias, out_dtype)
+
+    def _bias_cast(self, y32, bias, out_dtype):
+        out = torch.empty(y32.shape, dtype=out_dtype, device=y32.device)
+        check(
+            function("distie_bias_cast")(
+                y32.data_ptr(), bias.data_ptr() if bias is not None else None, out.data_ptr(), y32.shape[0],
+                y32.shape[1], _CODE[out_dtype], self._stream(),
+            ),
+            "bias_cast",
+        )
+        self.launches += 1
+        return out
+
+    def swiglu(self, gate_up, out) -> None:
+        check(
+            function("distie_swiglu")(
+                gate_up.data_ptr(), out.data_ptr(), gate_up.shape[0], out.shape[1], self.code, self._stream()
+            ),
+            "swiglu",
+        )
+        self.launches += 1
+
+    def rope_kv_write(self, qkv, step, kv, rotary, num_heads, num_kv_heads, head_dim) -> None:
+        write = kv is not None
+        table = kv.block_table if write else step.seq_seat  # any valid pointer when nothing is written
+        check(
+            function("distie_rope_kv_write")(
+                qkv.data_ptr(), step.positions.data_ptr(), step.token_seq.data_ptr(), step.seq_seat.data_ptr(),
+                table.data_ptr(), table.shape[-1] if write else 1,
+                rotary.inv_freq.data_ptr() if rotary is not None else None,
+                kv.k.data_ptr() if write else None, kv.v.data_ptr() if write else None,
+                step.num_tokens, qkv.stride(0), num_heads, num_kv_heads, head_dim,
+                rotary.rotary_dim if rotary is not None else 0,
+                int(rotary.interleaved) if rotary is not None else 0,
+                kv.page_size if write else 1, kv.num_pages if write else 1, int(write), self.code,
+                self.error_flag.data_ptr(), self._stream(),
+            ),
+            "rope_kv_write",
+        )
+        self.launches += 1
+
+    def plan_splits(self, tokens: int, num_heads: int, num_kv_heads: int, max_kv_len: int) -> int:
+        group = num_heads // num_kv_heads
+        chunks = (group + 7) // 8 if group > 8 else 1
+        blocks = max(1, tokens * num_kv_heads * chunks)
+        by_machine = -(-2 * self.sm_count // blocks)
+        by_length = max(1, max_kv_len // 256)
+        return max(1, min(by_machine, by_length, 64))
+
+    def attention(self, qkv, out, step, kv, num_heads, num_kv_heads, head_dim, window, scale) -> None:
+        window = int(window) if window else 0
+        n_dec = step.num_decode_tokens if head_dim in _DECODE_HEAD_DIMS else 0
+        element = qkv.element_size()
+        if n_dec > 0:
+            splits = self.plan_splits(n_dec, num_heads, num_kv_heads, step.max_kv_len)
+            scratch = None
+            if splits > 1:
+                floats = function("distie_attention_decode_scratch_floats")(n_dec, num_heads, head_dim, splits)
+                scratch = torch.empty(floats, dtype=torch.float32, device=qkv.device)
+            check(
+                function("distie_attention_decode")(
+                    qkv.data_ptr(), qkv.stride(0), out.data_ptr(), out.stride(0),
+                    scratch.data_ptr() if scratch is not None else None, step.positions.data_ptr(),
+                    step.token_seq.data_ptr(), step.seq_seat.data_ptr(), kv.block_table.data_ptr(),
+                    kv.block_table.shape[-1], kv.k.data_ptr(), kv.v.data_ptr(), n_dec, num_heads, num_kv_heads,
+                    head_dim, kv.page_size, kv.num_pages, window, float(scale), splits, self.code,
+                    self.error_flag.data_ptr(), self._stream(),
+                ),
+                "attention_decode",
+            )
+            self.launches += 1 if splits == 1 else 2
+        rest = step.num_tokens - n_dec
+        if rest > 0:
+            check(
+                function("distie_attention_generic")(
+                    qkv.data_ptr() + n_dec * qkv.stride(0) * element, qkv.stride(0),
+                    out.data_ptr() + n_dec * out.stride(0) * element, out.stride(0),
+                    step.positions.data_ptr() + 4 * n_dec, step.token_seq.data_ptr() + 4 * n_dec,
+                    step.seq_seat.data_ptr(), kv.block_table.data_ptr(), kv.block_table.shape[-1],
+                    kv.k.data_ptr(), kv.v.data_ptr(), rest, num_heads, num_kv_heads, head_dim, kv.page_size,
+                    kv.num_pages, window, float(scale), self.code, self.error_flag.data_ptr(), self._stream(),
+                ),
+                "attention_generic",
+            )
+            self.launches += 1
+
+    def sample(self, logits, temperatures, uniforms, out_tokens) -> None:
+        check(
+            function("distie_sample")(
+                logits.data_ptr(), logits.stride(0), logits.shape[0], logits.shape[1],
+                temperatures.data_ptr() if temperatures is not None else None,
+                uniforms.data_ptr() if uniforms is not None else None, out_tokens.data_ptr(), self._stream(),
+            ),
+            "sample",
+        )
+        self.launches += 1

@@ -1,0 +1,92 @@
+"""The set of operations the parts are written against.
+
+Parts never call a kernel by name; they are handed a :class:`KernelSet` when they
+are built.  The engine has two of them, both in :mod:`distie_b200.kernels.device`:
+the bfloat16 set that serving uses and the float32 set in which every product,
+sum and exponential is a true 32-bit operation.  Tests pass a third, written with
+plain tensor operations, to check each kernel against and to run the engine's
+bookkeeping on a machine without a GPU; the product never falls back to it.
+
+Shapes (``T`` tokens of this step, ``B`` requests of this step):
+
+``StepTensors``   the step's metadata on the device, all int32
+    token_ids [T], positions [T], token_seq [T] (batch row of each token),
+    seq_seat [B] (seat = row of the block tables and of the state slots).
+``KvSlot``        one cache slot of one group
+    k, v  [pages, kv_heads, page_size, head_dim]; block_table [seats, width] int32
+"""
+
+from __future__ import annotations
+
+from abc import ABC, abstractmethod
+from dataclasses import dataclass
+
+import torch
+
+
+@dataclass
+class StepTensors:
+    token_ids: torch.Tensor
+    positions: torch.Tensor
+    token_seq: torch.Tensor
+    seq_seat: torch.Tensor
+    num_tokens: int
+    num_seqs: int
+    num_decode_tokens: int  # the first this-many tokens are single-token rows
+    max_kv_len: int = 0  # bound on the keys any token sees; a captured step uses a fixed bound
+
+
+@dataclass
+class KvSlot:
+    k: torch.Tensor
+    v: torch.Tensor
+    block_table: torch.Tensor
+    page_size: int
+    num_pages: int
+
+
+@dataclass(frozen=True)
+class RotaryTable:
+    """What the fused rotation kernel needs of a rotary position encoding."""
+
+    inv_freq: torch.Tensor  # [rotary_dim / 2] float32
+    rotary_dim: int
+    interleaved: bool = False
+
+
+class KernelSet(ABC):
+    dtype: torch.dtype
+    device: torch.device
+
+    @abstractmethod
+    def embed(self, step: StepTensors, table: torch.Tensor, residual: torch.Tensor) -> None:
+        """residual[t] = table[token_ids[t]] as float32."""
+
+    @abstractmethod
+    def add_rmsnorm(self, delta, residual, weight, eps: float, out, rows_index=None) -> None:
+        """residual += delta (float32, kept), out = weight * cast(residual * rsqrt(mean sq + eps))."""
+
+    @abstractmethod
+    def linear(self, x, weight, bias=None, out_dtype=None):
+        """x @ weight.T (+ bias); weight is [out, in]."""
+
+    @abstractmethod
+    def swiglu(self, gate_up, out) -> None:
+        """out = silu(gate_up[:, :I]) * gate_up[:, I:]."""
+
+    @abstractmethod
+    def rope_kv_write(self, qkv, step: StepTensors, kv: KvSlot | None, rotary: RotaryTable | None,
+                      num_heads: int, num_kv_heads: int, head_dim: int) -> None:
+        """Rotate q (in place) and k, store k and v of the new tokens in their pages (if kv)."""
+
+    @abstractmethod
+    def attention(self, qkv, out, step: StepTensors, kv: KvSlot, num_heads: int, num_kv_heads: int,
+                  head_dim: int, window: int | None, scale: float) -> None:
+        """Causal (optionally windowed) attention of every token over its request's pages."""
+
+    @abstractmethod
+    def sample(self, logits, temperatures, uniforms, out_tokens) -> None:
+        """Arg-max for rows with temperature <= 0, inverse-CDF draw at uniforms[row] otherwise."""
+
+    def check_errors(self) -> None:
+        """Raise if a kernel of an earlier launch reported a bad index (after a synchronise)."""

@@ -1,0 +1,47 @@
+"""Position encodings.  A mixer is given one as a parameter.
+
+``rotary``: the reference's default RoPE (worker/src/inference/qwen2/model.py:93-117):
+``inv_freq[j] = 1 / theta**(2j / d)`` computed in float32 exactly as there, angles
+``pos * inv_freq`` and their cos/sin evaluated in float32 inside the fused kernel,
+pairs ``(j, j + d/2)`` (rotate-half).  ``rotary_dim < head_dim`` and interleaved
+pairs are parameters for other layer kinds.  ``none`` rotates nothing.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..config.model_spec import PartSpec
+from ..kernels.interface import RotaryTable
+from .base import POSITION_ENCODINGS, BuildContext
+
+
+@POSITION_ENCODINGS.register("rotary")
+class RotaryEncoding:
+    """params: ``head_dim``, ``theta``, optional ``rotary_dim``, ``interleaved``."""
+
+    def __init__(self, table: RotaryTable) -> None:
+        self._table = table
+
+    @classmethod
+    def build(cls, spec: PartSpec, ctx: BuildContext) -> "RotaryEncoding":
+        head_dim = int(spec.params["head_dim"])
+        rotary_dim = int(spec.params.get("rotary_dim") or head_dim)
+        theta = float(spec.params["theta"])
+        if rotary_dim % 2 or rotary_dim > head_dim:
+            raise ValueError(f"rotary_dim {rotary_dim} must be even and at most head_dim {head_dim}")
+        inv_freq = 1.0 / (theta ** (torch.arange(0, rotary_dim, 2, dtype=torch.float32) / rotary_dim))
+        return cls(RotaryTable(inv_freq.to(ctx.device), rotary_dim, bool(spec.params.get("interleaved", False))))
+
+    def rotary_table(self) -> RotaryTable | None:
+        return self._table
+
+
+@POSITION_ENCODINGS.register("none")
+class NoPositionEncoding:
+    @classmethod
+    def build(cls, spec: PartSpec, ctx: BuildContext) -> "NoPositionEncoding":
+        return cls()
+
+    def rotary_table(self) -> RotaryTable | None:
+        return None

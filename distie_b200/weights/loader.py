@@ -1,0 +1,156 @@
+"""Weights by tensor name: checking a checkpoint against what the parts declare,
+and converting what passes for the engine.
+
+The reference copies module by module out of a library model and raises on the
+first mismatch (worker/src/inference/qwen2/model.py:383-452).  Here every part
+declares its tensors (:class:`~distie_b200.parts.base.TensorSpec`), the checkpoint
+is compared with the whole list, and ONE error names everything that is missing,
+unexpected or of the wrong shape.
+
+Conversion on the way to the device:
+
+* ``matrix`` / ``table``: the engine's dtype.  bfloat16 engine: bfloat16 and
+  float16 tensors become bfloat16, a tensor stored in float32 stays float32 (its
+  products then run in float32).  float32 engine: everything becomes float32.
+* ``bias`` / ``norm``: float32 (exact for bfloat16 inputs).
+* integer tensors: int32.
+"""
+
+from __future__ import annotations
+
+from typing import Iterable, Mapping
+
+import torch
+
+from ..parts.base import TensorSpec
+from .safetensors_io import ModelTensors
+
+
+class WeightsError(ValueError):
+    """The checkpoint does not match the model: lists every problem at once."""
+
+    def __init__(self, missing, unexpected, wrong_shape, wrong_kind=()) -> None:
+        self.missing = list(missing)
+        self.unexpected = list(unexpected)
+        self.wrong_shape = list(wrong_shape)
+        self.wrong_kind = list(wrong_kind)
+        lines = ["checkpoint does not match the model:"]
+        if self.missing:
+            lines.append(f"  missing tensors ({len(self.missing)}): " + ", ".join(self.missing))
+        if self.unexpected:
+            lines.append(f"  unexpected tensors ({len(self.unexpected)}): " + ", ".join(self.unexpected))
+        if self.wrong_shape:
+            lines.append(
+                f"  wrong shapes ({len(self.wrong_shape)}): "
+                + ", ".join(f"{n}: checkpoint {tuple(have)}, model {tuple(want)}" for n, have, want in self.wrong_shape)
+            )
+        if self.wrong_kind:
+            lines.append(
+                f"  wrong element types ({len(self.wrong_kind)}): "
+                + ", ".join(f"{n}: {dtype}" for n, dtype in self.wrong_kind)
+            )
+        super().__init__("\n".join(lines))
+
+
+def check_checkpoint(
+    shapes: Mapping[str, tuple[int, ...]],
+    specs: Iterable[TensorSpec],
+    tolerated: Iterable[str] = (),
+    dtypes: Mapping[str, torch.dtype] | None = None,
+) -> None:
+    specs = list(specs)
+    wanted = {s.name: s for s in specs}
+    missing = [name for name in wanted if name not in shapes]
+    allowed = set(tolerated)
+    unexpected = sorted(name for name in shapes if name not in wanted and name not in allowed)
+    wrong = [
+        (name, shapes[name], spec.shape)
+        for name, spec in wanted.items()
+        if name in shapes and tuple(shapes[name]) != tuple(spec.shape)
+    ]
+    wrong_kind = []
+    if dtypes is not None:
+        for name in wanted:
+            if name in dtypes and not dtypes[name].is_floating_point:
+                wrong_kind.append((name, dtypes[name]))
+    if missing or unexpected or wrong or wrong_kind:
+        raise WeightsError(missing, unexpected, wrong, wrong_kind)
+
+
+class WeightStore:
+    """Hands converted device tensors to the parts, each name once (tied uses share the tensor)."""
+
+    def __init__(self, source, specs: Iterable[TensorSpec], dtype: torch.dtype, device) -> None:
+        self._source = source  # anything with .tensor(name) -> CPU tensor
+        self._roles = {s.name: s.role for s in specs}
+        self.dtype = dtype
+        self.device = torch.device(device) if device is not None else None
+        self._cache: dict[str, torch.Tensor] = {}
+
+    def _convert(self, name: str, role: str) -> torch.Tensor:
+        key = f"{role}:{name}"
+        if key in self._cache:
+            return self._cache[key]
+        raw = self._source.tensor(name)
+        if not raw.dtype.is_floating_point:
+            target = torch.int32
+        elif role in ("bias", "norm"):
+            target = torch.float32
+        elif self.dtype == torch.float32 or raw.dtype in (torch.float32, torch.float64):
+            target = torch.float32
+        else:
+            target = self.dtype
+        out = raw.to(dtype=target)
+        if self.device is not None:
+            out = out.to(self.device)
+        out = out.contiguous()
+        self._cache[key] = out
+        return out
+
+    def matrix(self, name: str) -> torch.Tensor:
+        return self._convert(name, "matrix")
+
+    table = matrix
+
+    def vector(self, name: str) -> torch.Tensor:
+        return self._convert(name, "bias")
+
+    def has(self, name: str) -> bool:
+        return name in self._roles
+
+    def release(self) -> None:
+        """Forget the per-name tensors once the parts hold (possibly fused) copies."""
+        self._cache.clear()
+
+
+class DictSource:
+    """Adapter so that a plain dict of CPU tensors can stand in for a model folder."""
+
+    def __init__(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        self._tensors = tensors
+
+    def keys(self):
+        return self._tensors.keys()
+
+    def shape(self, name):
+        return tuple(self._tensors[name].shape)
+
+    def dtype(self, name):
+        return self._tensors[name].dtype
+
+    def tensor(self, name):
+        return self._tensors[name]
+
+
+def open_weights(folder_or_dict, specs, tolerated, dtype: torch.dtype, device) -> WeightStore:
+    """Open a model folder (or a dict of tensors), check it against ``specs``, return the store."""
+    source = DictSource(folder_or_dict) if isinstance(folder_or_dict, Mapping) else ModelTensors(folder_or_dict)
+    specs = list(specs)
+    names = list(source.keys())
+    check_checkpoint(
+        {name: source.shape(name) for name in names},
+        specs,
+        tolerated,
+        {name: source.dtype(name) for name in names},
+    )
+    return WeightStore(source, specs, dtype, device)

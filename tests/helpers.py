@@ -1,0 +1,200 @@
+"""Shared pieces of the tests: the two tiny configurations, weights, replay schedules, comparisons."""
+
+from __future__ import annotations
+
+import random
+
+import torch
+
+import plain_qwen2 as plain
+
+# Two tiny configurations of the architecture that differ in every size and option.
+TINY_A = {
+    "architectures": ["Qwen2ForCausalLM"],
+    "vocab_size": 256,
+    "hidden_size": 64,
+    "intermediate_size": 160,
+    "num_hidden_layers": 2,
+    "num_attention_heads": 4,
+    "num_key_value_heads": 2,
+    "head_dim": 16,
+    "rms_norm_eps": 1e-6,
+    "rope_theta": 10000.0,
+    "tie_word_embeddings": True,
+    "max_position_embeddings": 512,
+}
+TINY_B = {
+    "architectures": ["Qwen2ForCausalLM"],
+    "vocab_size": 384,
+    "hidden_size": 96,
+    "intermediate_size": 224,
+    "num_hidden_layers": 3,
+    "num_attention_heads": 3,
+    "num_key_value_heads": 1,
+    "rms_norm_eps": 1e-5,
+    "rope_theta": 1000000.0,
+    "tie_word_embeddings": False,
+    "max_position_embeddings": 1024,
+}
+TINY = {"A": (TINY_A, 16, 0, 0.0), "B": (TINY_B, 8, 1, 0.02)}  # config, page size, seed, norm noise
+
+# Weights far larger than N(0, 0.02): logits then have a scale at which a wrong key shows.
+TEST_STD = 0.2
+
+FP32_TOL = 1e-4   # max |diff| / logit scale, float32 engine against the plain implementation
+BF16_TOL = 4e-2   # the same for the bfloat16 engine (8 bits of mantissa through a few layers)
+
+
+def tiny(name: str):
+    cfg, page, seed, noise = TINY[name]
+    return dict(cfg), page, plain.random_weights(cfg, seed, std=TEST_STD, norm_noise=noise)
+
+
+def bf16_rounded(weights: dict) -> dict:
+    return {k: v.to(torch.bfloat16).float() for k, v in weights.items()}
+
+
+def random_ids(vocab: int, length: int, seed: int) -> list[int]:
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(0, vocab, (length,), generator=g).tolist()
+
+
+# -- replay schedules -----------------------------------------------------------
+def schedule_whole(requests: dict) -> list[dict]:
+    return [
+        {"step": i, "entries": [{"id": rid, "tokens": ids, "want": list(range(len(ids)))}], "end": [rid]}
+        for i, (rid, ids) in enumerate(requests.items())
+    ]
+
+
+def schedule_tail(requests: dict, tail: int = 32) -> list[dict]:
+    """Most of each request in one step, the last `tail` tokens one by one."""
+    steps, n = [], 0
+    for rid, ids in requests.items():
+        head = max(1, len(ids) - tail)
+        steps.append({"step": n, "entries": [{"id": rid, "tokens": ids[:head], "want": list(range(head))}], "end": []})
+        n += 1
+        for at in range(head, len(ids)):
+            steps.append(
+                {"step": n, "entries": [{"id": rid, "tokens": [ids[at]], "want": [0]}], "end": [rid] if at == len(ids) - 1 else []}
+            )
+            n += 1
+        if head == len(ids):
+            steps[-1]["end"] = [rid]
+    return steps
+
+
+PORTIONS = (7, 2, 13, 2, 5, 3, 11, 2, 17, 4, 2, 29, 2, 9)
+
+
+def schedule_portions(requests: dict) -> list[dict]:
+    steps, n = [], 0
+    for rid, ids in requests.items():
+        at, turn = 0, 0
+        while at < len(ids):
+            size = min(PORTIONS[turn % len(PORTIONS)], len(ids) - at)
+            if len(ids) - at - size == 1:  # never leave a single token over: portions go down to two
+                size += 1
+            turn += 1
+            steps.append(
+                {
+                    "step": n,
+                    "entries": [{"id": rid, "tokens": ids[at : at + size], "want": list(range(size))}],
+                    "end": [rid] if at + size == len(ids) else [],
+                }
+            )
+            at += size
+            n += 1
+    return steps
+
+
+def schedule_mixed(requests: dict, seed: int = 0, live_max: int = 4) -> list[dict]:
+    """Up to four live requests; portions of some beside single tokens of others; some sit a step out."""
+    rng = random.Random(seed)
+    waiting = list(requests.items())
+    live: dict[str, int] = {}
+    steps, n = [], 0
+    while waiting or live:
+        while waiting and len(live) < live_max and (not live or rng.random() < 0.7):
+            rid, _ = waiting.pop(0)
+            live[rid] = 0
+        entries, end = [], []
+        for rid in list(live):
+            ids, at = requests[rid], live[rid]
+            if len(live) > 1 and rng.random() < 0.2:
+                continue  # left out of this step, goes on later
+            left = len(ids) - at
+            if at > 0 and rng.random() < 0.5:
+                size = 1
+            else:
+                size = min(left, rng.choice((2, 3, 5, 8, 13, 21, 40)))
+            if left - size == 1 and size > 1:
+                size += 1
+            entries.append({"id": rid, "tokens": ids[at : at + size], "want": list(range(size))})
+            live[rid] = at + size
+            if live[rid] == len(ids):
+                end.append(rid)
+                del live[rid]
+        if not entries:
+            continue
+        steps.append({"step": n, "entries": entries, "end": end})
+        n += 1
+    return steps
+
+
+def peak_tokens(steps: list[dict], granule: int = 64) -> int:
+    """The most tokens live requests hold at any time, each rounded up to `granule`."""
+    held: dict[str, int] = {}
+    peak = 0
+    for step in steps:
+        for entry in step["entries"]:
+            held[entry["id"]] = held.get(entry["id"], 0) + len(entry["tokens"])
+        peak = max(peak, sum(-(-v // granule) * granule for v in held.values()))
+        for rid in step["end"]:
+            held.pop(rid, None)
+    return peak
+
+
+def collect(steps: list[dict], outputs: dict) -> dict:
+    """Per request, the logits of every position, gathered from per-step outputs {step: array [wanted, vocab]}."""
+    rows: dict[str, dict[int, torch.Tensor]] = {}
+    cursor: dict[str, int] = {}
+    for step in steps:
+        out = outputs.get(step["step"])
+        at = 0
+        for entry in step["entries"]:
+            base = cursor.get(entry["id"], 0)
+            for place in entry["want"]:
+                rows.setdefault(entry["id"], {})[base + place] = torch.as_tensor(out[at])
+                at += 1
+            cursor[entry["id"]] = base + len(entry["tokens"])
+    return {rid: torch.stack([r[i] for i in sorted(r)]) for rid, r in rows.items()}
+
+
+def run_schedule(session, steps: list[dict]) -> dict:
+    outputs = {}
+    for step in steps:
+        result = session.run_step(step["entries"], step["end"])
+        if result is not None:
+            outputs[step["step"]] = result
+    return outputs
+
+
+def worst_error(got: dict, expected: dict) -> tuple[float, str, int]:
+    """(max |diff| / scale, request, position) over all requests."""
+    worst = (0.0, "", -1)
+    for rid, want in expected.items():
+        have = got[rid]
+        assert have.shape == want.shape, (rid, have.shape, want.shape)
+        scale = plain.logit_scale(want)
+        diff = (have.float() - want).abs().max(dim=-1).values / scale
+        at = int(diff.argmax())
+        if float(diff[at]) > worst[0]:
+            worst = (float(diff[at]), rid, at)
+    return worst
+
+
+def first_bad_position(have: torch.Tensor, want: torch.Tensor, tol: float) -> int | None:
+    scale = plain.logit_scale(want)
+    bad = ((have.float() - want).abs().max(dim=-1).values / scale) > tol
+    return int(bad.nonzero()[0]) if bool(bad.any()) else None

@@ -1,0 +1,130 @@
+"""The engine's bookkeeping (cache, batching, scheduling, replay) on the CPU.
+
+The CUDA kernels are replaced by their plain tensor-op references
+(``ref_kernels.RefKernels``), everything else is the product's code, and the
+results are compared with the plain whole-sequence implementation.  What these
+tests catch is a fault of the cache or of the batch, not of a kernel.
+"""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+import helpers
+import plain_qwen2 as plain
+from ref_kernels import RefKernels
+
+from distie_b200.config import EngineConfig, get_architecture
+from distie_b200.engine.engine import Engine
+from distie_b200.engine.trace_replay import TraceSession
+
+
+def cpu_engine(name: str, num_blocks: int, max_seqs: int = 8, **knobs) -> tuple[Engine, dict, dict]:
+    cfg, page, weights = helpers.tiny(name)
+    arch = get_architecture(cfg["architectures"][0])
+    config = EngineConfig(
+        num_blocks=num_blocks, page_size=page, max_seqs=max_seqs, dtype="float32", decode_graphs=False, device="cpu",
+        **{"token_budget": 4096, **knobs},
+    )
+    engine = Engine.assemble(arch, arch.config_cls.from_dict(cfg), weights, RefKernels(torch.float32), config)
+    return engine, cfg, weights
+
+
+def requests_for(cfg, lengths, seed=10):
+    return {f"r{i}": helpers.random_ids(cfg["vocab_size"], n, seed + i) for i, n in enumerate(lengths)}
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("mode", ["whole", "tail", "portions", "mixed"])
+def test_replay_modes_match_plain(name, mode):
+    cfg, page, weights = helpers.tiny(name)
+    requests = requests_for(cfg, [40, 67, 33, 90, 50, 36])
+    steps = {
+        "whole": helpers.schedule_whole,
+        "tail": helpers.schedule_tail,
+        "portions": helpers.schedule_portions,
+        "mixed": helpers.schedule_mixed,
+    }[mode](requests)
+    peak = helpers.peak_tokens(steps)
+    engine, _, _ = cpu_engine(name, num_blocks=peak // page)
+    session = TraceSession(engine)
+    got = helpers.collect(steps, helpers.run_schedule(session, steps))
+    expected = {rid: plain.forward_logits(ids, weights, cfg) for rid, ids in requests.items()}
+    error, rid, at = helpers.worst_error(got, expected)
+    assert error <= helpers.FP32_TOL, f"{mode}: request {rid} position {at} off by {error:.2e} of the logit scale"
+    assert engine.cache.free_pages() == engine.cache.total_pages(), "pages were lost"
+    assert engine.cache.free_seats == engine.cache.max_seats
+
+
+def test_mixed_schedule_reuses_pages():
+    cfg, page, _ = helpers.tiny("A")
+    requests = requests_for(cfg, [40, 67, 33, 90, 50, 36])
+    steps = helpers.schedule_mixed(requests)
+    peak = helpers.peak_tokens(steps)
+    total = sum(-(-len(v) // 64) * 64 for v in requests.values())
+    assert peak < total, "the schedule must need fewer pages than all requests together"
+    assert max(len(s["entries"]) for s in steps) >= 3
+    assert any(len(e["tokens"]) == 1 for s in steps for e in s["entries"])
+    assert any(len(e["tokens"]) > 1 for s in steps for e in s["entries"] if len(s["entries"]) > 1)
+
+
+def test_generate_matches_plain_and_sequential():
+    engine, cfg, weights = cpu_engine("B", num_blocks=64, max_seqs=4)
+    prompts = [helpers.random_ids(cfg["vocab_size"], n, 50 + n) for n in (1, 5, 17, 40)]
+    together = [r.token_ids for r in engine.generate(prompts, max_new_tokens=6)]
+    assert together == [plain.greedy_generate(p, weights, cfg, 6) for p in prompts]
+    alone = [engine.generate(p, max_new_tokens=6)[0].token_ids for p in prompts]
+    assert alone == together
+    assert engine.cache.free_pages() == engine.cache.total_pages()
+
+
+def test_chunked_prefill_and_preemption_keep_outputs():
+    # A pool so small that decoding runs out of pages: the newest request is preempted and recomputed.
+    engine, cfg, weights = cpu_engine("B", num_blocks=14, max_seqs=4, token_budget=24, prefill_chunk=11)
+    prompts = [helpers.random_ids(cfg["vocab_size"], n, 70 + n) for n in (17, 40, 23)]
+    results = engine.generate(prompts, max_new_tokens=12)
+    assert [r.token_ids for r in results] == [plain.greedy_generate(p, weights, cfg, 12) for p in prompts]
+    assert sum(r.preemptions for r in results) >= 1, "the pool was meant to be too small"
+    assert engine.cache.free_pages() == engine.cache.total_pages()
+
+
+def test_temperature_sampling_is_reproducible_and_batch_independent():
+    engine, cfg, _ = cpu_engine("A", num_blocks=64, max_seqs=4)
+    prompts = [helpers.random_ids(cfg["vocab_size"], n, 90 + n) for n in (9, 21, 14)]
+    first = [r.token_ids for r in engine.generate(prompts, max_new_tokens=8, temperature=0.8, seed=1)]
+    again = [r.token_ids for r in engine.generate(prompts, max_new_tokens=8, temperature=0.8, seed=1)]
+    assert first == again
+    alone = engine.generate(prompts[1], max_new_tokens=8, temperature=0.8, seed=2)[0].token_ids
+    assert alone == first[1], "request 1 has seed 1 + 1 in the batch: alone with seed 2 it must repeat itself"
+    other = [r.token_ids for r in engine.generate(prompts, max_new_tokens=8, temperature=0.8, seed=5)]
+    assert other != first
+
+
+def test_trace_free_running_and_forced():
+    engine, cfg, weights = cpu_engine("A", num_blocks=32)
+    prompt = helpers.random_ids(cfg["vocab_size"], 12, 5)
+    free = engine.trace(prompt, 5)
+    assert free.token_ids == plain.greedy_generate(prompt, weights, cfg, 5)
+    forced_ids = [3, 1, 4, 1, 5]
+    forced = engine.trace(prompt, 5, forced_ids)
+    want = plain.forward_logits(prompt + forced_ids[:-1], weights, cfg)[len(prompt) - 1 :]
+    assert float((forced.logits - want).abs().max()) <= helpers.FP32_TOL * plain.logit_scale(want)
+    with pytest.raises(ValueError):
+        engine.trace([], 3)
+    with pytest.raises(ValueError):
+        engine.trace(prompt, 3, [1])
+    assert engine.cache.free_pages() == engine.cache.total_pages()
+
+
+def test_corrupted_cache_is_detected():
+    """The comparison can fail: a page overwritten between steps changes later logits."""
+    engine, cfg, weights = cpu_engine("A", num_blocks=16)
+    ids = helpers.random_ids(cfg["vocab_size"], 40, 3)
+    session = TraceSession(engine)
+    session.run_step([{"id": "x", "tokens": ids[:30], "want": []}])
+    page = engine.cache.pages_held(session.live["x"][0])[0][0]
+    engine.cache.groups[0].slab[:, 0, page] += 1.0
+    got = session.run_step([{"id": "x", "tokens": ids[30:], "want": list(range(10))}], ["x"])
+    want = plain.forward_logits(ids, weights, cfg)[30:]
+    assert float((torch.as_tensor(got) - want).abs().max()) > 100 * helpers.FP32_TOL * plain.logit_scale(want)
