@@ -47,6 +47,7 @@ class _Bucket:
         self.tokens = torch.zeros(size, dtype=torch.int32, device=device)
         self.logits: torch.Tensor | None = None
         self.graph: torch.cuda.CUDAGraph | None = None
+        self.kernels_per_replay = 0  # own kernels inside the captured step
         pin = device.type == "cuda"
         self.host_ints = torch.zeros(5 * size, dtype=torch.int32, pin_memory=pin)
         self.host_floats = torch.zeros(2 * size, dtype=torch.float32, pin_memory=pin)
@@ -175,6 +176,52 @@ class ModelRunner:
         self.finish_step()
         return [token for token, item in zip(tokens, items) if item.samples]
 
+    @torch.inference_mode()
+    def decode_burst(self, items, steps: int) -> torch.Tensor:
+        """``steps`` greedy decode steps back to back on the device, each feeding the next.
+
+        The sampled tokens of a step become the next step's inputs without a trip to the
+        host; the caller has grown every request's pages for ``past_len + steps`` tokens
+        beforehand and advances its own bookkeeping afterwards.  Returns the tokens
+        ``[steps, rows]`` (int32, on the device).  Used to time the step itself.
+        """
+        rows = len(items)
+        size = self.bucket_for(rows)
+        bucket = self._buckets.get(size)
+        if bucket is None:
+            bucket = _Bucket(size, self.device)
+            self._buckets[size] = bucket
+        if any(item.seq.temperature > 0 or len(item.token_ids) != 1 for item in items):
+            raise ValueError("a burst decodes greedily, one token per request and step")
+        ints = bucket.host_ints.numpy()
+        ints[:size] = 0
+        ints[size : 2 * size] = 0
+        ints[2 * size : 3 * size] = np.arange(size, dtype=np.int32)
+        ints[3 * size : 4 * size] = self.cache.pad_seat
+        ints[4 * size :] = np.arange(size, dtype=np.int32)
+        bucket.host_floats.zero_()
+        advance = torch.zeros(size, dtype=torch.int32)
+        for row, item in enumerate(items):
+            ints[row] = item.token_ids[0]
+            ints[size + row] = item.past_len
+            ints[3 * size + row] = item.seq.seat
+            advance[row] = 1
+        advance = advance.to(self.device)
+        self.cache.upload_tables([item.seq.seat for item in items])
+        bucket.ints.copy_(bucket.host_ints, non_blocking=True)
+        bucket.floats.copy_(bucket.host_floats, non_blocking=True)
+        if bucket.graph is None:
+            self._capture(bucket)  # runs the first step once more than asked: same tokens, same slots
+        out = torch.empty((steps, size), dtype=torch.int32, device=self.device)
+        for k in range(steps):
+            bucket.graph.replay()
+            out[k].copy_(bucket.tokens)
+            bucket.ints[:size].copy_(bucket.tokens)
+            bucket.ints[size : 2 * size].add_(advance)
+        self.graph_replays += steps
+        self.steps += steps
+        return out[:, :rows]
+
     def _forward_bucket(self, bucket: _Bucket) -> None:
         layout = bucket.layout
         layout.max_kv_len = self.cache.max_tokens_per_request  # a fixed bound: the graph must not depend on lengths
@@ -194,8 +241,10 @@ class ModelRunner:
         if self._graph_pool is None:
             self._graph_pool = torch.cuda.graph_pool_handle()
         graph = torch.cuda.CUDAGraph()
+        before = self.kernels.launches
         with torch.cuda.graph(graph, pool=self._graph_pool):
             self._forward_bucket(bucket)
+        bucket.kernels_per_replay = self.kernels.launches - before
         bucket.graph = graph
         graph.replay()
         _log.info("decode graph captured bucket=%s", bucket.size)

@@ -25,6 +25,11 @@ class PreNormBlock:
         self.feed_forward = feed_forward
         self.dtype = dtype
 
+    @property
+    def graph_safe(self) -> bool:
+        """False when a part reads host-side batch data, which a captured step cannot replay."""
+        return all(getattr(part, "graph_safe", True) for part in (self.mixer, self.feed_forward))
+
     @classmethod
     def tensor_specs(cls, layer: LayerSpec, hidden_size: int) -> list[TensorSpec]:
         return (

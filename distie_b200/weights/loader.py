@@ -144,7 +144,12 @@ class DictSource:
 
 def open_weights(folder_or_dict, specs, tolerated, dtype: torch.dtype, device) -> WeightStore:
     """Open a model folder (or a dict of tensors), check it against ``specs``, return the store."""
-    source = DictSource(folder_or_dict) if isinstance(folder_or_dict, Mapping) else ModelTensors(folder_or_dict)
+    if isinstance(folder_or_dict, Mapping):
+        source = DictSource(folder_or_dict)
+    elif isinstance(folder_or_dict, (str, bytes)) or hasattr(folder_or_dict, "__fspath__"):
+        source = ModelTensors(folder_or_dict)
+    else:
+        source = folder_or_dict  # anything with keys / shape / dtype / tensor
     specs = list(specs)
     names = list(source.keys())
     check_checkpoint(

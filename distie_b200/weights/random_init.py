@@ -37,6 +37,42 @@ def random_tensors(specs, seed: int, std: float, norm_noise: float, dtype: torch
     return out
 
 
+class RandomSource:
+    """Random tensors made on demand on a device: a weight source without a folder.
+
+    Same distributions as :func:`random_tensors` (not the same numbers: every tensor has
+    its own generator, seeded by ``seed`` and its place in the declared order), for models
+    too large to be worth a trip through the file system.
+    """
+
+    def __init__(self, specs, seed: int = 0, std: float = _DEFAULT_STD, norm_noise: float = 0.0,
+                 dtype: torch.dtype = torch.bfloat16, device="cpu") -> None:
+        self._specs = {}
+        for index, spec in enumerate(specs):
+            self._specs.setdefault(spec.name, (spec, index))
+        self.seed, self.std, self.norm_noise, self._dtype, self.device = int(seed), std, norm_noise, dtype, torch.device(device)
+
+    def keys(self):
+        return self._specs.keys()
+
+    def shape(self, name):
+        return tuple(self._specs[name][0].shape)
+
+    def dtype(self, name):
+        return self._dtype
+
+    def tensor(self, name):
+        spec, index = self._specs[name]
+        generator = torch.Generator(device=self.device).manual_seed(self.seed * 1_000_003 + index)
+        if spec.role == "norm":
+            value = torch.ones(spec.shape, device=self.device)
+            if self.norm_noise:
+                value += torch.randn(spec.shape, generator=generator, device=self.device) * self.norm_noise
+        else:
+            value = torch.randn(spec.shape, generator=generator, device=self.device) * self.std
+        return value.to(self._dtype)
+
+
 def write_random_model(
     folder: str,
     config: dict,

@@ -1,0 +1,288 @@
+"""Generation through the Python entry point on the GPU, the parts alone, and a toy mixer."""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+import helpers
+import plain_qwen2 as plain
+
+pytestmark = pytest.mark.gpu
+
+
+def folder_for(name, tmp_path_factory, dtype="bfloat16"):
+    from distie_b200.weights import ModelTensors, write_random_model
+
+    cfg, page, _ = helpers.tiny(name)
+    folder = str(tmp_path_factory.mktemp(f"gen{name}"))
+    write_random_model(folder, cfg, seed=helpers.TINY[name][2], std=helpers.TEST_STD, norm_noise=helpers.TINY[name][3], dtype=dtype)
+    stored = ModelTensors(folder)
+    return folder, cfg, page, {n: stored.tensor(n).float() for n in stored.keys()}
+
+
+@pytest.fixture(scope="module", params=["A", "B"])
+def tiny_model(request, tmp_path_factory):
+    return folder_for(request.param, tmp_path_factory)
+
+
+@pytest.mark.parametrize("graphs", [True, False])
+def test_greedy_generation_float32(tiny_model, graphs):
+    from distie_b200.engine.engine import Engine
+
+    folder, cfg, page, weights = tiny_model
+    engine = Engine.load(folder, dtype="float32", num_blocks=64, page_size=page, max_seqs=4, decode_graphs=graphs)
+    prompts = [helpers.random_ids(cfg["vocab_size"], n, 30 + n) for n in (7, 13, 29)]
+    results = engine.generate(prompts, max_new_tokens=16)
+    assert [r.token_ids for r in results] == [plain.greedy_generate(p, weights, cfg, 16) for p in prompts]
+    assert all(r.finish_reason == "length" and r.completion_tokens == 16 for r in results)
+    if graphs:
+        assert engine.runner.graph_replays > 0, "pure-decode steps were meant to replay graphs"
+    assert engine.cache.free_pages() == engine.cache.total_pages()
+
+
+def test_first_tokens_of_a_sequence(tiny_model):
+    """Positions 0, 1, 2: a one-token prompt and the tokens right after it."""
+    from distie_b200.engine.engine import Engine
+
+    folder, cfg, page, weights = tiny_model
+    forced = [11, 5, 200, 7]
+    ids = [42] + forced[:-1]
+    want = {"x": plain.forward_logits(ids, weights, cfg)}
+    budget = helpers.Bf16Budget({"x": ids}, weights, cfg, want)
+    for dtype in ("float32", "bfloat16"):
+        engine = Engine.load(folder, dtype=dtype, num_blocks=16, page_size=page, max_seqs=2, decode_graphs=False)
+        got = {"x": engine.trace([42], 4, forced).logits}
+        if dtype == "float32":
+            assert helpers.worst_error(got, want)[0] <= helpers.FP32_TOL
+        else:
+            budget.check(got, want, "first tokens")
+
+
+def test_long_decoding_bfloat16_and_float32(tiny_model):
+    """Several hundred decode steps after a short prompt, teacher-forced so that logits stay comparable."""
+    from distie_b200.engine.engine import Engine
+
+    folder, cfg, page, weights = tiny_model
+    ids = helpers.random_ids(cfg["vocab_size"], 420, 77)
+    full = plain.forward_logits(ids, weights, cfg)
+    budget = helpers.Bf16Budget({"x": ids}, weights, cfg, {"x": full})
+    budget.max_error["x"], budget.rms_error["x"], budget.top1["x"] = helpers.error_stats(
+        plain.forward_logits(ids, {k: v.to(torch.bfloat16) for k, v in weights.items()}, cfg)[7:], full[7:]
+    )
+    want = {"x": full[7:]}
+    for dtype in ("float32", "bfloat16"):
+        engine = Engine.load(folder, dtype=dtype, num_blocks=64, page_size=page, max_seqs=2, decode_graphs=False)
+        trace = engine.trace(ids[:8], len(ids) - 8 + 1, ids[8:] + [0])
+        got = {"x": trace.logits[: want["x"].shape[0]]}
+        if dtype == "float32":
+            assert helpers.worst_error(got, want)[0] <= helpers.FP32_TOL
+        else:
+            budget.check(got, want, "long decoding")
+
+
+def test_preemption_and_chunked_prefill_on_gpu(tmp_path_factory):
+    """tiny-B, prompts 1/5/17/40/63, portions of 11 beside decoding, a pool that forces preemption."""
+    from distie_b200.engine.engine import Engine
+
+    folder, cfg, page, weights = folder_for("B", tmp_path_factory)
+    engine = Engine.load(
+        folder, dtype="float32", num_blocks=24, page_size=page, max_seqs=5, token_budget=32, prefill_chunk=11, decode_graphs=True
+    )
+    prompts = [helpers.random_ids(cfg["vocab_size"], n, 90 + n) for n in (1, 5, 17, 40, 63)]
+    results = engine.generate(prompts, max_new_tokens=24)
+    assert [r.token_ids for r in results] == [plain.greedy_generate(p, weights, cfg, 24) for p in prompts]
+    assert sum(r.preemptions for r in results) >= 1
+    sampled = engine.generate(prompts, max_new_tokens=24, temperature=0.8, seed=1)
+    again = engine.generate(prompts, max_new_tokens=24, temperature=0.8, seed=1)
+    assert [r.token_ids for r in sampled] == [r.token_ids for r in again]
+    assert engine.cache.free_pages() == engine.cache.total_pages()
+
+
+def test_missing_extension_fails_loudly(monkeypatch):
+    from distie_b200.csrc import build
+    from distie_b200.kernels import library
+
+    monkeypatch.setattr(library, "_libraries", {})
+    monkeypatch.setattr(library, "_functions", {})
+    monkeypatch.setattr(build, "build_cuda_unit", lambda name: "/nonexistent/libdistie.so")
+    with pytest.raises(library.KernelError):
+        library.function("distie_embed")
+
+
+# -- each part alone ------------------------------------------------------------
+def part_context(dtype, tensors, hidden):
+    from distie_b200.kernels import make_kernels
+    from distie_b200.parts.base import BuildContext
+    from distie_b200.weights.loader import DictSource, WeightStore
+
+    kernels = make_kernels(dtype, "cuda:0")
+    return BuildContext(kernels, hidden, WeightStore(DictSource(tensors), [], dtype, "cuda:0"))
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 2e-2)])
+def test_feed_forward_part_alone(dtype, tol):
+    from distie_b200.config import PartSpec
+    from distie_b200.parts import FEED_FORWARDS, build_part
+
+    hidden, inter = 72, 200
+    w = {f"ff.{n}_proj.weight": torch.randn(s) * 0.2 for n, s in (("gate", (inter, hidden)), ("up", (inter, hidden)), ("down", (hidden, inter)))}
+    w = {k: v.to(torch.bfloat16).float() for k, v in w.items()}
+    part = build_part(FEED_FORWARDS, PartSpec("swiglu", {"intermediate_size": inter}, "ff."), part_context(dtype, w, hidden))
+    x = torch.randn(9, hidden).to(torch.bfloat16).float()
+    got = part.forward(x.cuda().to(dtype), None).float().cpu()
+    want = plain.swiglu_mlp(x, {k.replace("ff.", "p."): v for k, v in w.items()}, "p.")
+    assert float((got - want).abs().max()) <= tol * float(want.abs().max())
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 2e-2)])
+def test_norm_part_alone(dtype, tol):
+    from distie_b200.config import PartSpec
+    from distie_b200.parts import NORMS, build_part
+
+    hidden = 88
+    w = {"n.weight": (1 + 0.1 * torch.randn(hidden)).to(torch.bfloat16).float()}
+    part = build_part(NORMS, PartSpec("rmsnorm", {"eps": 1e-5}, "n."), part_context(dtype, w, hidden))
+    x = torch.randn(5, hidden) * 4
+    out = torch.empty(5, hidden, dtype=dtype, device="cuda")
+    part.apply(None, x.cuda(), out)
+    want = plain.rms_norm(x, w["n.weight"], 1e-5)
+    assert float((out.float().cpu() - want).abs().max()) <= tol * float(want.abs().max())
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-5), (torch.bfloat16, 3e-2)])
+@pytest.mark.parametrize("window", [None, 9])
+def test_attention_part_alone(dtype, tol, window):
+    """The mixer over a real cache manager: a prompt in two portions, compared with the plain layer."""
+    from distie_b200.cache import CacheManager
+    from distie_b200.config import PartSpec
+    from distie_b200.engine.batch import BatchEntry, StepStaging, lay_out
+    from distie_b200.parts import MIXERS, LayerRun, build_part
+
+    hidden, heads, kv_heads, head_dim, theta, tokens = 80, 5, 1, 16, 5000.0, 37
+    names = {"q": (heads * head_dim, hidden), "k": (kv_heads * head_dim, hidden), "v": (kv_heads * head_dim, hidden)}
+    w = {f"a.{n}_proj.weight": (torch.randn(s) * 0.3).to(torch.bfloat16).float() for n, s in names.items()}
+    w.update({f"a.{n}_proj.bias": (torch.randn(s[0]) * 0.3).to(torch.bfloat16).float() for n, s in names.items()})
+    w["a.o_proj.weight"] = (torch.randn(hidden, heads * head_dim) * 0.3).to(torch.bfloat16).float()
+    spec = PartSpec(
+        "gqa_attention",
+        {"num_heads": heads, "num_kv_heads": kv_heads, "head_dim": head_dim, "qkv_bias": True, "out_bias": False,
+         "window": window, "position": PartSpec("rotary", {"head_dim": head_dim, "theta": theta})},
+        "a.",
+    )
+    ctx = part_context(dtype, w, hidden)
+    part = build_part(MIXERS, spec, ctx)
+    cache = CacheManager({0: MIXERS.get("gqa_attention").cache_need(spec)}, {}, num_pages=8, page_size=8, max_seats=2,
+                         max_tokens_per_request=64, dtype=dtype, device="cuda:0")
+    seat = cache.open_seat()
+    x = torch.randn(tokens, hidden).to(torch.bfloat16).float()
+    staging = StepStaging(256, torch.device("cuda:0"))
+    outs, done = [], 0
+    for count in (20, 17):
+        assert cache.grow(seat, done + count)
+        layout = lay_out([BatchEntry(seat, [0] * count, done)])
+        cache.upload_tables([seat])
+        step, _ = staging.upload(layout)
+        run = LayerRun(step=step, seqs=layout.seqs, kv=cache.kv_slot(0), writes_cache=True)
+        outs.append(part.forward(x[done : done + count].cuda().to(dtype), run).float().cpu())
+        done += count
+        cache.trim(seat, done)
+    ctx.kernels.check_errors()
+    want, _ = plain.attention_layer(x, w, "a.", torch.arange(tokens), heads, kv_heads, head_dim, theta, window)
+    assert float((torch.cat(outs) - want).abs().max()) <= tol * float(want.abs().max())
+    if window is not None:
+        assert len(cache.pages_held(seat)[0]) < -(-tokens // 8), "pages behind the window were meant to be given back"
+
+
+# -- a toy mixer with state of its own, registered from outside the package --------
+def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
+    """A running-mean mixer defined here: state per request, no change to the framework's files."""
+    from distie_b200.config import LayerCall, LayerSpec, ModelSpec, PartSpec, register_architecture, unregister_architecture
+    from distie_b200.engine.engine import Engine
+    from distie_b200.engine.trace_replay import TraceSession
+    from distie_b200.parts import MIXERS, StateNeed, TensorSpec
+    from distie_b200.weights import write_random_model
+
+    hidden, vocab = 48, 64
+
+    class RunningMeanMixer:
+        """delta[t] = W @ mean(x[0..t]) of the token's request; state = (sum [hidden], count [1])."""
+
+        graph_safe = False
+
+        def __init__(self, weight, kernels):
+            self.weight, self.kernels = weight, kernels
+
+        @classmethod
+        def tensor_specs(cls, spec, hidden_size):
+            return [TensorSpec(spec.prefix + "mix.weight", (hidden_size, hidden_size))]
+
+        @classmethod
+        def cache_need(cls, spec):
+            return None
+
+        @classmethod
+        def state_need(cls, spec):
+            return StateNeed((hidden + 1,), torch.float32)
+
+        @classmethod
+        def build(cls, spec, ctx):
+            return cls(ctx.weights.matrix(spec.prefix + "mix.weight"), ctx.kernels)
+
+        def forward(self, x, run):
+            means = torch.empty_like(x, dtype=torch.float32)
+            for seq in run.seqs:
+                state = run.state[seq.seat]
+                rows = x[seq.start : seq.start + seq.q_len].float()
+                sums = state[:hidden] + torch.cumsum(rows, 0)
+                counts = state[hidden] + torch.arange(1, seq.q_len + 1, device=x.device)
+                means[seq.start : seq.start + seq.q_len] = sums / counts[:, None]
+                state[:hidden] = sums[-1]
+                state[hidden] = counts[-1]
+            return self.kernels.linear(means.to(x.dtype), self.weight)
+
+    class ToyConfig:
+        def __init__(self, raw):
+            self.raw = raw
+            self.eos_token_id = None
+
+        @classmethod
+        def from_dict(cls, raw):
+            return cls(dict(raw))
+
+    def recipe(cfg):
+        layers = tuple(
+            LayerSpec(
+                "pre_norm",
+                PartSpec("test_running_mean", {}, f"l{i}."),
+                PartSpec("swiglu", {"intermediate_size": 80}, f"l{i}.ff."),
+                {"input": PartSpec("rmsnorm", {"eps": 1e-5}, f"l{i}.n1."), "post_mixer": PartSpec("rmsnorm", {"eps": 1e-5}, f"l{i}.n2.")},
+            )
+            for i in range(2)
+        )
+        return ModelSpec("ToyRunningMean", vocab, hidden, layers, (LayerCall(0, 0), LayerCall(1, 1)),
+                         PartSpec("rmsnorm", {"eps": 1e-5}, "norm."), "embed.weight", None)
+
+    MIXERS.register("test_running_mean", RunningMeanMixer)
+    register_architecture("ToyRunningMean", ToyConfig, recipe)
+    try:
+        folder = write_random_model(str(tmp_path / "toy"), {"architectures": ["ToyRunningMean"]}, seed=4, std=0.3, dtype="float32")
+        engine = Engine.load(folder, dtype="float32", num_blocks=4, page_size=16, max_seqs=3, decode_graphs=True)
+        assert not engine.runner.use_graphs, "a part that reads host-side batch data keeps steps eager"
+        assert engine.cache.states[0].shape == (4, hidden + 1) and not engine.cache.groups
+        session = TraceSession(engine)
+        ids_a, ids_b = helpers.random_ids(vocab, 21, 1), helpers.random_ids(vocab, 9, 2)
+        whole = session.run_step([{"id": "w", "tokens": ids_a, "want": list(range(21))}], ["w"])
+        parts = [
+            session.run_step([{"id": "a", "tokens": ids_a[:8], "want": list(range(8))}, {"id": "b", "tokens": ids_b, "want": [8]}], ["b"]),
+            session.run_step([{"id": "a", "tokens": ids_a[8:9], "want": [0]}]),
+            session.run_step([{"id": "a", "tokens": ids_a[9:], "want": list(range(12))}], ["a"]),
+        ]
+        cut = torch.cat([torch.as_tensor(parts[0][:8]), torch.as_tensor(parts[1]), torch.as_tensor(parts[2])])
+        assert float((cut - torch.as_tensor(whole)).abs().max()) <= 1e-4 * max(1.0, float(torch.as_tensor(whole).abs().max()))
+        seat = engine.cache.open_seat()  # a reopened seat starts from zero state
+        assert float(engine.cache.states[0][seat].abs().sum()) == 0.0
+        engine.cache.close_seat(seat)
+    finally:
+        MIXERS.unregister("test_running_mean")
+        unregister_architecture("ToyRunningMean")

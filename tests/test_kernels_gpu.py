@@ -1,0 +1,271 @@
+"""Each CUDA kernel alone against its plain reference, at sizes the engine's tiny models do not use."""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+import ref_kernels as ref
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+TOL = {torch.float32: 2e-5, torch.bfloat16: 1.6e-2}  # relative to the largest magnitude of the expected result
+
+
+@pytest.fixture(scope="module")
+def kernel_sets():
+    from distie_b200.kernels import make_kernels
+
+    return {dtype: make_kernels(dtype, "cuda:0") for dtype in DTYPES}
+
+
+def close(got, want, dtype, what=""):
+    scale = max(1e-6, float(want.float().abs().max()))
+    error = float((got.float() - want.float()).abs().max()) / scale
+    assert error <= TOL[dtype], f"{what}: off by {error:.3e} of the scale"
+
+
+def step_of(tokens_per_seq, pasts, seats, device="cuda"):
+    """StepTensors for a batch in which request i brings tokens_per_seq[i] tokens after pasts[i] cached ones."""
+    from distie_b200.kernels.interface import StepTensors
+
+    positions, token_seq = [], []
+    order = sorted(range(len(tokens_per_seq)), key=lambda i: (tokens_per_seq[i] != 1, i))
+    for row, i in enumerate(order):
+        positions += list(range(pasts[i], pasts[i] + tokens_per_seq[i]))
+        token_seq += [row] * tokens_per_seq[i]
+    total = len(positions)
+    as_i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=device)  # noqa: E731
+    return StepTensors(
+        token_ids=torch.zeros(total, dtype=torch.int32, device=device),
+        positions=as_i32(positions),
+        token_seq=as_i32(token_seq),
+        seq_seat=as_i32([seats[i] for i in order]),
+        num_tokens=total,
+        num_seqs=len(order),
+        num_decode_tokens=sum(1 for n in tokens_per_seq if n == 1),
+        max_kv_len=max(p + n for p, n in zip(pasts, tokens_per_seq)),
+    )
+
+
+def make_cache(dtype, pages, kv_heads, page_size, head_dim, seats, width, fill=True, seed=0):
+    from distie_b200.kernels.interface import KvSlot
+
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    shape = (pages, kv_heads, page_size, head_dim)
+    k = torch.randn(shape, generator=g, device="cuda").to(dtype) if fill else torch.zeros(shape, dtype=dtype, device="cuda")
+    v = torch.randn(shape, generator=g, device="cuda").to(dtype) if fill else torch.zeros(shape, dtype=dtype, device="cuda")
+    perm = torch.randperm(pages, generator=torch.Generator().manual_seed(seed))
+    table = torch.full((seats, width), -1, dtype=torch.int32)
+    table.view(-1)[: min(pages, seats * width)] = perm[: min(pages, seats * width)].to(torch.int32)
+    return KvSlot(k, v, table.cuda(), page_size, pages)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden,vocab", [(80, 97), (1536, 1000), (200, 33)])
+def test_embed(kernel_sets, dtype, hidden, vocab):
+    ks = kernel_sets[dtype]
+    table = torch.randn(vocab, hidden, device="cuda").to(dtype)
+    step = step_of([11], [0], [0])
+    step.token_ids = torch.randint(0, vocab, (11,), dtype=torch.int32, device="cuda")
+    out = torch.empty(11, hidden, dtype=torch.float32, device="cuda")
+    ks.embed(step, table, out)
+    assert torch.equal(out, ref.embed(step.token_ids, table))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows,hidden,eps", [(5, 96, 1e-5), (33, 1536, 1e-6), (2, 8200, 1e-6), (7, 50, 1e-3)])
+def test_add_rmsnorm(kernel_sets, dtype, rows, hidden, eps):
+    ks = kernel_sets[dtype]
+    residual = torch.randn(rows, hidden, device="cuda") * 3
+    delta = torch.randn(rows, hidden, device="cuda").to(dtype)
+    weight = 1 + 0.1 * torch.randn(hidden, device="cuda")
+    for with_delta in (True, False):
+        res = residual.clone()
+        out = torch.empty(rows, hidden, dtype=dtype, device="cuda")
+        ks.add_rmsnorm(delta if with_delta else None, res, weight, eps, out)
+        want_res, want = ref.add_rmsnorm(delta if with_delta else None, residual, weight, eps, dtype)
+        assert torch.allclose(res, want_res, atol=1e-6, rtol=1e-6)
+        close(out, want, dtype, "rmsnorm")
+    rows_index = torch.tensor([rows - 1, 0, rows // 2], dtype=torch.int32, device="cuda")
+    res = residual.clone()
+    out = torch.empty(3, hidden, dtype=dtype, device="cuda")
+    ks.add_rmsnorm(delta, res, weight, eps, out, rows_index)
+    _, want = ref.add_rmsnorm(delta, residual, weight, eps, dtype, rows_index)
+    assert torch.equal(res, residual), "row-selected norm must leave the residual alone"
+    close(out, want, dtype, "rmsnorm rows")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("tokens,inter", [(3, 224), (70, 8960), (1, 17)])
+def test_swiglu(kernel_sets, dtype, tokens, inter):
+    ks = kernel_sets[dtype]
+    gate_up = (torch.randn(tokens, 2 * inter, device="cuda") * 2).to(dtype)
+    out = torch.empty(tokens, inter, dtype=dtype, device="cuda")
+    ks.swiglu(gate_up, out)
+    close(out, ref.swiglu(gate_up), dtype, "swiglu")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("m,k,n,bias", [(5, 96, 40, True), (64, 1536, 2048, True), (7, 224, 96, False), (130, 80, 1000, False)])
+def test_linear(kernel_sets, dtype, m, k, n, bias):
+    ks = kernel_sets[dtype]
+    x = torch.randn(m, k, device="cuda").to(dtype)
+    w = (torch.randn(n, k, device="cuda") * 0.1).to(dtype)
+    b = torch.randn(n, device="cuda") if bias else None
+    want = torch.nn.functional.linear(x.double(), w.double(), b.double() if bias else None)
+    close(ks.linear(x, w, b), want, dtype, "linear")
+    got32 = ks.linear(x, w, b, out_dtype=torch.float32)
+    assert got32.dtype == torch.float32
+    close(got32, want, dtype, "linear float32 out")
+    if dtype == torch.bfloat16:  # a matrix stored in 32-bit keeps a 32-bit product
+        w32 = w.float() + 1e-4 * torch.randn(n, k, device="cuda")
+        want32 = torch.nn.functional.linear(x.double(), w32.double(), b.double() if bias else None)
+        close(ks.linear(x, w32, b, out_dtype=torch.float32), want32, torch.float32, "float32-stored matrix")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize(
+    "heads,kv_heads,head_dim,rotary_dim,interleaved,page",
+    [(4, 2, 16, 16, False, 16), (3, 1, 32, 32, False, 8), (12, 2, 128, 128, False, 16), (5, 5, 48, 24, True, 4), (6, 3, 80, 80, False, 32)],
+)
+def test_rope_kv_write(kernel_sets, dtype, heads, kv_heads, head_dim, rotary_dim, interleaved, page):
+    from distie_b200.kernels.interface import RotaryTable
+
+    ks = kernel_sets[dtype]
+    tokens_per_seq, pasts, seats = [1, 9, 1, 20], [37, 0, page * 2 - 1, page - 3], [2, 0, 3, 1]
+    step = step_of(tokens_per_seq, pasts, seats)
+    width = 16
+    kv = make_cache(dtype, 64, kv_heads, page, head_dim, 4, width, fill=False)
+    kv_ref = make_cache(dtype, 64, kv_heads, page, head_dim, 4, width, fill=False)
+    inv_freq = (1.0 / (10000.0 ** (torch.arange(0, rotary_dim, 2, dtype=torch.float32) / rotary_dim))).cuda()
+    rotary = RotaryTable(inv_freq, rotary_dim, interleaved)
+    qkv = torch.randn(step.num_tokens, (heads + 2 * kv_heads) * head_dim, device="cuda").to(dtype)
+    mine, theirs = qkv.clone(), qkv.clone()
+    ks.rope_kv_write(mine, step, kv, rotary, heads, kv_heads, head_dim)
+    ref.rope_kv_write(theirs, step, kv_ref, rotary, heads, kv_heads, head_dim)
+    ks.check_errors()
+    close(mine, theirs, dtype, "rotated q (k and v columns untouched)")
+    close(kv.k, kv_ref.k, dtype, "cached keys")
+    assert torch.equal(kv.v, kv_ref.v), "values are copied bit for bit"
+    assert float(kv.k.float().abs().sum()) > 0
+    # Nothing is written when the call only reads the cache; no rotation without a table.
+    kv_none = make_cache(dtype, 64, kv_heads, page, head_dim, 4, width, fill=False)
+    again = qkv.clone()
+    ks.rope_kv_write(again, step, None, None, heads, kv_heads, head_dim)
+    assert torch.equal(again, qkv) and float(kv_none.k.float().abs().sum()) == 0
+
+
+def filled_cache_for(dtype, kv_heads, head_dim, page, lengths, seed=1):
+    """A cache whose tables cover `lengths[i]` tokens for seat i, pages in scrambled order."""
+    pages_each = [-(-n // page) for n in lengths]
+    total = sum(pages_each) + 3
+    kv = make_cache(dtype, total, kv_heads, page, head_dim, len(lengths), max(pages_each) + 1, seed=seed)
+    perm = torch.randperm(total, generator=torch.Generator().manual_seed(seed)).to(torch.int32)
+    table = torch.full((len(lengths), max(pages_each) + 1), -1, dtype=torch.int32)
+    at = 0
+    for seat, count in enumerate(pages_each):
+        table[seat, :count] = perm[at : at + count]
+        at += count
+    kv.block_table = table.cuda()
+    return kv
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize(
+    "heads,kv_heads,head_dim,page,window",
+    [(4, 2, 16, 16, None), (3, 1, 32, 8, None), (12, 2, 128, 16, None), (6, 1, 64, 16, 37), (5, 5, 48, 4, None), (16, 2, 256, 32, 100), (14, 2, 80, 16, None)],
+)
+def test_attention_mixed_batch(kernel_sets, dtype, heads, kv_heads, head_dim, page, window):
+    """Portions beside single tokens: every token against its own request's pages only."""
+    ks = kernel_sets[dtype]
+    tokens_per_seq, pasts = [1, 23, 1, 2, 1], [130, 45, 0, 310, 63]
+    lengths = [p + n for p, n in zip(pasts, tokens_per_seq)]
+    kv = filled_cache_for(dtype, kv_heads, head_dim, page, lengths)
+    step = step_of(tokens_per_seq, pasts, list(range(5)))
+    qkv = torch.randn(step.num_tokens, (heads + 2 * kv_heads) * head_dim, device="cuda").to(dtype)
+    out = torch.zeros(step.num_tokens, heads * head_dim, dtype=dtype, device="cuda")
+    ks.attention(qkv, out, step, kv, heads, kv_heads, head_dim, window, head_dim**-0.5)
+    ks.check_errors()
+    want = ref.attention(qkv, step, kv, heads, kv_heads, head_dim, window, head_dim**-0.5)
+    close(out, want, dtype, "attention")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("head_dim,page,far", [(128, 16, 3), (64, 16, 511), (32, 8, 256), (128, 16, 1008)])
+def test_attention_finds_one_far_key(kernel_sets, dtype, head_dim, page, far):
+    """One key among a thousand is made to stand out; the output must be its value (a page edge included)."""
+    ks = kernel_sets[dtype]
+    heads, kv_heads, length = 4, 2, 1024
+    kv = filled_cache_for(dtype, kv_heads, head_dim, page, [length], seed=5)
+    kv.k.mul_(0.05)
+    step = step_of([1], [length - 1], [0])
+    qkv = torch.zeros(1, (heads + 2 * kv_heads) * head_dim, dtype=dtype, device="cuda")
+    qkv[0, : heads * head_dim] = 1.0
+    page_id = int(kv.block_table[0, far // page])
+    kv.k[page_id, :, far % page, :] = 6.0  # score head_dim * 6 * scale: far above everything else
+    for splits_len in (length, 1):  # many splits and a single one
+        step.max_kv_len = splits_len
+        out = torch.zeros(1, heads * head_dim, dtype=dtype, device="cuda")
+        ks.attention(qkv, out, step, kv, heads, kv_heads, head_dim, None, head_dim**-0.5)
+        want = kv.v[page_id, :, far % page, :].repeat_interleave(heads // kv_heads, dim=0).reshape(1, -1)
+        close(out, want, dtype, f"far key {far}")
+    # The same key just outside a window must not be seen; just inside it must.
+    for window, seen in ((length - 1 - far, False), (length - far, True)):
+        if window < 1:
+            continue
+        out = torch.zeros(1, heads * head_dim, dtype=dtype, device="cuda")
+        ks.attention(qkv, out, step, kv, heads, kv_heads, head_dim, window, head_dim**-0.5)
+        want = kv.v[page_id, :, far % page, :].repeat_interleave(heads // kv_heads, dim=0).reshape(1, -1)
+        error = float((out.float() - want.float()).abs().max())
+        assert (error < 0.05) == seen, f"window {window}: key {far} seen={error < 0.05}, expected {seen}"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_decode_kernel_equals_generic_kernel(kernel_sets, dtype):
+    """The split-KV kernel and the size-agnostic kernel are two routes to the same numbers."""
+    ks = kernel_sets[dtype]
+    heads, kv_heads, head_dim, page = 12, 2, 128, 16
+    pasts = [5, 1000, 255, 256, 15, 16, 700, 0]
+    kv = filled_cache_for(dtype, kv_heads, head_dim, page, [p + 1 for p in pasts], seed=9)
+    step = step_of([1] * 8, pasts, list(range(8)))
+    qkv = torch.randn(8, (heads + 2 * kv_heads) * head_dim, device="cuda").to(dtype)
+    fast = torch.zeros(8, heads * head_dim, dtype=dtype, device="cuda")
+    slow = torch.zeros_like(fast)
+    ks.attention(qkv, fast, step, kv, heads, kv_heads, head_dim, None, head_dim**-0.5)
+    step.num_decode_tokens = 0  # every token through the other kernel
+    ks.attention(qkv, slow, step, kv, heads, kv_heads, head_dim, None, head_dim**-0.5)
+    close(fast, slow, dtype, "decode vs generic")
+
+
+@pytest.mark.parametrize("vocab", [100, 384, 151936])
+def test_sampling(kernel_sets, vocab):
+    ks = kernel_sets[torch.float32]
+    rows = 6
+    logits = torch.randn(rows, vocab, device="cuda") * 3
+    logits[1, 7] = logits[1, 3] = logits[1].max() + 1  # a tie: the lowest index wins
+    out = torch.empty(rows, dtype=torch.int32, device="cuda")
+    ks.sample(logits, None, None, out)
+    greedy = logits.argmax(dim=-1).tolist()
+    assert [t for r, t in enumerate(out.tolist()) if r != 1] == [t for r, t in enumerate(greedy) if r != 1]
+    assert out[1].item() == 3
+    temperatures = torch.tensor([0.0, 0.7, 1.0, 1.5, 0.3, 2.0], device="cuda")
+    uniforms = torch.tensor([0.5, 0.0, 0.999999, 0.25, 0.5, 0.75], device="cuda")
+    ks.sample(logits, temperatures, uniforms, out)
+    picks = out.tolist()
+    assert picks[0] == int(logits[0].argmax())
+    for row in range(1, rows):
+        z = logits[row].double() / float(temperatures[row])
+        p = torch.exp(z - z.max())
+        cdf = torch.cumsum(p, 0) / p.sum()
+        u, i = float(uniforms[row]), picks[row]
+        below = float(cdf[i - 1]) if i > 0 else 0.0
+        assert below - 1e-5 <= u <= float(cdf[i]) + 1e-5, f"row {row}: picked {i}, cdf [{below}, {float(cdf[i])}], u {u}"
+    # The distribution over many draws follows the softmax.
+    small = torch.tensor([[0.0, 1.0, 2.0, -1.0]], device="cuda").repeat(4000, 1)
+    us = torch.rand(4000, device="cuda")
+    outs = torch.empty(4000, dtype=torch.int32, device="cuda")
+    ks.sample(small, torch.ones(4000, device="cuda"), us, outs)
+    freq = torch.bincount(outs.long(), minlength=4).float() / 4000
+    assert torch.allclose(freq.cpu(), torch.softmax(small[0].cpu(), -1), atol=0.03)

@@ -1,0 +1,84 @@
+"""Trace replay on the GPU against the plain implementation: every way of cutting, float32 and bfloat16."""
+
+from __future__ import annotations
+
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import helpers
+import plain_qwen2 as plain
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+MODES = {
+    "whole": helpers.schedule_whole,
+    "tail": helpers.schedule_tail,
+    "portions": helpers.schedule_portions,
+    "mixed": helpers.schedule_mixed,
+}
+LENGTHS = [40, 67, 33, 300, 50, 36, 129, 64]
+
+
+@pytest.fixture(scope="module", params=["A", "B"])
+def model(request, tmp_path_factory):
+    """A model folder of the tiny configuration, written by the random-weights mode, and its plain logits."""
+    from distie_b200.weights import ModelTensors, write_random_model
+
+    cfg, page, _ = helpers.tiny(request.param)
+    noise = helpers.TINY[request.param][3]
+    folder = str(tmp_path_factory.mktemp(f"tiny{request.param}"))
+    write_random_model(folder, cfg, seed=helpers.TINY[request.param][2], std=helpers.TEST_STD, norm_noise=noise, dtype="bfloat16")
+    stored = ModelTensors(folder)
+    weights = {name: stored.tensor(name).float() for name in stored.keys()}
+    requests = {f"r{i}": helpers.random_ids(cfg["vocab_size"], n, 10 + i) for i, n in enumerate(LENGTHS)}
+    expected = {rid: plain.forward_logits(ids, weights, cfg) for rid, ids in requests.items()}
+    budget = helpers.Bf16Budget(requests, weights, cfg, expected)
+    return {"folder": folder, "cfg": cfg, "page": page, "requests": requests, "expected": expected, "budget": budget}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("mode", list(MODES))
+def test_replay_matches_plain(model, mode, dtype):
+    from distie_b200.engine.trace_replay import TraceSession
+
+    steps = MODES[mode](model["requests"])
+    session = TraceSession.open(model["folder"], dtype, helpers.peak_tokens(steps), page_size=model["page"])
+    got = helpers.collect(steps, helpers.run_schedule(session, steps))
+    if dtype == "float32":
+        error, rid, at = helpers.worst_error(got, model["expected"])
+        if error > helpers.FP32_TOL:
+            first = helpers.first_bad_position(got[rid], model["expected"][rid], helpers.FP32_TOL)
+            pytest.fail(
+                f"{mode}: request {rid} (length {len(model['requests'][rid])}) first wrong at position {first}, "
+                f"worst {error:.2e} of the logit scale at {at}"
+            )
+    else:
+        model["budget"].check(got, model["expected"], mode)
+    cache = session.engine.cache
+    assert cache.free_pages() == cache.total_pages() and cache.free_seats == cache.max_seats
+
+
+def test_trace_run_program(model, tmp_path):
+    """The program itself: JSON lines in, done lines and .f32 files out, exit code 0."""
+    steps = helpers.schedule_mixed(model["requests"], seed=3)
+    out_dir = tmp_path / "out"
+    text = "".join(json.dumps(step) + "\n" for step in steps)
+    proc = subprocess.run(
+        [sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", model["folder"], "--dtype", "float32",
+         "--out", str(out_dir), "--max-tokens", str(helpers.peak_tokens(steps)), "--page-size", str(model["page"])],
+        input=text, capture_output=True, text=True, timeout=600,
+    )
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert proc.stdout.split("\n")[: len(steps)] == [f"done {s['step']}" for s in steps]
+    vocab = model["cfg"]["vocab_size"]
+    outputs = {s["step"]: np.fromfile(out_dir / f"{s['step']}.f32", dtype="<f4").reshape(-1, vocab) for s in steps}
+    got = helpers.collect(steps, outputs)
+    error, rid, at = helpers.worst_error(got, model["expected"])
+    assert error <= helpers.FP32_TOL, f"request {rid} position {at} off by {error:.2e}"
