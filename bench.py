@@ -289,6 +289,8 @@ def main() -> int:
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
     parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--only", default=None, choices=["decode", "prefill"],
+                        help="run one part and print a short line (for profiling captures; not a bench value)")
     args = parser.parse_args()
     if args.impl == "reference":
         print(json.dumps({
@@ -311,6 +313,13 @@ def main() -> int:
     engine = build_engine(shape, layers, 64, pages)
     weight_bytes = engine.model.weight_bytes()
     kv_bytes_per_token = engine.cache.bytes_per_token()
+
+    if args.only == "decode":
+        print(json.dumps({"only": "decode", "batch": args.batch, "layers": layers, **time_decode(engine, args.batch, args.steps, args.warmup)}))
+        return 0
+    if args.only == "prefill":
+        print(json.dumps({"only": "prefill", "layers": layers, **time_prefill(engine, repeats=max(1, args.steps))}))
+        return 0
 
     with ClockSampler() as sampler:
         head = time_decode(engine, args.batch, args.steps, args.warmup)

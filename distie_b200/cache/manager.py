@@ -76,6 +76,7 @@ class KvGroup:
         self.device_table: torch.Tensor | None = None
         self._host_tensor: torch.Tensor | None = None
         self._views: dict[int, KvSlot] = {}
+        self._uploaded = None  # CUDA event after the last upload: the pinned table waits for it before it changes
 
     def bytes_per_token(self, element_size: int) -> int:
         return 2 * len(self.slots) * self.need.num_kv_heads * self.need.head_dim * element_size
@@ -98,6 +99,10 @@ class KvGroup:
     def _mark(self, seat: int, column: int) -> None:
         self.dirty[seat] = min(self.dirty.get(seat, column), column)
 
+    def _before_write(self) -> None:
+        if self._uploaded is not None:
+            self._uploaded.synchronize()
+
     def grow(self, seat: int, tokens: int) -> None:
         held = self.seats.setdefault(seat, _SeatPages())
         count = self.missing(seat, tokens)
@@ -110,6 +115,7 @@ class KvGroup:
             )
         ids = list(self.pool.allocate(count))
         held.ids.extend(ids)
+        self._before_write()
         self.host_table[seat, start : start + count] = ids
         self._mark(seat, start)
 
@@ -122,6 +128,7 @@ class KvGroup:
         if drop <= 0:
             return 0
         self.pool.free(held.ids[:drop])
+        self._before_write()
         self.host_table[seat, held.first : keep_from] = -1
         self._mark(seat, held.first)
         del held.ids[:drop]
@@ -134,6 +141,7 @@ class KvGroup:
             return
         if held.ids:
             self.pool.free(held.ids)
+        self._before_write()
         self.host_table[seat, :] = -1
         self._mark(seat, 0)
 
@@ -155,11 +163,17 @@ class KvGroup:
     def upload(self, seats) -> None:
         if self.device_table is None:
             return
+        copied = False
         for seat in seats:
             column = self.dirty.pop(seat, None)
             if column is None:
                 continue
             self.device_table[seat, column:].copy_(self._host_tensor[seat, column:], non_blocking=True)
+            copied = True
+        if copied and self.device_table.is_cuda:
+            if self._uploaded is None:
+                self._uploaded = torch.cuda.Event()
+            self._uploaded.record()
 
     def slot_view(self, slot: int) -> KvSlot:
         view = self._views.get(slot)

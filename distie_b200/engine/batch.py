@@ -99,6 +99,8 @@ class StepStaging:
         self.device = device
         pin = device.type == "cuda"
         self._host = [torch.empty(capacity, dtype=torch.int32, pin_memory=pin) for _ in range(2)]
+        # A pinned buffer is rewritten only after the copy that last read it has run.
+        self._copied = [torch.cuda.Event() if pin else None for _ in range(2)]
         self._turn = 0
         self.device_buffer = torch.empty(capacity, dtype=torch.int32, device=device)
 
@@ -106,10 +108,14 @@ class StepStaging:
         n = layout.packed.shape[0]
         if n > self.capacity:
             raise ValueError(f"step needs {n} integers of staging, capacity is {self.capacity}")
-        host = self._host[self._turn]
+        host, copied = self._host[self._turn], self._copied[self._turn]
         self._turn ^= 1
+        if copied is not None:
+            copied.synchronize()
         host.numpy()[:n] = layout.packed
         self.device_buffer[:n].copy_(host[:n], non_blocking=True)
+        if copied is not None:
+            copied.record()
         return views(self.device_buffer, layout)
 
 

@@ -52,6 +52,17 @@ class _Bucket:
         self.host_ints = torch.zeros(5 * size, dtype=torch.int32, pin_memory=pin)
         self.host_floats = torch.zeros(2 * size, dtype=torch.float32, pin_memory=pin)
         self.layout = StepLayout([], size, size, size, size, 0, np.zeros(0, dtype=np.int32))
+        self.copied = torch.cuda.Event() if pin else None  # the pinned buffers wait for it before they change
+
+    def before_write(self) -> None:
+        if self.copied is not None:
+            self.copied.synchronize()
+
+    def upload(self) -> None:
+        self.ints.copy_(self.host_ints, non_blocking=True)
+        self.floats.copy_(self.host_floats, non_blocking=True)
+        if self.copied is not None:
+            self.copied.record()
 
 
 class ModelRunner:
@@ -127,7 +138,7 @@ class ModelRunner:
         n = len(sampling)
         host = self._floats_host[self._floats_turn]
         self._floats_turn ^= 1
-        array = host.numpy()
+        array = host.numpy()  # rewritten two steps later at the earliest, and every sampling step ends with a sync
         for row, item in enumerate(sampling):
             array[row] = max(0.0, float(item.seq.temperature))
             array[n + row] = uniform(item.seq.seed, len(item.seq.output_ids))
@@ -147,6 +158,7 @@ class ModelRunner:
         if bucket is None:
             bucket = _Bucket(size, self.device)
             self._buckets[size] = bucket
+        bucket.before_write()
         ints = bucket.host_ints.numpy()
         floats = bucket.host_floats.numpy()
         ids, positions, token_seq = ints[:size], ints[size : 2 * size], ints[2 * size : 3 * size]
@@ -164,8 +176,7 @@ class ModelRunner:
             floats[row] = max(0.0, float(item.seq.temperature))
             floats[size + row] = uniform(item.seq.seed, len(item.seq.output_ids))
         self.cache.upload_tables([item.seq.seat for item in items])
-        bucket.ints.copy_(bucket.host_ints, non_blocking=True)
-        bucket.floats.copy_(bucket.host_floats, non_blocking=True)
+        bucket.upload()
         if bucket.graph is None:
             self._capture(bucket)
         else:
@@ -193,6 +204,7 @@ class ModelRunner:
             self._buckets[size] = bucket
         if any(item.seq.temperature > 0 or len(item.token_ids) != 1 for item in items):
             raise ValueError("a burst decodes greedily, one token per request and step")
+        bucket.before_write()
         ints = bucket.host_ints.numpy()
         ints[:size] = 0
         ints[size : 2 * size] = 0
@@ -208,8 +220,7 @@ class ModelRunner:
             advance[row] = 1
         advance = advance.to(self.device)
         self.cache.upload_tables([item.seq.seat for item in items])
-        bucket.ints.copy_(bucket.host_ints, non_blocking=True)
-        bucket.floats.copy_(bucket.host_floats, non_blocking=True)
+        bucket.upload()
         if bucket.graph is None:
             self._capture(bucket)  # runs the first step once more than asked: same tokens, same slots
         out = torch.empty((steps, size), dtype=torch.int32, device=self.device)

@@ -45,9 +45,9 @@ FP32_TOL = 1e-4   # max |diff| / logit scale, float32 engine against the plain i
 # bfloat16 has no fixed tolerance: what the dtype itself costs is measured by running the plain
 # implementation with bfloat16 tensors (the reference's formulas, rounding after every operation),
 # and the engine, which keeps more in 32-bit, must stay within that: see `Bf16Budget`.
-BF16_MAX_MARGIN = 1.25
-BF16_RMS_MARGIN = 1.0
-BF16_TOP1_MARGIN = 0.02
+BF16_RMS_MARGIN = 1.0    # pooled rms error: at most what the formulas in bfloat16 cost
+BF16_MAX_MARGIN = 2.0    # largest single error: at most twice the largest of the formulas in bfloat16
+BF16_TOP1_MARGIN = 0.02  # pooled top-1 agreement may fall this far below theirs
 
 
 def tiny(name: str):
@@ -206,26 +206,39 @@ def first_bad_position(have: torch.Tensor, want: torch.Tensor, tol: float) -> in
 
 
 class Bf16Budget:
-    """Errors of the plain implementation run in bfloat16, per request, against its float32 run."""
+    """Errors of the plain implementation run in bfloat16 against its float32 run, pooled over requests.
 
-    def __init__(self, requests: dict, weights: dict, cfg: dict, expected: dict) -> None:
+    Per-request maxima are too noisy to compare (one near-tie in a softmax moves them by a factor
+    of two), so the budget pools: the rms over every logit of every request, the largest single
+    error, and the share of positions with the same arg-max.  One position that is wrong by a third
+    of the logit scale among thousands already doubles the pooled rms.
+    """
+
+    def __init__(self, requests: dict, weights: dict, cfg: dict, expected: dict, skip: int = 0) -> None:
         low = {k: v.to(torch.bfloat16) for k, v in weights.items()}
-        self.max_error, self.rms_error, self.top1 = {}, {}, {}
-        for rid, ids in requests.items():
-            rough = plain.forward_logits(ids, low, cfg)
-            self.max_error[rid], self.rms_error[rid], self.top1[rid] = error_stats(rough, expected[rid])
+        rough = {rid: plain.forward_logits(ids, low, cfg)[skip:] for rid, ids in requests.items()}
+        self.max_error, self.rms_error, self.top1 = pooled_stats(rough, {r: expected[r][-rough[r].shape[0]:] for r in rough})
 
     def check(self, got: dict, expected: dict, what: str = "") -> None:
-        for rid, want in expected.items():
-            worst, rms, top1 = error_stats(got[rid], want)
-            assert worst <= BF16_MAX_MARGIN * self.max_error[rid], (
-                f"{what} request {rid}: max error {worst:.3e} of the scale, the formulas in bfloat16 cost "
-                f"{self.max_error[rid]:.3e}; first position beyond: {first_bad_position(got[rid], want, BF16_MAX_MARGIN * self.max_error[rid])}"
-            )
-            assert rms <= BF16_RMS_MARGIN * self.rms_error[rid], (
-                f"{what} request {rid}: rms error {rms:.3e}, the formulas in bfloat16 cost {self.rms_error[rid]:.3e}"
-            )
-            assert top1 >= self.top1[rid] - BF16_TOP1_MARGIN, f"{what} request {rid}: top-1 agreement {top1:.3f} < {self.top1[rid]:.3f}"
+        worst, rms, top1 = pooled_stats(got, expected)
+        assert rms <= BF16_RMS_MARGIN * self.rms_error, (
+            f"{what}: pooled rms error {rms:.3e} of the logit scale; the formulas in bfloat16 cost {self.rms_error:.3e}"
+        )
+        assert worst <= BF16_MAX_MARGIN * self.max_error, (
+            f"{what}: largest error {worst:.3e} of the logit scale; the formulas in bfloat16 reach {self.max_error:.3e}"
+        )
+        assert top1 >= self.top1 - BF16_TOP1_MARGIN, f"{what}: top-1 agreement {top1:.3f}, theirs {self.top1:.3f}"
+
+
+def pooled_stats(have: dict, want: dict) -> tuple[float, float, float]:
+    """(largest, rms) of |diff| / logit scale over all requests, and the pooled top-1 agreement."""
+    diffs, same = [], []
+    for rid, target in want.items():
+        assert have[rid].shape == target.shape, (rid, have[rid].shape, target.shape)
+        diffs.append(((have[rid].float() - target).abs() / plain.logit_scale(target)).flatten())
+        same.append((have[rid].argmax(-1) == target.argmax(-1)).float())
+    diff, same = torch.cat(diffs), torch.cat(same)
+    return float(diff.max()), float(diff.pow(2).mean().sqrt()), float(same.mean())
 
 
 def error_stats(have: torch.Tensor, want: torch.Tensor) -> tuple[float, float, float]:

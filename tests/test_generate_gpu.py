@@ -46,13 +46,12 @@ def test_first_tokens_of_a_sequence(tiny_model):
     from distie_b200.engine.engine import Engine
 
     folder, cfg, page, weights = tiny_model
-    forced = [11, 5, 200, 7]
-    ids = [42] + forced[:-1]
-    want = {"x": plain.forward_logits(ids, weights, cfg)}
-    budget = helpers.Bf16Budget({"x": ids}, weights, cfg, want)
+    starts = {f"s{i}": helpers.random_ids(cfg["vocab_size"], 5, 200 + i) for i in range(16)}
+    want = {rid: plain.forward_logits(ids[:4], weights, cfg) for rid, ids in starts.items()}
+    budget = helpers.Bf16Budget({rid: ids[:4] for rid, ids in starts.items()}, weights, cfg, want)
     for dtype in ("float32", "bfloat16"):
         engine = Engine.load(folder, dtype=dtype, num_blocks=16, page_size=page, max_seqs=2, decode_graphs=False)
-        got = {"x": engine.trace([42], 4, forced).logits}
+        got = {rid: engine.trace(ids[:1], 4, ids[1:]).logits for rid, ids in starts.items()}
         if dtype == "float32":
             assert helpers.worst_error(got, want)[0] <= helpers.FP32_TOL
         else:
@@ -66,10 +65,7 @@ def test_long_decoding_bfloat16_and_float32(tiny_model):
     folder, cfg, page, weights = tiny_model
     ids = helpers.random_ids(cfg["vocab_size"], 420, 77)
     full = plain.forward_logits(ids, weights, cfg)
-    budget = helpers.Bf16Budget({"x": ids}, weights, cfg, {"x": full})
-    budget.max_error["x"], budget.rms_error["x"], budget.top1["x"] = helpers.error_stats(
-        plain.forward_logits(ids, {k: v.to(torch.bfloat16) for k, v in weights.items()}, cfg)[7:], full[7:]
-    )
+    budget = helpers.Bf16Budget({"x": ids}, weights, cfg, {"x": full}, skip=7)
     want = {"x": full[7:]}
     for dtype in ("float32", "bfloat16"):
         engine = Engine.load(folder, dtype=dtype, num_blocks=64, page_size=page, max_seqs=2, decode_graphs=False)
