@@ -287,3 +287,71 @@ extern "C" int distie_attention_decode(const void* q, int q_row_stride, void* ou
                                   num_kv_heads, page_size, num_pages, window, scale, num_splits, error, stream);
   return DISTIE_ERR_UNSUPPORTED;
 }
+
+// ---------------------------------------------------------------------------
+// distie_attention_decode_static: the same split-KV attention for callers that
+// cannot allocate.  Declared and explained in no_alloc.h.
+// ---------------------------------------------------------------------------
+#include "no_alloc.h"
+
+namespace distie {
+
+// Room for the partial results of one call, held by every GPU that loads this library until the
+// process exits.  Host code must not pass this name to a kernel: on the host it is only a handle
+// for cudaGetSymbolAddress; the device address is looked up once per device below.
+static __device__ __align__(256) float g_static_scratch[DISTIE_STATIC_SCRATCH_FLOATS];
+
+constexpr int kMaxDevices = 64;
+static float* g_static_scratch_address[kMaxDevices] = {};
+
+// Device address of the array on the current device; looked up on the first call on that device.
+static int static_scratch_address(float** out) {
+  int device = -1;
+  cudaError_t err = cudaGetDevice(&device);
+  if (err != cudaSuccess) return (int)err;
+  if (device < 0 || device >= kMaxDevices) return DISTIE_ERR_ARG;
+  if (g_static_scratch_address[device] == nullptr) {
+    void* address = nullptr;
+    err = cudaGetSymbolAddress(&address, g_static_scratch);
+    if (err != cudaSuccess) return (int)err;
+    g_static_scratch_address[device] = static_cast<float*>(address);
+  }
+  *out = g_static_scratch_address[device];
+  return 0;
+}
+
+}  // namespace distie
+
+extern "C" long long distie_attention_decode_static_capacity(void) { return DISTIE_STATIC_SCRATCH_FLOATS; }
+
+extern "C" const char* distie_no_alloc_error(int code) {
+  switch (code) {
+    case 0: return "ok";
+    case DISTIE_ERR_ARG: return "invalid argument";
+    case DISTIE_ERR_UNSUPPORTED: return "head size or element type not supported by this kernel";
+    case DISTIE_ERR_SCRATCH_TOO_SMALL:
+      return "tokens * heads * splits * (head_dim + 2) exceeds the built-in scratch of "
+             "DISTIE_STATIC_SCRATCH_FLOATS floats: use fewer splits or tokens, or the allocating entry point";
+    default: return "CUDA error (the code is a cudaError_t)";
+  }
+}
+
+extern "C" int distie_attention_decode_static(const void* q, int q_row_stride, void* out, int out_row_stride,
+                                              const int* positions, const int* token_seq, const int* seq_seat,
+                                              const int* block_table, int table_width, const void* k_cache,
+                                              const void* v_cache, int tokens, int num_heads, int num_kv_heads,
+                                              int head_dim, int page_size, int num_pages, int window, float scale,
+                                              int num_splits, int dtype, int* error, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (num_heads < 1 || head_dim < 1 || num_splits < 1) return DISTIE_ERR_ARG;
+  const long long needed = distie_attention_decode_scratch_floats(tokens, num_heads, head_dim, num_splits);
+  if (needed > (long long)DISTIE_STATIC_SCRATCH_FLOATS) return DISTIE_ERR_SCRATCH_TOO_SMALL;
+  float* scratch = nullptr;
+  const int status = static_scratch_address(&scratch);
+  if (status != 0) return status;
+  // Nothing in the array has to start at zero: the first kernel writes every partial
+  // (max, sum, mix) of every (token, head, split) before the merge kernel reads it.
+  return distie_attention_decode(q, q_row_stride, out, out_row_stride, scratch, positions, token_seq, seq_seat,
+                                 block_table, table_width, k_cache, v_cache, tokens, num_heads, num_kv_heads, head_dim,
+                                 page_size, num_pages, window, scale, num_splits, dtype, error, stream);
+}

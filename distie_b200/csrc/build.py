@@ -44,7 +44,7 @@ CUDA_UNITS: dict[str, list[str]] = {
     # every model needs these
     "base": ["elementwise.cu", "attention_generic.cu", "attention_decode.cu", "sampling.cu"],
 }
-_HEADERS = ["common.cuh"]
+_HEADERS = ["common.cuh", "no_alloc.h"]
 
 
 class BuildError(RuntimeError):
