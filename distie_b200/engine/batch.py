@@ -21,7 +21,7 @@ from typing import Sequence
 import numpy as np
 import torch
 
-from ..kernels.interface import StepTensors
+from ..kernels.interface import Q_TILE, StepTensors
 from ..parts.base import SeqSlice
 
 
@@ -43,7 +43,8 @@ class StepLayout:
     num_decode_tokens: int
     num_rows: int
     max_kv_len: int
-    packed: np.ndarray  # int32: token_ids | positions | token_seq | seq_seat | logit_rows
+    packed: np.ndarray  # int32: token_ids | positions | token_seq | seq_seat | logit_rows | q_tiles
+    num_q_tiles: int = 0
 
 
 def lay_out(entries: Sequence[BatchEntry], vocab_size: int | None = None) -> StepLayout:
@@ -68,10 +69,13 @@ def lay_out(entries: Sequence[BatchEntry], vocab_size: int | None = None) -> Ste
         max_kv = max(max_kv, entry.past_len + q_len)
     total = cursor
     rows = sum(len(e.want) for e in entries)
-    packed = np.empty(3 * total + len(entries) + rows, dtype=np.int32)
+    tiles = [(s.start + at, min(Q_TILE, s.q_len - at)) for s in seqs if s.q_len > 1 for at in range(0, s.q_len, Q_TILE)]
+    packed = np.empty(3 * total + len(entries) + rows + 2 * len(tiles), dtype=np.int32)
     ids, positions, token_seq = packed[:total], packed[total : 2 * total], packed[2 * total : 3 * total]
     seats = packed[3 * total : 3 * total + len(entries)]
-    logit_rows = packed[3 * total + len(entries) :]
+    logit_rows = packed[3 * total + len(entries) : 3 * total + len(entries) + rows]
+    if tiles:
+        packed[3 * total + len(entries) + rows :] = np.asarray(tiles, dtype=np.int32).reshape(-1)
     for row, index in enumerate(order):
         entry = entries[index]
         s, n = starts[index], len(entry.tokens)
@@ -88,7 +92,7 @@ def lay_out(entries: Sequence[BatchEntry], vocab_size: int | None = None) -> Ste
             at += 1
     if vocab_size is not None and total and (ids.min() < 0 or ids.max() >= vocab_size):
         raise ValueError(f"token id outside [0, {vocab_size})")
-    return StepLayout(seqs, total, len(entries), decode_tokens, rows, max_kv, packed)
+    return StepLayout(seqs, total, len(entries), decode_tokens, rows, max_kv, packed, len(tiles))
 
 
 class StepStaging:
@@ -131,4 +135,8 @@ def views(buffer: torch.Tensor, layout: StepLayout) -> tuple[StepTensors, torch.
         num_decode_tokens=layout.num_decode_tokens,
         max_kv_len=layout.max_kv_len,
     )
-    return step, buffer[3 * t + b : 3 * t + b + layout.num_rows]
+    rows_end = 3 * t + b + layout.num_rows
+    if layout.num_q_tiles:
+        step.q_tiles = buffer[rows_end : rows_end + 2 * layout.num_q_tiles]
+        step.num_q_tiles = layout.num_q_tiles
+    return step, buffer[3 * t + b : rows_end]

@@ -74,7 +74,7 @@ class ModelRunner:
         self.sampler = Sampler(self.kernels)
         self.max_step_tokens = max_step_tokens
         self.max_seqs = max_seqs
-        self.staging = StepStaging(4 * max_step_tokens + max_seqs, self.device)
+        self.staging = StepStaging(5 * max_step_tokens + 3 * max_seqs, self.device)
         self._floats_host = [
             torch.zeros(2 * max_seqs, dtype=torch.float32, pin_memory=self.device.type == "cuda") for _ in range(2)
         ]

@@ -23,12 +23,15 @@ from .library import KernelError, check, function
 
 _CODE = {torch.float32: 0, torch.bfloat16: 1}
 _DECODE_HEAD_DIMS = (16, 32, 64, 128, 256)
+_PREFILL_HEAD_DIMS = (64, 128)  # tensor-core attention for portions of prompts (bfloat16)
+_SKINNY_ROWS = 16               # weight-streaming products take up to this many rows of x
 
 _ERROR_TEXT = {
     1: "a token id outside the vocabulary reached the embedding",
     2: "a new token's page is missing from its block table (cache write)",
     3: "a block table does not cover the keys a token attends to",
     4: "a block table does not cover the keys a decoded token attends to",
+    5: "a block table does not cover the keys a portion of a prompt attends to",
 }
 
 
@@ -50,6 +53,8 @@ class DeviceKernels(KernelSet):
             torch.backends.cudnn.allow_tf32 = False
             torch.set_float32_matmul_precision("highest")
         library.load_unit("base")
+        if dtype == torch.bfloat16:
+            library.load_unit("bf16")
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.error_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.launches = 0  # own kernels launched (library products are not counted)
@@ -96,12 +101,40 @@ class DeviceKernels(KernelSet):
             x32 = x if x.dtype == torch.float32 else x.float()
             y = torch.addmm(bias, x32, weight.t()) if bias is not None else torch.mm(x32, weight.t())
             return y if out_dtype == torch.float32 else self._bias_cast(y, None, out_dtype)
+        if self._skinny(x, weight):
+            out = torch.empty((x.shape[0], weight.shape[0]), dtype=out_dtype, device=x.device)
+            self._linear_skinny(x, weight, bias, out, 0)
+            return out
         if bias is None and out_dtype == self.dtype:
             return torch.mm(x, weight.t())
         y32 = torch.mm(x, weight.t(), out_dtype=torch.float32)
         if out_dtype == torch.float32:
             return y32 if bias is None else y32.add_(bias)
         return self._bias_cast(y32, bias, out_dtype)
+
+    def _skinny(self, x, weight) -> bool:
+        return (
+            self.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.dtype == torch.bfloat16
+            and x.shape[0] <= _SKINNY_ROWS and weight.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and x.stride(1) == 1
+        )
+
+    def _linear_skinny(self, x, weight, bias, out, swiglu: int) -> None:
+        check(
+            function("distie_linear_skinny")(
+                x.data_ptr(), x.stride(0), weight.data_ptr(), bias.data_ptr() if bias is not None else None,
+                out.data_ptr(), out.stride(0), x.shape[0], weight.shape[0], weight.shape[1], _CODE[out.dtype],
+                swiglu, self._stream(),
+            ),
+            "linear_skinny",
+        )
+        self.launches += 1
+
+    def linear_swiglu(self, x, weight):
+        if self._skinny(x, weight):
+            out = torch.empty((x.shape[0], weight.shape[0] // 2), dtype=self.dtype, device=x.device)
+            self._linear_skinny(x, weight, None, out, 1)
+            return out
+        return super().linear_swiglu(x, weight)
 
     def _bias_cast(self, y32, bias, out_dtype):
         out = torch.empty(y32.shape, dtype=out_dtype, device=y32.device)
@@ -174,7 +207,19 @@ class DeviceKernels(KernelSet):
             )
             self.launches += 1 if splits == 1 else 2
         rest = step.num_tokens - n_dec
-        if rest > 0:
+        if rest > 0 and self.dtype == torch.bfloat16 and head_dim in _PREFILL_HEAD_DIMS and step.num_q_tiles and n_dec == step.num_decode_tokens:
+            check(
+                function("distie_attention_prefill")(
+                    qkv.data_ptr(), qkv.stride(0), out.data_ptr(), out.stride(0), step.q_tiles.data_ptr(),
+                    step.num_q_tiles, step.positions.data_ptr(), step.token_seq.data_ptr(), step.seq_seat.data_ptr(),
+                    kv.block_table.data_ptr(), kv.block_table.shape[-1], kv.k.data_ptr(), kv.v.data_ptr(), num_heads,
+                    num_kv_heads, head_dim, kv.page_size, kv.num_pages, window, float(scale),
+                    self.error_flag.data_ptr(), self._stream(),
+                ),
+                "attention_prefill",
+            )
+            self.launches += 1
+        elif rest > 0:
             check(
                 function("distie_attention_generic")(
                     qkv.data_ptr() + n_dec * qkv.stride(0) * element, qkv.stride(0),

@@ -24,6 +24,9 @@ from dataclasses import dataclass
 import torch
 
 
+Q_TILE = 64  # tokens per tile of StepTensors.q_tiles
+
+
 @dataclass
 class StepTensors:
     token_ids: torch.Tensor
@@ -34,6 +37,8 @@ class StepTensors:
     num_seqs: int
     num_decode_tokens: int  # the first this-many tokens are single-token rows
     max_kv_len: int = 0  # bound on the keys any token sees; a captured step uses a fixed bound
+    q_tiles: torch.Tensor | None = None  # [n, 2] int32: (first token, rows <= Q_TILE) of each tile of the
+    num_q_tiles: int = 0                 # multi-token entries; a tile holds consecutive tokens of one request
 
 
 @dataclass
@@ -73,6 +78,13 @@ class KernelSet(ABC):
     @abstractmethod
     def swiglu(self, gate_up, out) -> None:
         """out = silu(gate_up[:, :I]) * gate_up[:, I:]."""
+
+    def linear_swiglu(self, x, weight):
+        """silu(x Wg^T) * (x Wu^T) for weight = [Wg; Wu] stacked along the rows; sets may fuse it."""
+        gate_up = self.linear(x, weight)
+        out = torch.empty((x.shape[0], weight.shape[0] // 2), dtype=gate_up.dtype, device=x.device)
+        self.swiglu(gate_up, out)
+        return out
 
     @abstractmethod
     def rope_kv_write(self, qkv, step: StepTensors, kv: KvSlot | None, rotary: RotaryTable | None,

@@ -29,6 +29,10 @@ _SIGNATURES: dict[str, tuple[str, list]] = {
     "distie_attention_decode": ("base", [P, I, P, I, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, F, I, I, P, P]),
     "distie_attention_decode_scratch_floats": ("base", [I, I, I, I]),
     "distie_sample": ("base", [P, L, I, I, P, P, P, P]),
+    "distie_attention_prefill": ("bf16", [P, I, P, I, P, I, P, P, P, P, I, P, P, I, I, I, I, I, I, F, P, P]),
+    "distie_attention_prefill_tile": ("bf16", []),
+    "distie_linear_skinny": ("bf16", [P, I, P, P, P, I, I, I, I, I, I, P]),
+    "distie_linear_skinny_max_rows": ("bf16", []),
 }
 _RESULT = {"distie_attention_decode_scratch_floats": c_longlong}
 

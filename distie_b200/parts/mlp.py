@@ -44,7 +44,4 @@ class SwiGluFeedForward:
         )
 
     def forward(self, x: torch.Tensor, run: LayerRun) -> torch.Tensor:
-        gate_up = self.gate_up(x)
-        act = torch.empty((x.shape[0], self.inter), dtype=gate_up.dtype, device=x.device)
-        self.kernels.swiglu(gate_up, act)
-        return self.down(act)
+        return self.down(self.kernels.linear_swiglu(x, self.gate_up.weight))

@@ -37,7 +37,13 @@ def step_of(tokens_per_seq, pasts, seats, device="cuda"):
         token_seq += [row] * tokens_per_seq[i]
     total = len(positions)
     as_i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=device)  # noqa: E731
-    return StepTensors(
+    tiles, start = [], 0
+    for i in order:
+        n = tokens_per_seq[i]
+        if n > 1:
+            tiles += [(start + at, min(64, n - at)) for at in range(0, n, 64)]
+        start += n
+    step = StepTensors(
         token_ids=torch.zeros(total, dtype=torch.int32, device=device),
         positions=as_i32(positions),
         token_seq=as_i32(token_seq),
@@ -47,6 +53,10 @@ def step_of(tokens_per_seq, pasts, seats, device="cuda"):
         num_decode_tokens=sum(1 for n in tokens_per_seq if n == 1),
         max_kv_len=max(p + n for p, n in zip(pasts, tokens_per_seq)),
     )
+    if tiles:
+        step.q_tiles = as_i32(tiles).reshape(-1)
+        step.num_q_tiles = len(tiles)
+    return step
 
 
 def make_cache(dtype, pages, kv_heads, page_size, head_dim, seats, width, fill=True, seed=0):
@@ -108,7 +118,11 @@ def test_swiglu(kernel_sets, dtype, tokens, inter):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("m,k,n,bias", [(5, 96, 40, True), (64, 1536, 2048, True), (7, 224, 96, False), (130, 80, 1000, False)])
+@pytest.mark.parametrize(
+    "m,k,n,bias",
+    [(5, 96, 40, True), (64, 1536, 2048, True), (7, 224, 96, False), (130, 80, 1000, False), (1, 1536, 2048, True),
+     (16, 200, 57, True), (9, 8960, 1536, False), (8, 1536, 1000, False), (3, 72, 9, True), (17, 96, 40, True)],
+)
 def test_linear(kernel_sets, dtype, m, k, n, bias):
     ks = kernel_sets[dtype]
     x = torch.randn(m, k, device="cuda").to(dtype)
@@ -123,6 +137,17 @@ def test_linear(kernel_sets, dtype, m, k, n, bias):
         w32 = w.float() + 1e-4 * torch.randn(n, k, device="cuda")
         want32 = torch.nn.functional.linear(x.double(), w32.double(), b.double() if bias else None)
         close(ks.linear(x, w32, b, out_dtype=torch.float32), want32, torch.float32, "float32-stored matrix")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("m,k,inter", [(3, 96, 100), (8, 1536, 8960), (13, 200, 57), (40, 96, 224), (1, 64, 8)])
+def test_linear_swiglu(kernel_sets, dtype, m, k, inter):
+    ks = kernel_sets[dtype]
+    x = torch.randn(m, k, device="cuda").to(dtype)
+    w = (torch.randn(2 * inter, k, device="cuda") * 0.1).to(dtype)
+    gate_up = torch.nn.functional.linear(x.double(), w.double())
+    want = torch.nn.functional.silu(gate_up[:, :inter]) * gate_up[:, inter:]
+    close(ks.linear_swiglu(x, w), want, dtype, "fused gate/up + SwiGLU")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -220,6 +245,47 @@ def test_attention_finds_one_far_key(kernel_sets, dtype, head_dim, page, far):
         want = kv.v[page_id, :, far % page, :].repeat_interleave(heads // kv_heads, dim=0).reshape(1, -1)
         error = float((out.float() - want.float()).abs().max())
         assert (error < 0.05) == seen, f"window {window}: key {far} seen={error < 0.05}, expected {seen}"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("head_dim,page,window", [(128, 16, None), (64, 8, None), (128, 16, 70), (64, 16, 200), (128, 32, 1)])
+def test_prompt_portion_attention_long_context(kernel_sets, dtype, head_dim, page, window):
+    """A portion of 150 tokens after 900 cached ones beside a whole short prompt: tiles, diagonal, window edges."""
+    ks = kernel_sets[dtype]
+    heads, kv_heads = 6, 2
+    tokens_per_seq, pasts = [150, 1, 70, 64], [900, 40, 0, 64]
+    kv = filled_cache_for(dtype, kv_heads, head_dim, page, [p + n for p, n in zip(pasts, tokens_per_seq)], seed=3)
+    step = step_of(tokens_per_seq, pasts, list(range(4)))
+    qkv = torch.randn(step.num_tokens, (heads + 2 * kv_heads) * head_dim, device="cuda").to(dtype)
+    out = torch.zeros(step.num_tokens, heads * head_dim, dtype=dtype, device="cuda")
+    ks.attention(qkv, out, step, kv, heads, kv_heads, head_dim, window, head_dim**-0.5)
+    ks.check_errors()
+    want = ref.attention(qkv, step, kv, heads, kv_heads, head_dim, window, head_dim**-0.5)
+    close(out, want, dtype, "attention over a long context")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("far", [5, 511, 512, 959, 1000])
+def test_prompt_portion_finds_one_far_key(kernel_sets, dtype, far):
+    """Rows of a portion whose one far key stands out must return that key's value, rows before it must not."""
+    ks = kernel_sets[dtype]
+    heads, kv_heads, head_dim, page, past, count = 4, 2, 128, 16, 960, 64
+    kv = filled_cache_for(dtype, kv_heads, head_dim, page, [past + count], seed=6)
+    kv.k.mul_(0.05)
+    page_id = int(kv.block_table[0, far // page])
+    kv.k[page_id, :, far % page, :] = 6.0
+    step = step_of([count], [past], [0])
+    qkv = torch.zeros(count, (heads + 2 * kv_heads) * head_dim, dtype=dtype, device="cuda")
+    qkv[:, : heads * head_dim] = 1.0
+    value = kv.v[page_id, :, far % page, :].repeat_interleave(heads // kv_heads, dim=0).reshape(1, -1).float()
+    for window in (None, 40):
+        out = torch.zeros(count, heads * head_dim, dtype=dtype, device="cuda")
+        ks.attention(qkv, out, step, kv, heads, kv_heads, head_dim, window, head_dim**-0.5)
+        for row in range(count):
+            pos = past + row
+            seen = far <= pos and (window is None or far > pos - window)
+            hit = float((out[row].float() - value[0]).abs().max()) < 0.05
+            assert hit == seen, f"far {far} window {window}: row at position {pos} saw it={hit}, expected {seen}"
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
