@@ -1,0 +1,299 @@
+// Split-KV attention for single tokens (decoding) on the tensor cores, bfloat16.
+//
+// Decoding reads every cached key and value of a request once per step.  The
+// float32-math kernel in attention_decode.cu spends far more instructions per
+// byte than the memory system needs time per byte (a dot product per key and
+// head on the CUDA cores, reduced over lanes with shuffles); this one lets the
+// tensor cores do the products so that the loads set the pace:
+//
+//   grid   (token, kv head * chunks of up to 16 query heads, split)
+//   block  4 warps; a warp takes groups of 16 keys of the split in turn
+//   S      the query heads of the group are the 16 rows of mma.m16n8k16, 8 keys
+//          the columns, head_dim the reduction:  S[head, key] = q[head] . k[key]
+//   P V    the same heads are the rows, 16 keys the reduction, head_dim the columns
+//
+// Operands come straight from global memory in 16-byte pieces, without shared
+// memory: the reduction index of an mma may be enumerated in any order as long as
+// both operands agree, and so may the columns of the output.  A lane therefore
+// loads 8 consecutive elements of a key row and uses them as its share of two
+// k-steps of S, and 2 * head_dim / 16 consecutive elements of 4 value rows, from
+// which it assembles its B fragments of P V with byte permutes; output column
+// (n-tile t, lane group g) stands for dimension g * head_dim / 8 + t.
+//
+// Softmax state (max, sum) is float32 per lane; the four warps and, with several
+// splits, the CTAs of a token are merged as in the other kernel (same scratch
+// layout, same merge kernel).  head_dim 64 or 128.
+#include "common.cuh"
+
+namespace distie {
+
+constexpr int kMmaDecodeWarps = 4;
+
+__device__ __forceinline__ uint4 load16(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+__device__ __forceinline__ void mma_16816_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__device__ __forceinline__ uint32_t word_of(const uint4& v, int i) {
+  return i == 0 ? v.x : (i == 1 ? v.y : (i == 2 ? v.z : v.w));
+}
+
+template <int D>
+__global__ void __launch_bounds__(kMmaDecodeWarps * 32)
+attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, __nv_bfloat16* __restrict__ out,
+                            int out_row_stride, float* __restrict__ scratch_o, float* __restrict__ scratch_ml,
+                            const int* __restrict__ positions, const int* __restrict__ token_seq,
+                            const int* __restrict__ seq_seat, const int* __restrict__ block_table, int table_width,
+                            const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
+                            int num_heads, int group_size, int head_chunks, int num_kv_heads, int page_size,
+                            int num_pages, int window, float scale_log2, int* __restrict__ error) {
+  constexpr int QC = D / 32;      // 16-byte pieces of a key row per lane (and of a query row)
+  constexpr int NT = D / 8;       // output n-tiles
+  constexpr int VW = D / 64;      // 16-byte pieces of a value row per lane
+  __shared__ float sh_m[kMmaDecodeWarps][16], sh_l[kMmaDecodeWarps][16];
+  __shared__ float sh_o[kMmaDecodeWarps][16][D + 1];
+
+  const int t = blockIdx.x;
+  const int kv_head = blockIdx.y / head_chunks, chunk = blockIdx.y % head_chunks;
+  const int split = blockIdx.z, num_splits = gridDim.z;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, c = lane & 3;
+  const int head0 = kv_head * group_size + chunk * 16;
+  const int heads_here = min(16, group_size - chunk * 16);
+
+  const int pos = positions[t];
+  const int seat = seq_seat[token_seq[t]];
+  const int* table = block_table + (size_t)seat * table_width;
+  const int first = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  const int first_page = first / page_size;
+  const int pages = pos / page_size - first_page + 1;
+  const int pages_per_split = (pages + num_splits - 1) / num_splits;
+  const int lo = max(first, (first_page + split * pages_per_split) * page_size);
+  const int hi = min(pos, (first_page + (split + 1) * pages_per_split) * page_size - 1);
+
+  // Query fragments: rows g and g + 8 of the head chunk, 8 consecutive dims per piece.
+  uint4 qa[QC], qb[QC];
+  const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+  for (int j = 0; j < QC; ++j) {
+    const __nv_bfloat16* base = q + (size_t)t * q_row_stride + 32 * j + 8 * c;
+    qa[j] = g < heads_here ? *reinterpret_cast<const uint4*>(base + (size_t)(head0 + g) * D) : zero;
+    qb[j] = g + 8 < heads_here ? *reinterpret_cast<const uint4*>(base + (size_t)(head0 + g + 8) * D) : zero;
+  }
+
+  float o[NT][4];
+#pragma unroll
+  for (int i = 0; i < NT; ++i)
+#pragma unroll
+    for (int r = 0; r < 4; ++r) o[i][r] = 0.f;
+  float row_max[2] = {-INFINITY, -INFINITY}, row_sum[2] = {0.f, 0.f};
+
+  const int lo16 = lo & ~15;
+  const int groups = hi >= lo ? (hi - lo16) / 16 + 1 : 0;
+  for (int grp = warp; grp < groups; grp += kMmaDecodeWarps) {
+    const int base_key = lo16 + grp * 16;
+    // ---- loads: 2 key rows (columns g and g + 8 of S), 4 value rows (reduction slots of P V) ----
+    uint4 kr[2][QC], vr[4][VW];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int key = base_key + g + 8 * h;
+      bool ok = key >= lo && key <= hi;
+      size_t at = 0;
+      if (ok) {
+        const int page = table[key / page_size];
+        if (page < 0 || page >= num_pages) {
+          if (error) atomicExch(error, 4);
+          ok = false;
+        } else {
+          at = (((size_t)page * num_kv_heads + kv_head) * page_size + key % page_size) * D + 8 * c;
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < QC; ++j) kr[h][j] = ok ? load16(k_cache + at + 32 * j) : zero;
+    }
+#pragma unroll
+    for (int s = 0; s < 4; ++s) {
+      const int key = base_key + 2 * c + (s & 1) + 8 * (s >> 1);  // slots 2c, 2c+1, 2c+8, 2c+9
+      bool ok = key >= lo && key <= hi;
+      size_t at = 0;
+      if (ok) {
+        const int page = table[key / page_size];
+        if (page < 0 || page >= num_pages) {
+          ok = false;
+        } else {
+          at = (((size_t)page * num_kv_heads + kv_head) * page_size + key % page_size) * D + g * (D / 8);
+        }
+      }
+#pragma unroll
+      for (int w = 0; w < VW; ++w) vr[s][w] = ok ? load16(v_cache + at + 8 * w) : zero;
+    }
+
+    // ---- S = Q K^T for keys base..base+7 (s1) and base+8..base+15 (s2) ---------------------------
+    float s1[4] = {0.f, 0.f, 0.f, 0.f}, s2[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int j = 0; j < QC; ++j) {
+      mma_16816_bf16(s1, qa[j].x, qb[j].x, qa[j].y, qb[j].y, kr[0][j].x, kr[0][j].y);
+      mma_16816_bf16(s1, qa[j].z, qb[j].z, qa[j].w, qb[j].w, kr[0][j].z, kr[0][j].w);
+      mma_16816_bf16(s2, qa[j].x, qb[j].x, qa[j].y, qb[j].y, kr[1][j].x, kr[1][j].y);
+      mma_16816_bf16(s2, qa[j].z, qb[j].z, qa[j].w, qb[j].w, kr[1][j].z, kr[1][j].w);
+    }
+
+    // ---- mask and online softmax; rows: [0] head g, [1] head g + 8 ----------------------------------
+    float p1[4], p2[4], corr[2];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const int key1 = base_key + 2 * c + (r & 1), key2 = key1 + 8;
+      p1[r] = (key1 >= lo && key1 <= hi) ? s1[r] * scale_log2 : -INFINITY;
+      p2[r] = (key2 >= lo && key2 <= hi) ? s2[r] * scale_log2 : -INFINITY;
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      float m = fmaxf(fmaxf(p1[2 * h], p1[2 * h + 1]), fmaxf(p2[2 * h], p2[2 * h + 1]));
+      m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+      m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+      const float m_new = fmaxf(row_max[h], m);
+      corr[h] = m_new == -INFINITY ? 1.f : exp2f(row_max[h] - m_new);
+      row_max[h] = m_new;
+      const float shift = m_new == -INFINITY ? 0.f : m_new;
+      float sum = 0.f;
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        p1[2 * h + e] = exp2f(p1[2 * h + e] - shift);
+        p2[2 * h + e] = exp2f(p2[2 * h + e] - shift);
+        sum += p1[2 * h + e] + p2[2 * h + e];
+      }
+      row_sum[h] = row_sum[h] * corr[h] + sum;
+    }
+    const uint32_t a0 = pack2(p1[0], p1[1]), a1 = pack2(p1[2], p1[3]);
+    const uint32_t a2 = pack2(p2[0], p2[1]), a3 = pack2(p2[2], p2[3]);
+
+    // ---- O = O * corr + P V --------------------------------------------------------------------------
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      o[nt][0] *= corr[0]; o[nt][1] *= corr[0];
+      o[nt][2] *= corr[1]; o[nt][3] *= corr[1];
+      const int w = (nt >> 1) & 3, piece = nt >> 3;
+      const uint32_t sel = (nt & 1) ? 0x7632u : 0x5410u;
+      const uint32_t b0 = __byte_perm(word_of(vr[0][piece], w), word_of(vr[1][piece], w), sel);
+      const uint32_t b1 = __byte_perm(word_of(vr[2][piece], w), word_of(vr[3][piece], w), sel);
+      mma_16816_bf16(o[nt], a0, a1, a2, a3, b0, b1);
+    }
+  }
+
+  // ---- merge the warps ---------------------------------------------------------------------------------
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    float l = row_sum[h];
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    if (c == 0) { sh_m[warp][g + 8 * h] = row_max[h]; sh_l[warp][g + 8 * h] = l; }
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      sh_o[warp][g + 8 * h][(2 * c) * (D / 8) + nt] = o[nt][2 * h];
+      sh_o[warp][g + 8 * h][(2 * c + 1) * (D / 8) + nt] = o[nt][2 * h + 1];
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < heads_here * D; idx += kMmaDecodeWarps * 32) {
+    const int hd = idx / D, e = idx % D;
+    float m_all = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kMmaDecodeWarps; ++w) m_all = fmaxf(m_all, sh_m[w][hd]);
+    float l_all = 0.f, acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < kMmaDecodeWarps; ++w) {
+      const float weight = sh_m[w][hd] == -INFINITY ? 0.f : exp2f(sh_m[w][hd] - m_all);
+      l_all += sh_l[w][hd] * weight;
+      acc += sh_o[w][hd][e] * weight;
+    }
+    const int head = head0 + hd;
+    if (num_splits == 1) {
+      out[(size_t)t * out_row_stride + (size_t)head * D + e] = __float2bfloat16_rn(l_all > 0.f ? acc / l_all : 0.f);
+    } else {
+      const size_t row = ((size_t)t * num_heads + head) * num_splits + split;
+      scratch_o[row * D + e] = acc;
+      if (e == 0) {
+        scratch_ml[row * 2] = m_all;  // in base-2 units, like everything in this file
+        scratch_ml[row * 2 + 1] = l_all;
+      }
+    }
+  }
+}
+
+// Combines the partial results of the splits of one (token, head): maxima are base-2 exponents.
+__global__ void __launch_bounds__(128)
+attention_decode_mma_merge_kernel(const float* __restrict__ scratch_o, const float* __restrict__ scratch_ml,
+                                  __nv_bfloat16* __restrict__ out, int out_row_stride, int num_heads, int head_dim,
+                                  int num_splits) {
+  const int t = blockIdx.x, head = blockIdx.y;
+  const size_t row0 = ((size_t)t * num_heads + head) * num_splits;
+  float m_all = -INFINITY;
+  for (int s = 0; s < num_splits; ++s) m_all = fmaxf(m_all, scratch_ml[(row0 + s) * 2]);
+  for (int e = threadIdx.x; e < head_dim; e += blockDim.x) {
+    float l_all = 0.f, acc = 0.f;
+    for (int s = 0; s < num_splits; ++s) {
+      const float ms = scratch_ml[(row0 + s) * 2];
+      const float weight = ms == -INFINITY ? 0.f : exp2f(ms - m_all);
+      l_all += scratch_ml[(row0 + s) * 2 + 1] * weight;
+      acc += scratch_o[(row0 + s) * head_dim + e] * weight;
+    }
+    out[(size_t)t * out_row_stride + (size_t)head * head_dim + e] =
+        __float2bfloat16_rn(l_all > 0.f ? acc / l_all : 0.f);
+  }
+}
+
+}  // namespace distie
+
+using namespace distie;
+
+// Same arguments and scratch layout as distie_attention_decode (bfloat16 only).
+extern "C" int distie_attention_decode_mma(const void* q, int q_row_stride, void* out, int out_row_stride,
+                                           float* scratch, const int* positions, const int* token_seq,
+                                           const int* seq_seat, const int* block_table, int table_width,
+                                           const void* k_cache, const void* v_cache, int tokens, int num_heads,
+                                           int num_kv_heads, int head_dim, int page_size, int num_pages, int window,
+                                           float scale, int num_splits, int* error, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (num_heads < 1 || num_kv_heads < 1 || num_heads % num_kv_heads != 0 || page_size < 1 || table_width < 1 ||
+      num_splits < 1 || num_splits > 65535 || (num_splits > 1 && scratch == nullptr) || (q_row_stride & 7))
+    return DISTIE_ERR_ARG;
+  if (head_dim != 64 && head_dim != 128) return DISTIE_ERR_UNSUPPORTED;
+  const int group = num_heads / num_kv_heads;
+  const int chunks = (group + 15) / 16;
+  const dim3 grid(tokens, num_kv_heads * chunks, num_splits);
+  float* scratch_o = scratch;
+  float* scratch_ml = scratch ? scratch + (size_t)tokens * num_heads * num_splits * head_dim : nullptr;
+  const float scale_log2 = scale * 1.4426950408889634f;
+#define DISTIE_MMA_DECODE(DV)                                                                                     \
+  attention_decode_mma_kernel<DV><<<grid, kMmaDecodeWarps * 32, 0, stream>>>(                                     \
+      (const __nv_bfloat16*)q, q_row_stride, (__nv_bfloat16*)out, out_row_stride, scratch_o, scratch_ml, positions, \
+      token_seq, seq_seat, block_table, table_width, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, \
+      num_heads, group, chunks, num_kv_heads, page_size, num_pages, window, scale_log2, error)
+  if (head_dim == 64) DISTIE_MMA_DECODE(64);
+  else DISTIE_MMA_DECODE(128);
+#undef DISTIE_MMA_DECODE
+  DISTIE_LAUNCH_CHECK();
+  if (num_splits > 1) {
+    const dim3 merge_grid(tokens, num_heads);
+    attention_decode_mma_merge_kernel<<<merge_grid, head_dim >= 128 ? 128 : 64, 0, stream>>>(
+        scratch_o, scratch_ml, (__nv_bfloat16*)out, out_row_stride, num_heads, head_dim, num_splits);
+    DISTIE_LAUNCH_CHECK();
+  }
+  return 0;
+}

@@ -105,4 +105,20 @@ __device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&v)[8]) {
   *reinterpret_cast<uint4*>(p) = raw;
 }
 
+// Four consecutive elements as floats (16-byte aligned for float, 8-byte for bfloat16).
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  return make_float4(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u),
+                     __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xffff0000u));
+}
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16* p, float4 v) {
+  uint2 raw;
+  __nv_bfloat162 t;
+  t = __floats2bfloat162_rn(v.x, v.y); raw.x = *reinterpret_cast<uint32_t*>(&t);
+  t = __floats2bfloat162_rn(v.z, v.w); raw.y = *reinterpret_cast<uint32_t*>(&t);
+  *reinterpret_cast<uint2*>(p) = raw;
+}
+
 }  // namespace distie

@@ -70,6 +70,71 @@ __global__ void add_rmsnorm_kernel(const T* __restrict__ delta, float* __restric
   }
 }
 
+// The same for rows whose width is a multiple of 4 and at most 16 * blockDim.x: every thread
+// loads all its elements before it computes anything (one round trip to memory instead of one
+// per loop iteration) and keeps the summed residual in registers for the second pass.
+// `delta` may also be the float32 partial sums of a product whose K was split over several CTAs:
+// `splits` slices, `split_stride` elements apart, which are added up here in a fixed order.
+template <typename T, typename DT>
+__global__ void add_rmsnorm_vec_kernel(const DT* __restrict__ delta, int splits, size_t split_stride,
+                                       float* __restrict__ residual, const float* __restrict__ weight,
+                                       T* __restrict__ out, const int* __restrict__ rows_index, int hidden,
+                                       float eps) {
+  constexpr int VPT = 4;
+  __shared__ float scratch[32];
+  const int out_row = blockIdx.x;
+  const int row = rows_index ? rows_index[out_row] : out_row;
+  float* res = residual + (size_t)row * hidden;
+  const DT* del = delta ? delta + (size_t)row * hidden : nullptr;
+  T* dst = out + (size_t)out_row * hidden;
+  const bool write_back = (delta != nullptr) && (rows_index == nullptr);
+  const int chunks = hidden >> 2;
+  float4 v[VPT], wv[VPT];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int ch = threadIdx.x + i * blockDim.x;
+    v[i] = wv[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (ch < chunks) {
+      v[i] = load4(res + 4 * ch);
+      wv[i] = load4(weight + 4 * ch);
+    }
+  }
+  if (del) {
+    for (int sp = 0; sp < splits; ++sp) {
+      float4 d[VPT];
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const int ch = threadIdx.x + i * blockDim.x;
+        d[i] = ch < chunks ? load4(del + sp * split_stride + 4 * ch) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        v[i].x += d[i].x; v[i].y += d[i].y; v[i].z += d[i].z; v[i].w += d[i].w;
+      }
+    }
+  }
+  float sumsq = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int ch = threadIdx.x + i * blockDim.x;
+    if (write_back && ch < chunks) store4(res + 4 * ch, v[i]);
+    sumsq += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+  }
+  const float total = block_sum(sumsq, scratch);
+  const float rstd = rsqrtf(total / (float)hidden + eps);
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int ch = threadIdx.x + i * blockDim.x;
+    if (ch >= chunks) continue;
+    float4 y;
+    y.x = wv[i].x * to_float(from_float<T>(v[i].x * rstd));
+    y.y = wv[i].y * to_float(from_float<T>(v[i].y * rstd));
+    y.z = wv[i].z * to_float(from_float<T>(v[i].z * rstd));
+    y.w = wv[i].w * to_float(from_float<T>(v[i].w * rstd));
+    store4(dst + 4 * ch, y);
+  }
+}
+
 // ---------------------------------------------------------------------------
 // Rotation of q and k (rotate-half or interleaved pairs, over the first
 // `rotary_dim` dims of each head) in float32, fused with the write of the new
@@ -162,6 +227,95 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict_
   }
 }
 
+// The common case (rotate-half over the whole head, head_dim a multiple of 16, rows aligned to
+// 16 bytes) in pieces of 8 elements: a thread loads the 8 low and the 8 matching high elements of
+// one head, rotates them and stores them (q in place, k to its page); the values are copied in
+// pieces of 8.  All loads of a thread come before its stores.
+// The input may be the product itself (QT = T; q is then rotated in place when q_out is the input)
+// or the float32 partial sums of a product whose K was split (`splits` slices, `split_stride`
+// elements apart), to which the bias is added here: the projection's epilogue, the rotation and
+// the cache write are then one kernel and q goes to its own buffer.
+template <typename T, typename QT>
+__global__ void rope_kv_write_vec_kernel(const QT* in, int splits, size_t split_stride, int row_stride,
+                                         const float* __restrict__ bias, T* q_out, int q_out_stride,
+                                         const int* __restrict__ positions, const int* __restrict__ token_seq,
+                                         const int* __restrict__ seq_seat, const int* __restrict__ block_table,
+                                         int table_width, const float* __restrict__ inv_freq, T* __restrict__ k_cache,
+                                         T* __restrict__ v_cache, int num_heads, int num_kv_heads, int head_dim,
+                                         int page_size, int num_pages, int write_cache, int* __restrict__ error) {
+  extern __shared__ float trig[];  // cos[head_dim/2], sin[head_dim/2]
+  const int t = blockIdx.x;
+  const int pos = positions[t];
+  const int half = head_dim >> 1;
+  for (int j = threadIdx.x; j < half; j += blockDim.x) {
+    float s = 0.f, c = 1.f;
+    if (inv_freq) sincosf((float)pos * inv_freq[j], &s, &c);
+    trig[j] = c;
+    trig[half + j] = s;
+  }
+  const QT* row = in + (size_t)t * row_stride;
+  T* k_dst = nullptr;
+  T* v_dst = nullptr;
+  if (write_cache) {
+    const int seat = seq_seat[token_seq[t]];
+    const int column = pos / page_size;
+    const int page = (pos >= 0 && column < table_width) ? block_table[(size_t)seat * table_width + column] : -1;
+    if (page < 0 || page >= num_pages) {
+      if (threadIdx.x == 0 && error) atomicExch(error, 2);
+      write_cache = 0;
+    } else {
+      const size_t base = ((size_t)page * num_kv_heads * page_size + (pos % page_size)) * head_dim;
+      k_dst = k_cache + base;
+      v_dst = v_cache + base;
+    }
+  }
+  __syncthreads();
+  const size_t cache_head_stride = (size_t)page_size * head_dim;
+  const int pieces = half >> 3;  // pieces of 8 pairs per head
+  const int rot_units = (num_heads + (write_cache ? num_kv_heads : 0)) * pieces;
+  const int v_units = write_cache ? num_kv_heads * (head_dim >> 3) : 0;
+  // Eight elements of the input row at `offset`, summed over the splits, plus the bias.
+  auto gather8 = [&](int offset, float (&dst)[8]) {
+    load8(row + offset, dst);
+    for (int sp = 1; sp < splits; ++sp) {
+      float more[8];
+      load8(row + sp * split_stride + offset, more);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) dst[i] += more[i];
+    }
+    if (bias) {
+      float b[8];
+      load8(bias + offset, b);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) dst[i] += b[i];
+    }
+  };
+  for (int unit = threadIdx.x; unit < rot_units + v_units; unit += blockDim.x) {
+    if (unit < rot_units) {
+      const int head = unit / pieces, j0 = (unit % pieces) * 8;
+      float lo[8], hi[8], out_lo[8], out_hi[8];
+      gather8(head * head_dim + j0, lo);
+      gather8(head * head_dim + half + j0, hi);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float c = trig[j0 + i], s = trig[half + j0 + i];
+        out_lo[i] = lo[i] * c - hi[i] * s;
+        out_hi[i] = hi[i] * c + lo[i] * s;
+      }
+      T* dst = head < num_heads ? q_out + (size_t)t * q_out_stride + (size_t)head * head_dim
+                                : k_dst + (size_t)(head - num_heads) * cache_head_stride;
+      store8(dst + j0, out_lo);
+      store8(dst + half + j0, out_hi);
+    } else {
+      const int piece = unit - rot_units;
+      const int head = piece / (head_dim >> 3), j0 = (piece % (head_dim >> 3)) * 8;
+      float v[8];
+      gather8((num_heads + num_kv_heads + head) * head_dim + j0, v);
+      store8(v_dst + (size_t)head * cache_head_stride + j0, v);
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------
 // out[t, i] = silu(gate_up[t, i]) * gate_up[t, inter + i], computed in float32.
 // ---------------------------------------------------------------------------
@@ -214,15 +368,27 @@ extern "C" int distie_add_rmsnorm(const void* delta, float* residual, const floa
                                   cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (hidden < 1) return DISTIE_ERR_ARG;
+  if (dtype != DISTIE_BF16 && dtype != DISTIE_F32) return DISTIE_ERR_UNSUPPORTED;
+  const bool aligned = (((uintptr_t)delta | (uintptr_t)residual | (uintptr_t)weight | (uintptr_t)out) & 15) == 0;
+  if ((hidden & 3) == 0 && hidden <= 16 * 1024 && aligned) {
+    int threads = 128;
+    while (threads * 16 < hidden) threads *= 2;
+    if (dtype == DISTIE_BF16)
+      add_rmsnorm_vec_kernel<<<rows, threads, 0, stream>>>((const __nv_bfloat16*)delta, 1, (size_t)0, residual,
+                                                           weight, (__nv_bfloat16*)out, rows_index, hidden, eps);
+    else
+      add_rmsnorm_vec_kernel<<<rows, threads, 0, stream>>>((const float*)delta, 1, (size_t)0, residual, weight,
+                                                           (float*)out, rows_index, hidden, eps);
+    DISTIE_LAUNCH_CHECK();
+    return 0;
+  }
   const int threads = hidden >= 4096 ? 512 : (hidden >= 1024 ? 256 : 128);
   if (dtype == DISTIE_BF16)
     add_rmsnorm_kernel<<<rows, threads, 0, stream>>>((const __nv_bfloat16*)delta, residual, weight,
                                                      (__nv_bfloat16*)out, rows_index, hidden, eps);
-  else if (dtype == DISTIE_F32)
+  else
     add_rmsnorm_kernel<<<rows, threads, 0, stream>>>((const float*)delta, residual, weight, (float*)out,
                                                      rows_index, hidden, eps);
-  else
-    return DISTIE_ERR_UNSUPPORTED;
   DISTIE_LAUNCH_CHECK();
   return 0;
 }
@@ -236,6 +402,27 @@ extern "C" int distie_rope_kv_write(void* qkv, const int* positions, const int* 
   if (head_dim < 2 || (head_dim & 1) || rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1) ||
       num_heads < 1 || num_kv_heads < 1 || page_size < 1 || table_width < 1)
     return DISTIE_ERR_ARG;
+  if (dtype != DISTIE_BF16 && dtype != DISTIE_F32) return DISTIE_ERR_UNSUPPORTED;
+  const bool aligned = (((uintptr_t)qkv | (uintptr_t)k_cache | (uintptr_t)v_cache) & 31) == 0;
+  if ((inv_freq == nullptr || rotary_dim == head_dim) && !interleaved && (head_dim & 15) == 0 &&
+      (row_stride & 7) == 0 && aligned) {
+    const int units = (num_heads + num_kv_heads) * (head_dim >> 4) + num_kv_heads * (head_dim >> 3);
+    int threads = 64;
+    while (threads < units && threads < 256) threads *= 2;
+    const size_t bytes = (size_t)head_dim * sizeof(float);
+    if (dtype == DISTIE_BF16)
+      rope_kv_write_vec_kernel<<<tokens, threads, bytes, stream>>>(
+          (const __nv_bfloat16*)qkv, 1, (size_t)0, row_stride, (const float*)nullptr, (__nv_bfloat16*)qkv, row_stride,
+          positions, token_seq, seq_seat, block_table, table_width, inv_freq, (__nv_bfloat16*)k_cache,
+          (__nv_bfloat16*)v_cache, num_heads, num_kv_heads, head_dim, page_size, num_pages, write_cache, error);
+    else
+      rope_kv_write_vec_kernel<<<tokens, threads, bytes, stream>>>(
+          (const float*)qkv, 1, (size_t)0, row_stride, (const float*)nullptr, (float*)qkv, row_stride, positions,
+          token_seq, seq_seat, block_table, table_width, inv_freq, (float*)k_cache, (float*)v_cache, num_heads,
+          num_kv_heads, head_dim, page_size, num_pages, write_cache, error);
+    DISTIE_LAUNCH_CHECK();
+    return 0;
+  }
   const int threads = 128;
   const size_t shared = (size_t)rotary_dim * sizeof(float);
   if (dtype == DISTIE_BF16)
@@ -250,6 +437,64 @@ extern "C" int distie_rope_kv_write(void* qkv, const int* positions, const int* 
         write_cache, error);
   else
     return DISTIE_ERR_UNSUPPORTED;
+  DISTIE_LAUNCH_CHECK();
+  return 0;
+}
+
+// The same two kernels fed with the float32 partial sums of a product whose K was split
+// (`splits` slices of [rows, width], `split_stride` elements apart).  They exist only in the
+// vectorised form: other shapes return DISTIE_ERR_UNSUPPORTED and the caller adds the slices up itself.
+extern "C" int distie_add_rmsnorm_split(const float* partials, int splits, long long split_stride, float* residual,
+                                        const float* weight, void* out, const int* rows_index, int rows, int hidden,
+                                        float eps, int dtype, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (hidden < 1 || splits < 1 || partials == nullptr) return DISTIE_ERR_ARG;
+  if (dtype != DISTIE_BF16 && dtype != DISTIE_F32) return DISTIE_ERR_UNSUPPORTED;
+  const bool aligned = (((uintptr_t)partials | (uintptr_t)residual | (uintptr_t)weight | (uintptr_t)out) & 15) == 0;
+  if ((hidden & 3) || hidden > 16 * 1024 || !aligned || (split_stride & 3)) return DISTIE_ERR_UNSUPPORTED;
+  int threads = 128;
+  while (threads * 16 < hidden) threads *= 2;
+  if (dtype == DISTIE_BF16)
+    add_rmsnorm_vec_kernel<<<rows, threads, 0, stream>>>(partials, splits, (size_t)split_stride, residual, weight,
+                                                         (__nv_bfloat16*)out, rows_index, hidden, eps);
+  else
+    add_rmsnorm_vec_kernel<<<rows, threads, 0, stream>>>(partials, splits, (size_t)split_stride, residual, weight,
+                                                         (float*)out, rows_index, hidden, eps);
+  DISTIE_LAUNCH_CHECK();
+  return 0;
+}
+
+extern "C" int distie_rope_kv_write_split(const float* partials, int splits, long long split_stride, int row_stride,
+                                          const float* bias, void* q_out, int q_out_stride, const int* positions,
+                                          const int* token_seq, const int* seq_seat, const int* block_table,
+                                          int table_width, const float* inv_freq, void* k_cache, void* v_cache,
+                                          int tokens, int num_heads, int num_kv_heads, int head_dim, int rotary_dim,
+                                          int interleaved, int page_size, int num_pages, int write_cache, int dtype,
+                                          int* error, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (head_dim < 2 || num_heads < 1 || num_kv_heads < 1 || page_size < 1 || table_width < 1 || splits < 1 ||
+      partials == nullptr || q_out == nullptr)
+    return DISTIE_ERR_ARG;
+  if (dtype != DISTIE_BF16 && dtype != DISTIE_F32) return DISTIE_ERR_UNSUPPORTED;
+  const bool aligned =
+      (((uintptr_t)partials | (uintptr_t)q_out | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)bias) & 31) == 0;
+  if (!((inv_freq == nullptr || rotary_dim == head_dim) && !interleaved && (head_dim & 15) == 0 &&
+        (row_stride & 7) == 0 && (q_out_stride & 7) == 0 && (split_stride & 7) == 0 && aligned))
+    return DISTIE_ERR_UNSUPPORTED;
+  const int units = (num_heads + num_kv_heads) * (head_dim >> 4) + num_kv_heads * (head_dim >> 3);
+  int threads = 64;
+  while (threads < units && threads < 256) threads *= 2;
+  const size_t bytes = (size_t)head_dim * sizeof(float);
+  if (dtype == DISTIE_BF16)
+    rope_kv_write_vec_kernel<<<tokens, threads, bytes, stream>>>(
+        partials, splits, (size_t)split_stride, row_stride, bias, (__nv_bfloat16*)q_out, q_out_stride, positions,
+        token_seq, seq_seat, block_table, table_width, inv_freq, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache,
+        num_heads, num_kv_heads, head_dim, page_size, num_pages, write_cache, error);
+  else
+    rope_kv_write_vec_kernel<<<tokens, threads, bytes, stream>>>(
+        partials, splits, (size_t)split_stride, row_stride, bias, (float*)q_out, q_out_stride, positions, token_seq,
+        seq_seat, block_table, table_width, inv_freq, (float*)k_cache, (float*)v_cache, num_heads, num_kv_heads,
+        head_dim, page_size, num_pages, write_cache, error);
   DISTIE_LAUNCH_CHECK();
   return 0;
 }

@@ -58,6 +58,8 @@ class DeviceKernels(KernelSet):
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.error_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.launches = 0  # own kernels launched (library products are not counted)
+        # Counters and partial sums of products that split K over several CTAs; zero between launches.
+        self.split_workspace = torch.zeros(2 * 1024 * 1024, dtype=torch.float32, device=self.device)
 
     # -- helpers ------------------------------------------------------------
     @staticmethod
@@ -84,15 +86,41 @@ class DeviceKernels(KernelSet):
 
     def add_rmsnorm(self, delta, residual, weight, eps, out, rows_index=None) -> None:
         rows = out.shape[0]
+        rows_ptr = rows_index.data_ptr() if rows_index is not None else None
+        if delta is not None and delta.dim() == 3:
+            code = function("distie_add_rmsnorm_split")(
+                delta.data_ptr(), delta.shape[0], delta.stride(0), residual.data_ptr(), weight.data_ptr(),
+                out.data_ptr(), rows_ptr, rows, residual.shape[1], float(eps), self.code, self._stream(),
+            )
+            if code == 0:
+                self.launches += 1
+                return
+            if code != -2:
+                check(code, "add_rmsnorm_split")
+            delta = (delta[0] if delta.shape[0] == 1 else delta.sum(0)).to(self.dtype)  # a width the fused kernel refuses
         check(
             function("distie_add_rmsnorm")(
                 delta.data_ptr() if delta is not None else None, residual.data_ptr(), weight.data_ptr(),
-                out.data_ptr(), rows_index.data_ptr() if rows_index is not None else None, rows,
-                residual.shape[1], float(eps), self.code, self._stream(),
+                out.data_ptr(), rows_ptr, rows, residual.shape[1], float(eps), self.code, self._stream(),
             ),
             "add_rmsnorm",
         )
         self.launches += 1
+
+    def linear_split(self, x, weight):
+        if self._skinny(x, weight):
+            m, n, k = x.shape[0], weight.shape[0], weight.shape[1]
+            splits = function("distie_linear_skinny_splits")(m, n, k, self.sm_count)
+            out = torch.empty((splits, m, n), dtype=torch.float32, device=x.device)
+            check(
+                function("distie_linear_skinny_partial")(
+                    x.data_ptr(), x.stride(0), weight.data_ptr(), out.data_ptr(), m, n, k, self.sm_count, self._stream()
+                ),
+                "linear_skinny_partial",
+            )
+            self.launches += 1
+            return out
+        return super().linear_split(x, weight)
 
     def linear(self, x, weight, bias=None, out_dtype=None):
         out_dtype = out_dtype or self.dtype
@@ -123,7 +151,7 @@ class DeviceKernels(KernelSet):
             function("distie_linear_skinny")(
                 x.data_ptr(), x.stride(0), weight.data_ptr(), bias.data_ptr() if bias is not None else None,
                 out.data_ptr(), out.stride(0), x.shape[0], weight.shape[0], weight.shape[1], _CODE[out.dtype],
-                swiglu, self._stream(),
+                swiglu, self.split_workspace.data_ptr(), self.split_workspace.numel(), self.sm_count, self._stream(),
             ),
             "linear_skinny",
         )
@@ -157,24 +185,50 @@ class DeviceKernels(KernelSet):
         )
         self.launches += 1
 
-    def rope_kv_write(self, qkv, step, kv, rotary, num_heads, num_kv_heads, head_dim) -> None:
+    def rope_kv_write(self, qkv, step, kv, rotary, num_heads, num_kv_heads, head_dim, bias=None, q_out=None) -> None:
         write = kv is not None
         table = kv.block_table if write else step.seq_seat  # any valid pointer when nothing is written
+        tail = [
+            step.positions.data_ptr(), step.token_seq.data_ptr(), step.seq_seat.data_ptr(),
+            table.data_ptr(), table.shape[-1] if write else 1,
+            rotary.inv_freq.data_ptr() if rotary is not None else None,
+            kv.k.data_ptr() if write else None, kv.v.data_ptr() if write else None,
+        ]
+        sizes = [
+            num_heads, num_kv_heads, head_dim,
+            rotary.rotary_dim if rotary is not None else 0,
+            int(rotary.interleaved) if rotary is not None else 0,
+            kv.page_size if write else 1, kv.num_pages if write else 1, int(write), self.code,
+            self.error_flag.data_ptr(), self._stream(),
+        ]
+        if qkv.dim() == 3:
+            if q_out is None:
+                raise KernelError("rope_kv_write: slices of a projection need a q_out buffer")
+            code = function("distie_rope_kv_write_split")(
+                qkv.data_ptr(), qkv.shape[0], qkv.stride(0), qkv.stride(1),
+                bias.data_ptr() if bias is not None else None, q_out.data_ptr(), q_out.stride(0),
+                *tail, step.num_tokens, *sizes,
+            )
+            if code == 0:
+                self.launches += 1
+                return
+            if code != -2:
+                check(code, "rope_kv_write_split")
+            # Sizes the fused kernel refuses: finish the projection here, rotate in place, copy q out.
+            summed = qkv[0] if qkv.shape[0] == 1 else qkv.sum(0)
+            if bias is not None:
+                summed = summed + bias
+            dense = summed.to(self.dtype)
+            self.rope_kv_write(dense, step, kv, rotary, num_heads, num_kv_heads, head_dim)
+            q_out.copy_(dense[:, : num_heads * head_dim])
+            return
         check(
-            function("distie_rope_kv_write")(
-                qkv.data_ptr(), step.positions.data_ptr(), step.token_seq.data_ptr(), step.seq_seat.data_ptr(),
-                table.data_ptr(), table.shape[-1] if write else 1,
-                rotary.inv_freq.data_ptr() if rotary is not None else None,
-                kv.k.data_ptr() if write else None, kv.v.data_ptr() if write else None,
-                step.num_tokens, qkv.stride(0), num_heads, num_kv_heads, head_dim,
-                rotary.rotary_dim if rotary is not None else 0,
-                int(rotary.interleaved) if rotary is not None else 0,
-                kv.page_size if write else 1, kv.num_pages if write else 1, int(write), self.code,
-                self.error_flag.data_ptr(), self._stream(),
-            ),
+            function("distie_rope_kv_write")(qkv.data_ptr(), *tail, step.num_tokens, qkv.stride(0), *sizes),
             "rope_kv_write",
         )
         self.launches += 1
+        if q_out is not None:
+            q_out.copy_(qkv[:, : num_heads * head_dim])
 
     def plan_splits(self, tokens: int, num_heads: int, num_kv_heads: int, max_kv_len: int) -> int:
         group = num_heads // num_kv_heads
@@ -194,17 +248,23 @@ class DeviceKernels(KernelSet):
             if splits > 1:
                 floats = function("distie_attention_decode_scratch_floats")(n_dec, num_heads, head_dim, splits)
                 scratch = torch.empty(floats, dtype=torch.float32, device=qkv.device)
-            check(
-                function("distie_attention_decode")(
-                    qkv.data_ptr(), qkv.stride(0), out.data_ptr(), out.stride(0),
-                    scratch.data_ptr() if scratch is not None else None, step.positions.data_ptr(),
-                    step.token_seq.data_ptr(), step.seq_seat.data_ptr(), kv.block_table.data_ptr(),
-                    kv.block_table.shape[-1], kv.k.data_ptr(), kv.v.data_ptr(), n_dec, num_heads, num_kv_heads,
-                    head_dim, kv.page_size, kv.num_pages, window, float(scale), splits, self.code,
-                    self.error_flag.data_ptr(), self._stream(),
-                ),
-                "attention_decode",
-            )
+            head = [
+                qkv.data_ptr(), qkv.stride(0), out.data_ptr(), out.stride(0),
+                scratch.data_ptr() if scratch is not None else None, step.positions.data_ptr(),
+                step.token_seq.data_ptr(), step.seq_seat.data_ptr(), kv.block_table.data_ptr(),
+                kv.block_table.shape[-1], kv.k.data_ptr(), kv.v.data_ptr(), n_dec, num_heads, num_kv_heads,
+                head_dim, kv.page_size, kv.num_pages, window, float(scale), splits,
+            ]
+            if self.dtype == torch.bfloat16 and head_dim in _PREFILL_HEAD_DIMS:
+                check(
+                    function("distie_attention_decode_mma")(*head, self.error_flag.data_ptr(), self._stream()),
+                    "attention_decode_mma",
+                )
+            else:
+                check(
+                    function("distie_attention_decode")(*head, self.code, self.error_flag.data_ptr(), self._stream()),
+                    "attention_decode",
+                )
             self.launches += 1 if splits == 1 else 2
         rest = step.num_tokens - n_dec
         if rest > 0 and self.dtype == torch.bfloat16 and head_dim in _PREFILL_HEAD_DIMS and step.num_q_tiles and n_dec == step.num_decode_tokens:

@@ -69,11 +69,25 @@ class KernelSet(ABC):
 
     @abstractmethod
     def add_rmsnorm(self, delta, residual, weight, eps: float, out, rows_index=None) -> None:
-        """residual += delta (float32, kept), out = weight * cast(residual * rsqrt(mean sq + eps))."""
+        """residual += delta (float32, kept), out = weight * cast(residual * rsqrt(mean sq + eps)).
+
+        ``delta`` is ``[T, hidden]`` in the set's dtype, or ``[S, T, hidden]`` float32 slices as
+        :meth:`linear_split` returns them, which are added up in the same kernel.
+        """
 
     @abstractmethod
     def linear(self, x, weight, bias=None, out_dtype=None):
         """x @ weight.T (+ bias); weight is [out, in]."""
+
+    def linear_split(self, x, weight):
+        """``x @ weight.T`` as float32 slices ``[S, T, out]`` whose sum over ``S`` is the product.
+
+        A set that splits the reduction of a skinny product over several thread blocks returns
+        the slices as they are and leaves the sum to the consumer (``add_rmsnorm``,
+        ``rope_kv_write``), which saves the product a round of synchronisation.  The default is
+        one slice.
+        """
+        return self.linear(x, weight, None, torch.float32).unsqueeze(0)
 
     @abstractmethod
     def swiglu(self, gate_up, out) -> None:
@@ -88,8 +102,14 @@ class KernelSet(ABC):
 
     @abstractmethod
     def rope_kv_write(self, qkv, step: StepTensors, kv: KvSlot | None, rotary: RotaryTable | None,
-                      num_heads: int, num_kv_heads: int, head_dim: int) -> None:
-        """Rotate q (in place) and k, store k and v of the new tokens in their pages (if kv)."""
+                      num_heads: int, num_kv_heads: int, head_dim: int, bias=None, q_out=None) -> None:
+        """Rotate q and k, store k and v of the new tokens in their pages (if kv).
+
+        ``qkv`` is ``[T, (heads + 2 kv_heads) * head_dim]`` in the set's dtype with q rotated in
+        place, or float32 slices ``[S, T, ...]`` of the projection (see :meth:`linear_split`), in
+        which case the slices are summed, ``bias`` is added and the rotated q is written to
+        ``q_out [T, heads * head_dim]``.
+        """
 
     @abstractmethod
     def attention(self, qkv, out, step: StepTensors, kv: KvSlot, num_heads: int, num_kv_heads: int,

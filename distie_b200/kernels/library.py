@@ -24,6 +24,10 @@ _SIGNATURES: dict[str, tuple[str, list]] = {
     "distie_add_rmsnorm": ("base", [P, P, P, P, P, I, I, F, I, P]),
     "distie_rope_kv_write": ("base", [P, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, I, I, I, P, P]),
     "distie_swiglu": ("base", [P, P, I, I, I, P]),
+    "distie_add_rmsnorm_split": ("base", [P, I, L, P, P, P, P, I, I, F, I, P]),
+    "distie_rope_kv_write_split": (
+        "base", [P, I, L, I, P, P, I, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, I, I, P, P]
+    ),
     "distie_bias_cast": ("base", [P, P, P, L, I, I, P]),
     "distie_attention_generic": ("base", [P, I, P, I, P, P, P, P, I, P, P, I, I, I, I, I, I, I, F, I, P, P]),
     "distie_attention_decode": ("base", [P, I, P, I, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, F, I, I, P, P]),
@@ -31,8 +35,11 @@ _SIGNATURES: dict[str, tuple[str, list]] = {
     "distie_sample": ("base", [P, L, I, I, P, P, P, P]),
     "distie_attention_prefill": ("bf16", [P, I, P, I, P, I, P, P, P, P, I, P, P, I, I, I, I, I, I, F, P, P]),
     "distie_attention_prefill_tile": ("bf16", []),
-    "distie_linear_skinny": ("bf16", [P, I, P, P, P, I, I, I, I, I, I, P]),
+    "distie_attention_decode_mma": ("bf16", [P, I, P, I, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, F, I, P, P]),
+    "distie_linear_skinny": ("bf16", [P, I, P, P, P, I, I, I, I, I, I, P, L, I, P]),
     "distie_linear_skinny_max_rows": ("bf16", []),
+    "distie_linear_skinny_splits": ("bf16", [I, I, I, I]),
+    "distie_linear_skinny_partial": ("bf16", [P, I, P, P, I, I, I, I, P]),
 }
 _RESULT = {"distie_attention_decode_scratch_floats": c_longlong}
 

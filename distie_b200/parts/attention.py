@@ -102,18 +102,24 @@ class GqaAttention:
     def forward(self, x: torch.Tensor, run: LayerRun) -> torch.Tensor:
         if run.kv is None:
             raise RuntimeError("attention needs a cache slot")
-        qkv = self.qkv(x)
-        self.kernels.rope_kv_write(
-            qkv,
+        k = self.kernels
+        # The projection's float32 slices go straight into the kernel that adds the bias, rotates q
+        # and k and stores k and v in their pages; q comes back in a buffer of its own.
+        slices = k.linear_split(x, self.qkv.weight)
+        q = torch.empty((x.shape[0], self.num_heads * self.head_dim), dtype=x.dtype, device=x.device)
+        k.rope_kv_write(
+            slices,
             run.step,
             run.kv if run.writes_cache else None,
             self.position.rotary_table(),
             self.num_heads,
             self.num_kv_heads,
             self.head_dim,
+            bias=self.qkv.bias,
+            q_out=q,
         )
-        mixed = torch.empty((x.shape[0], self.num_heads * self.head_dim), dtype=x.dtype, device=x.device)
-        self.kernels.attention(
-            qkv, mixed, run.step, run.kv, self.num_heads, self.num_kv_heads, self.head_dim, self.window, self.scale
-        )
-        return self.out(mixed)
+        mixed = torch.empty_like(q)
+        k.attention(q, mixed, run.step, run.kv, self.num_heads, self.num_kv_heads, self.head_dim, self.window, self.scale)
+        if self.out.bias is not None:
+            return self.out(mixed)
+        return k.linear_split(mixed, self.out.weight)  # summed by the norm that follows

@@ -18,7 +18,8 @@ block          ``tensor_specs``, ``build``, ``forward(stream, run)``
 
 ``forward`` of a mixer or feed-forward takes the normalised activations ``[T,
 hidden]`` of the step's tokens and returns what is to be added to the residual
-stream.  The :class:`LayerRun` tells a mixer everything about the step: the
+stream: ``[T, hidden]``, or float32 slices ``[S, T, hidden]`` whose sum it is (what
+``KernelSet.linear_split`` returns; the norm that follows adds them up).  The :class:`LayerRun` tells a mixer everything about the step: the
 tokens' positions and requests, its cache slot and its per-request state.
 """
 
@@ -118,7 +119,8 @@ class ResidualStream:
 
     def settle(self) -> torch.Tensor:
         if self.pending is not None:
-            self.residual.add_(self.pending.to(torch.float32))
+            delta = self.pending.sum(0) if self.pending.dim() == 3 else self.pending  # slices of a split product
+            self.residual.add_(delta.to(torch.float32))
             self.pending = None
         return self.residual
 

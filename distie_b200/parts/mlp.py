@@ -44,4 +44,5 @@ class SwiGluFeedForward:
         )
 
     def forward(self, x: torch.Tensor, run: LayerRun) -> torch.Tensor:
-        return self.down(self.kernels.linear_swiglu(x, self.gate_up.weight))
+        # The down product's float32 slices are summed by the norm that follows (or by the stream).
+        return self.kernels.linear_split(self.kernels.linear_swiglu(x, self.gate_up.weight), self.down.weight)

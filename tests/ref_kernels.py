@@ -20,6 +20,8 @@ def embed(ids, table):
 
 def add_rmsnorm(delta, residual, weight, eps, dtype, rows_index=None):
     """Returns (new residual, normed).  With rows_index only those rows are normed and the residual is unchanged."""
+    if delta is not None and delta.dim() == 3:  # float32 slices of a split product
+        delta = delta.float().sum(0)
     summed = residual if delta is None else residual + delta.float()
     source = summed if rows_index is None else summed[rows_index.long()]
     variance = (source * source).mean(dim=-1, keepdim=True)
@@ -54,7 +56,16 @@ def rotate(x, positions, rotary: RotaryTable | None):
     return out.to(x.dtype)
 
 
-def rope_kv_write(qkv, step: StepTensors, kv: KvSlot | None, rotary, num_heads, num_kv_heads, head_dim):
+def rope_kv_write(qkv, step: StepTensors, kv: KvSlot | None, rotary, num_heads, num_kv_heads, head_dim,
+                  bias=None, q_out=None):
+    if qkv.dim() == 3:  # float32 slices of the projection: sum, add the bias, then as below on a copy
+        dense = qkv.float().sum(0)
+        if bias is not None:
+            dense = dense + bias.float()
+        dense = dense.to(q_out.dtype)
+        rope_kv_write(dense, step, kv, rotary, num_heads, num_kv_heads, head_dim)
+        q_out.copy_(dense[:, : num_heads * head_dim])
+        return
     tokens = step.num_tokens
     q_end, k_end = num_heads * head_dim, (num_heads + num_kv_heads) * head_dim
     positions = step.positions[:tokens]
@@ -136,8 +147,8 @@ class RefKernels(KernelSet):
     def swiglu(self, gate_up, out):
         out.copy_(swiglu(gate_up))
 
-    def rope_kv_write(self, qkv, step, kv, rotary, num_heads, num_kv_heads, head_dim):
-        rope_kv_write(qkv, step, kv, rotary, num_heads, num_kv_heads, head_dim)
+    def rope_kv_write(self, qkv, step, kv, rotary, num_heads, num_kv_heads, head_dim, bias=None, q_out=None):
+        rope_kv_write(qkv, step, kv, rotary, num_heads, num_kv_heads, head_dim, bias, q_out)
 
     def attention(self, qkv, out, step, kv, num_heads, num_kv_heads, head_dim, window, scale):
         out.copy_(attention(qkv, step, kv, num_heads, num_kv_heads, head_dim, window, scale))

@@ -126,7 +126,8 @@ def test_feed_forward_part_alone(dtype, tol):
     w = {k: v.to(torch.bfloat16).float() for k, v in w.items()}
     part = build_part(FEED_FORWARDS, PartSpec("swiglu", {"intermediate_size": inter}, "ff."), part_context(dtype, w, hidden))
     x = torch.randn(9, hidden).to(torch.bfloat16).float()
-    got = part.forward(x.cuda().to(dtype), None).float().cpu()
+    got = part.forward(x.cuda().to(dtype), None).float()
+    got = (got.sum(0) if got.dim() == 3 else got).cpu()  # slices of a split product add up to the result
     want = plain.swiglu_mlp(x, {k.replace("ff.", "p."): v for k, v in w.items()}, "p.")
     assert float((got - want).abs().max()) <= tol * float(want.abs().max())
 
@@ -180,7 +181,8 @@ def test_attention_part_alone(dtype, tol, window):
         cache.upload_tables([seat])
         step, _ = staging.upload(layout)
         run = LayerRun(step=step, seqs=layout.seqs, kv=cache.kv_slot(0), writes_cache=True)
-        outs.append(part.forward(x[done : done + count].cuda().to(dtype), run).float().cpu())
+        delta = part.forward(x[done : done + count].cuda().to(dtype), run).float()
+        outs.append((delta.sum(0) if delta.dim() == 3 else delta).cpu())
         done += count
         cache.trim(seat, done)
     ctx.kernels.check_errors()

@@ -108,6 +108,39 @@ def test_add_rmsnorm(kernel_sets, dtype, rows, hidden, eps):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows,hidden,splits", [(8, 1536, 4), (3, 96, 1), (5, 50, 3), (2, 8200, 2)])
+def test_add_rmsnorm_sums_slices_of_a_split_product(kernel_sets, dtype, rows, hidden, splits):
+    ks = kernel_sets[dtype]
+    residual = torch.randn(rows, hidden, device="cuda") * 3
+    slices = torch.randn(splits, rows, hidden, device="cuda")
+    weight = 1 + 0.1 * torch.randn(hidden, device="cuda")
+    res = residual.clone()
+    out = torch.empty(rows, hidden, dtype=dtype, device="cuda")
+    ks.add_rmsnorm(slices, res, weight, 1e-6, out)
+    want_res, want = ref.add_rmsnorm(slices, residual, weight, 1e-6, dtype)
+    assert torch.allclose(res, want_res, atol=1e-5, rtol=1e-5)
+    close(out, want, dtype, "rmsnorm of slices")
+    rows_index = torch.tensor([rows - 1, 0], dtype=torch.int32, device="cuda")
+    out2 = torch.empty(2, hidden, dtype=dtype, device="cuda")
+    res2 = residual.clone()
+    ks.add_rmsnorm(slices, res2, weight, 1e-6, out2, rows_index)
+    assert torch.equal(res2, residual)
+    close(out2, ref.add_rmsnorm(slices, residual, weight, 1e-6, dtype, rows_index)[1], dtype, "rmsnorm of slices, rows")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("m,k,n", [(8, 1536, 2048), (1, 8960, 1536), (16, 200, 57), (5, 96, 40), (30, 96, 40)])
+def test_linear_split_slices_add_up(kernel_sets, dtype, m, k, n):
+    ks = kernel_sets[dtype]
+    x = torch.randn(m, k, device="cuda").to(dtype)
+    w = (torch.randn(n, k, device="cuda") * 0.1).to(dtype)
+    slices = ks.linear_split(x, w)
+    assert slices.dim() == 3 and slices.dtype == torch.float32 and slices.shape[1:] == (m, n)
+    want = torch.nn.functional.linear(x.double(), w.double())
+    close(slices.sum(0), want, torch.float32 if dtype == torch.float32 else dtype, "sum of slices")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("tokens,inter", [(3, 224), (70, 8960), (1, 17)])
 def test_swiglu(kernel_sets, dtype, tokens, inter):
     ks = kernel_sets[dtype]
@@ -175,6 +208,19 @@ def test_rope_kv_write(kernel_sets, dtype, heads, kv_heads, head_dim, rotary_dim
     close(kv.k, kv_ref.k, dtype, "cached keys")
     assert torch.equal(kv.v, kv_ref.v), "values are copied bit for bit"
     assert float(kv.k.float().abs().sum()) > 0
+    # The same from float32 slices of the projection plus a bias, q into its own buffer.
+    slices = torch.randn(3, step.num_tokens, qkv.shape[1], device="cuda")
+    bias = torch.randn(qkv.shape[1], device="cuda")
+    kv_a = make_cache(dtype, 64, kv_heads, page, head_dim, 4, width, fill=False)
+    kv_b = make_cache(dtype, 64, kv_heads, page, head_dim, 4, width, fill=False)
+    q_a = torch.zeros(step.num_tokens, heads * head_dim, dtype=dtype, device="cuda")
+    q_b = torch.zeros_like(q_a)
+    ks.rope_kv_write(slices, step, kv_a, rotary, heads, kv_heads, head_dim, bias=bias, q_out=q_a)
+    ref.rope_kv_write(slices, step, kv_b, rotary, heads, kv_heads, head_dim, bias=bias, q_out=q_b)
+    ks.check_errors()
+    close(q_a, q_b, dtype, "rotated q from slices")
+    close(kv_a.k, kv_b.k, dtype, "cached keys from slices")
+    close(kv_a.v, kv_b.v, dtype, "cached values from slices")
     # Nothing is written when the call only reads the cache; no rotation without a table.
     kv_none = make_cache(dtype, 64, kv_heads, page, head_dim, 4, width, fill=False)
     again = qkv.clone()
