@@ -58,7 +58,7 @@ __device__ __forceinline__ uint32_t tile_offset(int row, int chunk) {
 }
 
 template <int D>
-__global__ void __launch_bounds__(kPrefillWarps * 32)
+__global__ void __launch_bounds__(kPrefillWarps * 32, 3)
 attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, __nv_bfloat16* __restrict__ out,
                          int out_row_stride, const int* __restrict__ q_tiles, const int* __restrict__ positions,
                          const int* __restrict__ token_seq, const int* __restrict__ seq_seat,
@@ -70,11 +70,13 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, 
   constexpr int TILE_BYTES = kTileN * D * 2;
   constexpr int ROWS_PER_PASS = kPrefillWarps * 32 / CHUNKS;
   extern __shared__ __align__(128) unsigned char smem[];
-  unsigned char* q_s = smem;
-  unsigned char* k_s = smem + TILE_BYTES;             // two stages
-  unsigned char* v_s = smem + 3 * TILE_BYTES;         // two stages
+  unsigned char* k_s = smem;                          // two stages
+  unsigned char* v_s = smem + 2 * TILE_BYTES;         // two stages
+  unsigned char* q_s = v_s + TILE_BYTES;              // the query tile borrows stage 1 of V: it is read into
+                                                      // registers before the first load into that stage
 
-  const int tile = blockIdx.x, head = blockIdx.y;
+  // Tiles late in a request see the most keys and take longest: start them first.
+  const int tile = gridDim.x - 1 - blockIdx.x, head = blockIdx.y;
   const int kv_head = head / group_size;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, c = lane & 3;
@@ -134,20 +136,21 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, 
   float row_max[2] = {-INFINITY, -INFINITY}, row_sum[2] = {0.f, 0.f};
   const int pos_row[2] = {p0 + warp * 16 + g, p0 + warp * 16 + g + 8};
 
+  cp_async_wait<0>();
+  __syncthreads();
+#pragma unroll
+  for (int ks = 0; ks < D / 16; ++ks) {
+    const int row = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+    ldmatrix_x4(qf[ks], smem_addr(q_s + tile_offset<D>(row, 2 * ks + (lane >> 4))));
+  }
+  __syncthreads();  // every warp has its query fragments: stage 1 of V may be overwritten
+
   for (int block = 0; block < num_blocks; ++block) {
     const int stage = block & 1;
     if (block + 1 < num_blocks) load_kv(block + 1, stage ^ 1);
     cp_async_commit();
     cp_async_wait<1>();
     __syncthreads();
-
-    if (block == 0) {
-#pragma unroll
-      for (int ks = 0; ks < D / 16; ++ks) {
-        const int row = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
-        ldmatrix_x4(qf[ks], smem_addr(q_s + tile_offset<D>(row, 2 * ks + (lane >> 4))));
-      }
-    }
 
     // ---- S = Q K^T ------------------------------------------------------------------------
     float s[kTileN / 8][4];
@@ -254,7 +257,7 @@ int launch_prefill(const void* q, int q_row_stride, void* out, int out_row_strid
                    const int* positions, const int* token_seq, const int* seq_seat, const int* block_table,
                    int table_width, const void* k_cache, const void* v_cache, int num_heads, int num_kv_heads,
                    int page_size, int num_pages, int window, float scale, int* error, cudaStream_t stream) {
-  const int shared = 5 * kTileN * D * 2;
+  const int shared = 4 * kTileN * D * 2;
   static bool configured = false;
   if (!configured) {
     cudaError_t err = cudaFuncSetAttribute(attention_prefill_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, shared);

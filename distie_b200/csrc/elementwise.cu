@@ -70,13 +70,13 @@ __global__ void add_rmsnorm_kernel(const T* __restrict__ delta, float* __restric
   }
 }
 
-// The same for rows whose width is a multiple of 4 and at most 16 * blockDim.x: every thread
+// The same for rows whose width is a multiple of 4 and at most 16 * blockDim.x (blocks of up to 512): every thread
 // loads all its elements before it computes anything (one round trip to memory instead of one
 // per loop iteration) and keeps the summed residual in registers for the second pass.
 // `delta` may also be the float32 partial sums of a product whose K was split over several CTAs:
 // `splits` slices, `split_stride` elements apart, which are added up here in a fixed order.
 template <typename T, typename DT>
-__global__ void add_rmsnorm_vec_kernel(const DT* __restrict__ delta, int splits, size_t split_stride,
+__global__ void __launch_bounds__(512) add_rmsnorm_vec_kernel(const DT* __restrict__ delta, int splits, size_t split_stride,
                                        float* __restrict__ residual, const float* __restrict__ weight,
                                        T* __restrict__ out, const int* __restrict__ rows_index, int hidden,
                                        float eps) {
@@ -100,17 +100,23 @@ __global__ void add_rmsnorm_vec_kernel(const DT* __restrict__ delta, int splits,
     }
   }
   if (del) {
-    for (int sp = 0; sp < splits; ++sp) {
-      float4 d[VPT];
+    // Four slices per round, all their loads issued before any sum: one round trip for up to four.
+    for (int sp0 = 0; sp0 < splits; sp0 += 4) {
+      float4 d[4][VPT];
 #pragma unroll
-      for (int i = 0; i < VPT; ++i) {
-        const int ch = threadIdx.x + i * blockDim.x;
-        d[i] = ch < chunks ? load4(del + sp * split_stride + 4 * ch) : make_float4(0.f, 0.f, 0.f, 0.f);
-      }
+      for (int u = 0; u < 4; ++u)
 #pragma unroll
-      for (int i = 0; i < VPT; ++i) {
-        v[i].x += d[i].x; v[i].y += d[i].y; v[i].z += d[i].z; v[i].w += d[i].w;
-      }
+        for (int i = 0; i < VPT; ++i) {
+          const int ch = threadIdx.x + i * blockDim.x;
+          d[u][i] = (sp0 + u < splits && ch < chunks) ? load4(del + (sp0 + u) * split_stride + 4 * ch)
+                                                      : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+      for (int u = 0; u < 4; ++u)  // fixed order: slice 0 first
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+          v[i].x += d[u][i].x; v[i].y += d[u][i].y; v[i].z += d[u][i].z; v[i].w += d[u][i].w;
+        }
     }
   }
   float sumsq = 0.f;
@@ -276,19 +282,29 @@ __global__ void rope_kv_write_vec_kernel(const QT* in, int splits, size_t split_
   const int v_units = write_cache ? num_kv_heads * (head_dim >> 3) : 0;
   // Eight elements of the input row at `offset`, summed over the splits, plus the bias.
   auto gather8 = [&](int offset, float (&dst)[8]) {
+    float b[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) b[i] = 0.f;
+    if (bias) load8(bias + offset, b);
     load8(row + offset, dst);
-    for (int sp = 1; sp < splits; ++sp) {
-      float more[8];
-      load8(row + sp * split_stride + offset, more);
+    for (int sp0 = 1; sp0 < splits; sp0 += 3) {  // up to three more slices per round, loads first
+      float more[3][8];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) dst[i] += more[i];
-    }
-    if (bias) {
-      float b[8];
-      load8(bias + offset, b);
+      for (int u = 0; u < 3; ++u) {
+        if (sp0 + u < splits) {
+          load8(row + (sp0 + u) * split_stride + offset, more[u]);
+        } else {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) dst[i] += b[i];
+          for (int i = 0; i < 8; ++i) more[u][i] = 0.f;
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 3; ++u)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) dst[i] += more[u][i];
     }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) dst[i] += b[i];
   };
   for (int unit = threadIdx.x; unit < rot_units + v_units; unit += blockDim.x) {
     if (unit < rot_units) {
@@ -331,6 +347,20 @@ __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out
   }
 }
 
+// The same in pieces of 8 elements (inter a multiple of 8): blockIdx.y is the row, so no division per element.
+template <typename T>
+__global__ void swiglu_vec_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter) {
+  const size_t t = blockIdx.y;
+  const int i = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (i >= inter) return;
+  float g[8], u[8], y[8];
+  load8(gate_up + t * 2 * inter + i, g);
+  load8(gate_up + t * 2 * inter + inter + i, u);
+#pragma unroll
+  for (int e = 0; e < 8; ++e) y[e] = g[e] / (1.f + expf(-g[e])) * u[e];
+  store8(out + t * inter + i, y);
+}
+
 // out (T) [rows, cols] = cast(in (float32) + bias[col]): the epilogue of a product whose
 // float32 result gets its bias added before the one rounding to T.
 template <typename T>
@@ -370,7 +400,7 @@ extern "C" int distie_add_rmsnorm(const void* delta, float* residual, const floa
   if (hidden < 1) return DISTIE_ERR_ARG;
   if (dtype != DISTIE_BF16 && dtype != DISTIE_F32) return DISTIE_ERR_UNSUPPORTED;
   const bool aligned = (((uintptr_t)delta | (uintptr_t)residual | (uintptr_t)weight | (uintptr_t)out) & 15) == 0;
-  if ((hidden & 3) == 0 && hidden <= 16 * 1024 && aligned) {
+  if ((hidden & 3) == 0 && hidden <= 16 * 512 && aligned) {
     int threads = 128;
     while (threads * 16 < hidden) threads *= 2;
     if (dtype == DISTIE_BF16)
@@ -451,7 +481,7 @@ extern "C" int distie_add_rmsnorm_split(const float* partials, int splits, long 
   if (hidden < 1 || splits < 1 || partials == nullptr) return DISTIE_ERR_ARG;
   if (dtype != DISTIE_BF16 && dtype != DISTIE_F32) return DISTIE_ERR_UNSUPPORTED;
   const bool aligned = (((uintptr_t)partials | (uintptr_t)residual | (uintptr_t)weight | (uintptr_t)out) & 15) == 0;
-  if ((hidden & 3) || hidden > 16 * 1024 || !aligned || (split_stride & 3)) return DISTIE_ERR_UNSUPPORTED;
+  if ((hidden & 3) || hidden > 16 * 512 || !aligned || (split_stride & 3)) return DISTIE_ERR_UNSUPPORTED;
   int threads = 128;
   while (threads * 16 < hidden) threads *= 2;
   if (dtype == DISTIE_BF16)
@@ -504,6 +534,16 @@ extern "C" int distie_swiglu(const void* gate_up, void* out, int tokens, int int
   if (inter < 1) return DISTIE_ERR_ARG;
   const size_t total = (size_t)tokens * inter;
   const int threads = 256;
+  if ((inter & 7) == 0 && tokens <= 65535 && (((uintptr_t)gate_up | (uintptr_t)out) & 31) == 0 &&
+      (dtype == DISTIE_BF16 || dtype == DISTIE_F32)) {
+    const dim3 grid((inter / 8 + 127) / 128, tokens);
+    if (dtype == DISTIE_BF16)
+      swiglu_vec_kernel<<<grid, 128, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter);
+    else
+      swiglu_vec_kernel<<<grid, 128, 0, stream>>>((const float*)gate_up, (float*)out, inter);
+    DISTIE_LAUNCH_CHECK();
+    return 0;
+  }
   const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
   if (dtype == DISTIE_BF16)
     swiglu_kernel<<<blocks, threads, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, total);

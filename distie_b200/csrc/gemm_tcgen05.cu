@@ -1,0 +1,375 @@
+// Products of many rows (prompt portions) on the 5th-generation tensor cores:
+//   C[M, N] = A[M, K] (bfloat16 activations) x W[N, K]^T (bfloat16 weights), float32 accumulation.
+//
+// One CTA computes one 128 x BN tile of C.  Operands are staged in shared memory by
+// TMA (cp.async.bulk.tensor, 128-byte swizzle, K-major boxes of 64 elements) through a
+// ring of stages; one elected thread issues tcgen05.mma (M = 128, N = BN, K = 16 per
+// instruction) with the accumulator in tensor memory; four warps read the accumulator
+// back with tcgen05.ld and run the epilogue in registers.
+//
+//   warp 0      producer: waits for a free stage, arms its mbarrier with the byte count, issues the TMA loads
+//   warp 1      allocates tensor memory; one lane issues the MMAs of each stage as its barrier completes and
+//               commits them to the stage's "empty" barrier, at the end to the "accumulator ready" barrier
+//   warps 2..5  epilogue: warp w reads TMEM lanes 32 * (w % 4) .. + 31 (its rows of the tile), 32 columns at a
+//               time, and writes bfloat16, float32, or silu(gate) * up
+//
+// With the SwiGLU epilogue the weight is [2 * inter, K] (gate rows, then up rows) and a tile holds 128
+// gate rows and the 128 matching up rows (two TMA loads per stage), so gate and up of one output
+// element meet in the same thread.
+//
+// Rows and columns past the matrices are zero-filled by TMA and masked at the store; K needs to be a
+// multiple of 8 only.  Every wait on an mbarrier is bounded: when a wait runs out, the kernel sets
+// the error word to 6, stops issuing work, waits (bounded) for the copies it has in flight, releases
+// its tensor memory and returns.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace distie {
+
+constexpr int kGemmBM = 128;
+constexpr int kGemmBK = 64;
+constexpr int kGemmThreads = 192;
+constexpr uint32_t kSpinLimit = 1u << 26;
+
+constexpr int GEMM_EPI_BF16 = 0;
+constexpr int GEMM_EPI_F32 = 1;
+constexpr int GEMM_EPI_SWIGLU = 2;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// Bounded wait for the phase with the given parity; false when the limit ran out.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  const uint32_t addr = smem_u32(bar);
+  for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 bfloat16) with the
+// 128-byte swizzle: start address, leading byte offset 1 (unused for swizzled K-major), stride byte
+// offset 1024 (8 rows of 128 bytes), descriptor version 1, layout type 2 (SWIZZLE_128B).
+__device__ __forceinline__ uint64_t smem_desc(const void* tile) {
+  uint64_t desc = 0;
+  desc |= (uint64_t)((smem_u32(tile) & 0x3FFFF) >> 4);
+  desc |= (uint64_t)1 << 16;
+  desc |= (uint64_t)(1024 >> 4) << 32;
+  desc |= (uint64_t)1 << 46;
+  desc |= (uint64_t)2 << 61;
+  return desc;
+}
+
+// Instruction descriptor: float32 accumulator, bfloat16 A and B, both K-major, M = 128, N = BN.
+__host__ __device__ constexpr uint32_t instr_desc(int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kGemmBM >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tmem_load_32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+
+template <int BN, int STAGES>
+struct GemmShared {
+  alignas(1024) unsigned char a[STAGES][kGemmBM * kGemmBK * 2];
+  alignas(1024) unsigned char b[STAGES][BN * kGemmBK * 2];
+  uint64_t full[STAGES];
+  uint64_t empty[STAGES];
+  uint64_t accum;
+  uint32_t tmem_base;
+  uint32_t failed;
+};
+
+template <int BN, int STAGES, int EPI>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    void* __restrict__ out, int ldo, int M, int N, int K, int inter, int m_tiles,
+                    int* __restrict__ error) {
+  extern __shared__ unsigned char raw[];
+  auto& sm = *reinterpret_cast<GemmShared<BN, STAGES>*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
+  constexpr uint32_t TMEM_COLS = BN <= 128 ? 128 : 256;
+  constexpr uint32_t STAGE_BYTES = (kGemmBM + BN) * kGemmBK * 2;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = (blockIdx.x % m_tiles) * kGemmBM;
+  const int n_tile = blockIdx.x / m_tiles;
+  // Rows of W behind the tile's columns: [n0, n0 + BN), or with SwiGLU 128 gate rows and the 128 up rows.
+  const int n0 = EPI == GEMM_EPI_SWIGLU ? n_tile * (BN / 2) : n_tile * BN;
+  const int k_blocks = (K + kGemmBK - 1) / kGemmBK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&sm.full[s], 1);
+      mbar_init(&sm.empty[s], 1);
+    }
+    mbar_init(&sm.accum, 1);
+    sm.failed = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)),
+                 "r"(TMEM_COLS));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = sm.tmem_base;
+
+  if (warp == 0) {
+    // ---- producer ----------------------------------------------------------------------------------------
+    if (lane == 0) {
+      int issued = 0;
+      for (int kb = 0; kb < k_blocks; ++kb) {
+        const int s = kb % STAGES;
+        const uint32_t round = kb / STAGES;
+        if (!mbar_wait(&sm.empty[s], (round & 1) ^ 1)) { atomicExch(&sm.failed, 1u); break; }
+        mbar_expect_tx(&sm.full[s], STAGE_BYTES);
+        tma_load_2d(sm.a[s], &map_a, &sm.full[s], kb * kGemmBK, m0);
+        if (EPI == GEMM_EPI_SWIGLU) {
+          tma_load_2d(sm.b[s], &map_b, &sm.full[s], kb * kGemmBK, n0);
+          tma_load_2d(sm.b[s] + (BN / 2) * kGemmBK * 2, &map_b, &sm.full[s], kb * kGemmBK, inter + n0);
+        } else {
+          tma_load_2d(sm.b[s], &map_b, &sm.full[s], kb * kGemmBK, n0);
+        }
+        issued = kb + 1;
+      }
+      if (sm.failed) {
+        // Copies already issued still land in shared memory: give them a bounded time before leaving.
+        for (int kb = max(0, issued - STAGES); kb < issued; ++kb) mbar_wait(&sm.full[kb % STAGES], (kb / STAGES) & 1);
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer ----------------------------------------------------------------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = instr_desc(BN);
+      for (int kb = 0; kb < k_blocks; ++kb) {
+        const int s = kb % STAGES;
+        if (!mbar_wait(&sm.full[s], (kb / STAGES) & 1)) { atomicExch(&sm.failed, 1u); break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint64_t a_desc = smem_desc(sm.a[s]), b_desc = smem_desc(sm.b[s]);
+#pragma unroll
+        for (int k = 0; k < kGemmBK / 16; ++k)  // 32 bytes further along K inside the swizzled row: +2 in the address field
+          umma_bf16(tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+        umma_commit(&sm.empty[s]);  // arrives when these MMAs have read the stage
+      }
+      umma_commit(&sm.accum);       // arrives when the accumulator is complete
+    }
+  } else {
+    // ---- epilogue ------------------------------------------------------------------------------------------
+    const bool ready = mbar_wait(&sm.accum, 0);
+    if (!ready) atomicExch(&sm.failed, 1u);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const int quadrant = warp & 3;
+    const int row = m0 + quadrant * 32 + lane;
+    const uint32_t lane_base = tmem + ((uint32_t)(quadrant * 32) << 16);
+    if (ready && !sm.failed) {
+      if (EPI == GEMM_EPI_SWIGLU) {
+        constexpr int HALF = BN / 2;
+        for (int c0 = 0; c0 < HALF; c0 += 32) {
+          uint32_t gate[32], up[32];
+          tmem_load_32(lane_base + c0, gate);
+          tmem_load_32(lane_base + HALF + c0, up);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          const int col = n0 + c0;
+          if (row < M) {
+            __nv_bfloat16* dst = (__nv_bfloat16*)out + (size_t)row * ldo + col;
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              float v[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                const float g = __uint_as_float(gate[j + e]), u = __uint_as_float(up[j + e]);
+                v[e] = g / (1.f + __expf(-g)) * u;
+              }
+              if (col + j + 8 <= inter && ((ldo | col) & 7) == 0) {
+                store8(dst + j, v);
+              } else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e)
+                  if (col + j + e < inter) dst[j + e] = __float2bfloat16_rn(v[e]);
+              }
+            }
+          }
+        }
+      } else {
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          uint32_t acc[32];
+          tmem_load_32(lane_base + c0, acc);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          const int col = n0 + c0;
+          if (row < M && col < N) {
+            if (EPI == GEMM_EPI_F32) {
+              float* dst = (float*)out + (size_t)row * ldo + col;
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) {
+                if (col + j + 4 <= N && ((ldo | col) & 3) == 0) {
+                  *reinterpret_cast<float4*>(dst + j) =
+                      make_float4(__uint_as_float(acc[j]), __uint_as_float(acc[j + 1]), __uint_as_float(acc[j + 2]),
+                                  __uint_as_float(acc[j + 3]));
+                } else {
+#pragma unroll
+                  for (int e = 0; e < 4; ++e)
+                    if (col + j + e < N) dst[j + e] = __uint_as_float(acc[j + e]);
+                }
+              }
+            } else {
+              __nv_bfloat16* dst = (__nv_bfloat16*)out + (size_t)row * ldo + col;
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                float v[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(acc[j + e]);
+                if (col + j + 8 <= N && ((ldo | col) & 7) == 0) {
+                  store8(dst + j, v);
+                } else {
+#pragma unroll
+                  for (int e = 0; e < 8; ++e)
+                    if (col + j + e < N) dst[j + e] = __float2bfloat16_rn(v[e]);
+                }
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS));
+  }
+  if (threadIdx.x == 0 && sm.failed && error) atomicExch(error, 6);
+}
+
+// ---- host side ---------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiled encode_tiled() {
+  static EncodeTiled fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult status;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &status) == cudaSuccess &&
+        status == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiled>(ptr);
+  }
+  return fn;
+}
+
+// A [rows, K] bfloat16 matrix (row stride `ld` elements) seen through boxes of `box_rows` x 64, 128-byte swizzle.
+static int make_map(CUtensorMap* map, const void* base, int rows, int K, int ld, int box_rows) {
+  EncodeTiled encode = encode_tiled();
+  if (encode == nullptr) return DISTIE_ERR_UNSUPPORTED;
+  const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)kGemmBK, (cuuint32_t)box_rows};
+  const cuuint32_t elem[2] = {1, 1};
+  const CUresult res = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
+                              elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return res == CUDA_SUCCESS ? 0 : DISTIE_ERR_ARG;
+}
+
+template <int BN, int STAGES, int EPI>
+static int launch_gemm(const CUtensorMap& map_a, const CUtensorMap& map_b, void* out, int ldo, int M, int N, int K,
+                       int inter, int* error, cudaStream_t stream) {
+  const size_t shared = sizeof(GemmShared<BN, STAGES>) + 1024;
+  static bool configured = false;
+  if (!configured) {
+    const cudaError_t err =
+        cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, STAGES, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+    if (err != cudaSuccess) return (int)err;
+    configured = true;
+  }
+  const int m_tiles = (M + kGemmBM - 1) / kGemmBM;
+  const int columns = EPI == GEMM_EPI_SWIGLU ? inter : N;
+  const int per_tile = EPI == GEMM_EPI_SWIGLU ? BN / 2 : BN;
+  const int n_tiles = (columns + per_tile - 1) / per_tile;
+  gemm_tcgen05_kernel<BN, STAGES, EPI><<<m_tiles * n_tiles, kGemmThreads, shared, stream>>>(
+      map_a, map_b, out, ldo, M, N, K, inter, m_tiles, error);
+  DISTIE_LAUNCH_CHECK();
+  return 0;
+}
+
+}  // namespace distie
+
+using namespace distie;
+
+// out = x[M, K] w[N, K]^T.  epi 0: bfloat16 [M, N]; 1: float32 [M, N]; 2: w is [2 * inter, K] and
+// out[M, inter] = silu(x Wg^T) * (x Wu^T) in bfloat16 (N = 2 * inter).  x and w are bfloat16 with row
+// strides ldx and K; K must be a multiple of 8 and the pointers 16-byte aligned.
+extern "C" int distie_gemm_tcgen05(const void* x, int ldx, const void* w, void* out, int ldo, int M, int N, int K,
+                                   int epi, int* error, cudaStream_t stream) {
+  if (M <= 0) return 0;
+  if (N < 1 || K < 8 || (K & 7) || (ldx & 7) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15))
+    return DISTIE_ERR_UNSUPPORTED;
+  if (epi == GEMM_EPI_SWIGLU && (N & 1)) return DISTIE_ERR_ARG;
+  CUtensorMap map_a, map_b;
+  int status = make_map(&map_a, x, M, K, ldx, kGemmBM);
+  if (status != 0) return status;
+  const int inter = N / 2;
+  if (epi == GEMM_EPI_SWIGLU) {
+    status = make_map(&map_b, w, N, K, K, 128);
+    if (status != 0) return status;
+    return launch_gemm<256, 4, GEMM_EPI_SWIGLU>(map_a, map_b, out, ldo, M, N, K, inter, error, stream);
+  }
+  // Tile width: 256 columns when that still gives every SM a tile, else 128.
+  const int m_tiles = (M + kGemmBM - 1) / kGemmBM;
+  const bool wide = (long long)m_tiles * ((N + 255) / 256) >= 148;
+  status = make_map(&map_b, w, N, K, K, wide ? 256 : 128);
+  if (status != 0) return status;
+  if (epi == GEMM_EPI_F32) {
+    if (wide) return launch_gemm<256, 4, GEMM_EPI_F32>(map_a, map_b, out, ldo, M, N, K, 0, error, stream);
+    return launch_gemm<128, 6, GEMM_EPI_F32>(map_a, map_b, out, ldo, M, N, K, 0, error, stream);
+  }
+  if (epi == GEMM_EPI_BF16) {
+    if (wide) return launch_gemm<256, 4, GEMM_EPI_BF16>(map_a, map_b, out, ldo, M, N, K, 0, error, stream);
+    return launch_gemm<128, 6, GEMM_EPI_BF16>(map_a, map_b, out, ldo, M, N, K, 0, error, stream);
+  }
+  return DISTIE_ERR_ARG;
+}

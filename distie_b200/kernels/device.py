@@ -31,6 +31,7 @@ _ERROR_TEXT = {
     2: "a new token's page is missing from its block table (cache write)",
     3: "a block table does not cover the keys a token attends to",
     4: "a block table does not cover the keys a decoded token attends to",
+    6: "a tensor-core product gave up waiting for its own copies or instructions",
     5: "a block table does not cover the keys a portion of a prompt attends to",
 }
 
@@ -97,7 +98,14 @@ class DeviceKernels(KernelSet):
                 return
             if code != -2:
                 check(code, "add_rmsnorm_split")
-            delta = (delta[0] if delta.shape[0] == 1 else delta.sum(0)).to(self.dtype)  # a width the fused kernel refuses
+            # A width the fused kernel refuses: add the slices up here, in float32.
+            summed = delta[0] if delta.shape[0] == 1 else delta.sum(0)
+            if rows_index is None:
+                residual.add_(summed)
+                delta = None
+            else:
+                index = rows_index.long()
+                residual, delta, rows_ptr = residual.index_select(0, index) + summed.index_select(0, index), None, None
         check(
             function("distie_add_rmsnorm")(
                 delta.data_ptr() if delta is not None else None, residual.data_ptr(), weight.data_ptr(),
@@ -133,12 +141,34 @@ class DeviceKernels(KernelSet):
             out = torch.empty((x.shape[0], weight.shape[0]), dtype=out_dtype, device=x.device)
             self._linear_skinny(x, weight, bias, out, 0)
             return out
+        if self._tensor_core(x, weight) and (bias is None or out_dtype == torch.float32):
+            out = torch.empty((x.shape[0], weight.shape[0]), dtype=out_dtype, device=x.device)
+            self._gemm_tcgen05(x, weight, out, 1 if out_dtype == torch.float32 else 0)
+            return out if bias is None else out.add_(bias)
         if bias is None and out_dtype == self.dtype:
             return torch.mm(x, weight.t())
         y32 = torch.mm(x, weight.t(), out_dtype=torch.float32)
         if out_dtype == torch.float32:
             return y32 if bias is None else y32.add_(bias)
         return self._bias_cast(y32, bias, out_dtype)
+
+    def _tensor_core(self, x, weight) -> bool:
+        """Products of more rows than the weight-streaming kernel takes: the tcgen05 kernel."""
+        return (
+            self.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.dtype == torch.bfloat16
+            and x.shape[0] > _SKINNY_ROWS and weight.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and x.stride(1) == 1
+            and weight.is_contiguous()
+        )
+
+    def _gemm_tcgen05(self, x, weight, out, epi: int) -> None:
+        check(
+            function("distie_gemm_tcgen05")(
+                x.data_ptr(), x.stride(0), weight.data_ptr(), out.data_ptr(), out.stride(0), x.shape[0],
+                weight.shape[0], weight.shape[1], epi, self.error_flag.data_ptr(), self._stream(),
+            ),
+            "gemm_tcgen05",
+        )
+        self.launches += 1
 
     def _skinny(self, x, weight) -> bool:
         return (
@@ -161,6 +191,10 @@ class DeviceKernels(KernelSet):
         if self._skinny(x, weight):
             out = torch.empty((x.shape[0], weight.shape[0] // 2), dtype=self.dtype, device=x.device)
             self._linear_skinny(x, weight, None, out, 1)
+            return out
+        if self._tensor_core(x, weight) and weight.shape[0] % 2 == 0:
+            out = torch.empty((x.shape[0], weight.shape[0] // 2), dtype=self.dtype, device=x.device)
+            self._gemm_tcgen05(x, weight, out, 2)
             return out
         return super().linear_swiglu(x, weight)
 

@@ -172,6 +172,28 @@ def test_linear(kernel_sets, dtype, m, k, n, bias):
         close(ks.linear(x, w32, b, out_dtype=torch.float32), want32, torch.float32, "float32-stored matrix")
 
 
+@pytest.mark.parametrize(
+    "m,k,n", [(128, 64, 128), (17, 96, 40), (130, 1536, 2048), (2048, 1536, 1536), (300, 8960, 1536), (64, 200, 1000), (513, 72, 264)]
+)
+def test_tensor_core_product(kernel_sets, m, k, n):
+    """The tcgen05 kernel alone: bfloat16 and float32 results, ragged edges in every dimension."""
+    ks = kernel_sets[torch.bfloat16]
+    x = torch.randn(m, k, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(n, k, device="cuda") * 0.1).to(torch.bfloat16)
+    want = torch.nn.functional.linear(x.double(), w.double())
+    for out_dtype, epi in ((torch.bfloat16, 0), (torch.float32, 1)):
+        out = torch.full((m, n), float("nan"), dtype=out_dtype, device="cuda")
+        ks._gemm_tcgen05(x, w, out, epi)
+        ks.check_errors()
+        close(out, want, torch.bfloat16 if epi == 0 else torch.float32, f"tcgen05 product, epilogue {epi}")
+    if n % 2 == 0:
+        inter = n // 2
+        out = torch.full((m, inter), float("nan"), dtype=torch.bfloat16, device="cuda")
+        ks._gemm_tcgen05(x, w, out, 2)
+        ks.check_errors()
+        close(out, torch.nn.functional.silu(want[:, :inter]) * want[:, inter:], torch.bfloat16, "tcgen05 product with SwiGLU")
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("m,k,inter", [(3, 96, 100), (8, 1536, 8960), (13, 200, 57), (40, 96, 224), (1, 64, 8)])
 def test_linear_swiglu(kernel_sets, dtype, m, k, inter):
