@@ -29,13 +29,9 @@ namespace distie {
 
 constexpr int kMmaDecodeWarps = 4;
 
-__device__ __forceinline__ uint4 load16(const void* p) {
-  uint4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p));
-  return v;
-}
+// Keys and values are read once and the newest row was written by the kernel just before this one,
+// which may still have been running when this kernel started: through L2, past L1.
+__device__ __forceinline__ uint4 load16(const void* p) { return load16_cg(p); }
 
 __device__ __forceinline__ void mma_16816_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                                uint32_t b0, uint32_t b1) {
@@ -69,6 +65,7 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_row_strid
   __shared__ float sh_m[kMmaDecodeWarps][16], sh_l[kMmaDecodeWarps][16];
   __shared__ float sh_o[kMmaDecodeWarps][16][D + 1];
 
+  grid_dependency_release();
   const int t = blockIdx.x;
   const int kv_head = blockIdx.y / head_chunks, chunk = blockIdx.y % head_chunks;
   const int split = blockIdx.z, num_splits = gridDim.z;
@@ -87,14 +84,17 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_row_strid
   const int lo = max(first, (first_page + split * pages_per_split) * page_size);
   const int hi = min(pos, (first_page + (split + 1) * pages_per_split) * page_size - 1);
 
+  // Positions, seats and tables are inputs of the step; q and the newest key and value come from
+  // the kernel before this one.
+  grid_dependency_wait();
   // Query fragments: rows g and g + 8 of the head chunk, 8 consecutive dims per piece.
   uint4 qa[QC], qb[QC];
   const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
   for (int j = 0; j < QC; ++j) {
     const __nv_bfloat16* base = q + (size_t)t * q_row_stride + 32 * j + 8 * c;
-    qa[j] = g < heads_here ? *reinterpret_cast<const uint4*>(base + (size_t)(head0 + g) * D) : zero;
-    qb[j] = g + 8 < heads_here ? *reinterpret_cast<const uint4*>(base + (size_t)(head0 + g + 8) * D) : zero;
+    qa[j] = g < heads_here ? load16_cg(base + (size_t)(head0 + g) * D) : zero;
+    qb[j] = g + 8 < heads_here ? load16_cg(base + (size_t)(head0 + g + 8) * D) : zero;
   }
 
   float o[NT][4];
@@ -241,17 +241,19 @@ __global__ void __launch_bounds__(128)
 attention_decode_mma_merge_kernel(const float* __restrict__ scratch_o, const float* __restrict__ scratch_ml,
                                   __nv_bfloat16* __restrict__ out, int out_row_stride, int num_heads, int head_dim,
                                   int num_splits) {
+  grid_dependency_release();
+  grid_dependency_wait();
   const int t = blockIdx.x, head = blockIdx.y;
   const size_t row0 = ((size_t)t * num_heads + head) * num_splits;
   float m_all = -INFINITY;
-  for (int s = 0; s < num_splits; ++s) m_all = fmaxf(m_all, scratch_ml[(row0 + s) * 2]);
+  for (int s = 0; s < num_splits; ++s) m_all = fmaxf(m_all, __ldcg(scratch_ml + (row0 + s) * 2));
   for (int e = threadIdx.x; e < head_dim; e += blockDim.x) {
     float l_all = 0.f, acc = 0.f;
     for (int s = 0; s < num_splits; ++s) {
-      const float ms = scratch_ml[(row0 + s) * 2];
+      const float ms = __ldcg(scratch_ml + (row0 + s) * 2);
       const float weight = ms == -INFINITY ? 0.f : exp2f(ms - m_all);
-      l_all += scratch_ml[(row0 + s) * 2 + 1] * weight;
-      acc += scratch_o[(row0 + s) * head_dim + e] * weight;
+      l_all += __ldcg(scratch_ml + (row0 + s) * 2 + 1) * weight;
+      acc += __ldcg(scratch_o + (row0 + s) * head_dim + e) * weight;
     }
     out[(size_t)t * out_row_stride + (size_t)head * head_dim + e] =
         __float2bfloat16_rn(l_all > 0.f ? acc / l_all : 0.f);
@@ -280,20 +282,23 @@ extern "C" int distie_attention_decode_mma(const void* q, int q_row_stride, void
   float* scratch_o = scratch;
   float* scratch_ml = scratch ? scratch + (size_t)tokens * num_heads * num_splits * head_dim : nullptr;
   const float scale_log2 = scale * 1.4426950408889634f;
-#define DISTIE_MMA_DECODE(DV)                                                                                     \
-  attention_decode_mma_kernel<DV><<<grid, kMmaDecodeWarps * 32, 0, stream>>>(                                     \
-      (const __nv_bfloat16*)q, q_row_stride, (__nv_bfloat16*)out, out_row_stride, scratch_o, scratch_ml, positions, \
-      token_seq, seq_seat, block_table, table_width, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, \
-      num_heads, group, chunks, num_kv_heads, page_size, num_pages, window, scale_log2, error)
+  cudaError_t err;
+#define DISTIE_MMA_DECODE(DV)                                                                                      \
+  err = launch_dependent_family(8, attention_decode_mma_kernel<DV>, grid, dim3(kMmaDecodeWarps * 32), 0, stream,             \
+                         (const __nv_bfloat16*)q, q_row_stride, (__nv_bfloat16*)out, out_row_stride, scratch_o,     \
+                         scratch_ml, positions, token_seq, seq_seat, block_table, table_width,                     \
+                         (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, num_heads, group, chunks,   \
+                         num_kv_heads, page_size, num_pages, window, scale_log2, error)
   if (head_dim == 64) DISTIE_MMA_DECODE(64);
   else DISTIE_MMA_DECODE(128);
 #undef DISTIE_MMA_DECODE
-  DISTIE_LAUNCH_CHECK();
+  if (err != cudaSuccess) return (int)err;
   if (num_splits > 1) {
     const dim3 merge_grid(tokens, num_heads);
-    attention_decode_mma_merge_kernel<<<merge_grid, head_dim >= 128 ? 128 : 64, 0, stream>>>(
-        scratch_o, scratch_ml, (__nv_bfloat16*)out, out_row_stride, num_heads, head_dim, num_splits);
-    DISTIE_LAUNCH_CHECK();
+    err = launch_dependent_family(8, attention_decode_mma_merge_kernel, merge_grid, dim3(head_dim >= 128 ? 128 : 64), 0, stream,
+                           (const float*)scratch_o, (const float*)scratch_ml, (__nv_bfloat16*)out, out_row_stride,
+                           num_heads, head_dim, num_splits);
+    if (err != cudaSuccess) return (int)err;
   }
   return 0;
 }

@@ -58,7 +58,7 @@ __device__ __forceinline__ uint32_t tile_offset(int row, int chunk) {
 }
 
 template <int D>
-__global__ void __launch_bounds__(kPrefillWarps * 32, 3)
+__global__ void __launch_bounds__(kPrefillWarps * 32)
 attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, __nv_bfloat16* __restrict__ out,
                          int out_row_stride, const int* __restrict__ q_tiles, const int* __restrict__ positions,
                          const int* __restrict__ token_seq, const int* __restrict__ seq_seat,

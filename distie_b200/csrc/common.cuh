@@ -11,6 +11,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #define DISTIE_F32 0
 #define DISTIE_BF16 1
@@ -105,6 +106,50 @@ __device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&v)[8]) {
   *reinterpret_cast<uint4*>(p) = raw;
 }
 
+// Programmatic dependent launch.  A kernel launched with `launch_dependent` may start while the
+// kernel before it in the stream is still running; it may read data that no kernel of the step
+// writes (weights, the step's index arrays, block tables) at once, and must call
+// `grid_dependency_wait()` before it reads anything an earlier kernel produced and before it
+// writes global memory (a buffer it writes may still be read by an earlier kernel).  The wait
+// returns when all earlier kernels have finished and their writes are visible.  Calling
+// `grid_dependency_release()` early lets the next kernel start its own independent part in turn.
+// Launched the ordinary way, both calls do nothing.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependency_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// Loads of data that the kernel before this one produced, for kernels that start early (see
+// launch_dependent below): through L2 (.cg), never through the non-coherent path or a line that L1
+// may still hold from before the producer ran.
+__device__ __forceinline__ uint4 load16_cg(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void load8_cg(const float* p, float (&out)[8]) {
+  const uint4 a = load16_cg(p), b = load16_cg(p + 4);
+  out[0] = __uint_as_float(a.x); out[1] = __uint_as_float(a.y); out[2] = __uint_as_float(a.z); out[3] = __uint_as_float(a.w);
+  out[4] = __uint_as_float(b.x); out[5] = __uint_as_float(b.y); out[6] = __uint_as_float(b.z); out[7] = __uint_as_float(b.w);
+}
+__device__ __forceinline__ void load8_cg(const __nv_bfloat16* p, float (&out)[8]) {
+  const uint4 raw = load16_cg(p);
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    out[2 * i] = __uint_as_float(w[i] << 16);
+    out[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+__device__ __forceinline__ float4 load4_cg(const float* p) {
+  const uint4 a = load16_cg(p);
+  return make_float4(__uint_as_float(a.x), __uint_as_float(a.y), __uint_as_float(a.z), __uint_as_float(a.w));
+}
+__device__ __forceinline__ float4 load4_cg(const __nv_bfloat16* p) {
+  uint2 raw;
+  asm volatile("ld.global.cg.v2.u32 {%0,%1}, [%2];" : "=r"(raw.x), "=r"(raw.y) : "l"(p) : "memory");
+  return make_float4(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u),
+                     __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xffff0000u));
+}
+
 // Four consecutive elements as floats (16-byte aligned for float, 8-byte for bfloat16).
 __device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
 __device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
@@ -119,6 +164,34 @@ __device__ __forceinline__ void store4(__nv_bfloat16* p, float4 v) {
   t = __floats2bfloat162_rn(v.x, v.y); raw.x = *reinterpret_cast<uint32_t*>(&t);
   t = __floats2bfloat162_rn(v.z, v.w); raw.y = *reinterpret_cast<uint32_t*>(&t);
   *reinterpret_cast<uint2*>(p) = raw;
+}
+
+template <typename... Params, typename... Args>
+inline cudaError_t launch_dependent_family(int family, void (*kernel)(Params...), dim3 grid, dim3 block, size_t shared,
+                                           cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = shared;
+  config.stream = stream;
+  // DISTIE_DEPENDENT_LAUNCH=0 turns the early start off (every kernel then waits for the one before it).
+  static const int mask = [] {
+    const char* flag = getenv("DISTIE_DEPENDENT_LAUNCH");
+    return flag == nullptr ? 0xff : atoi(flag);
+  }();
+  const bool enabled = (mask & family) != 0;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = enabled ? 1 : 0;
+  config.attrs = attribute;
+  config.numAttrs = 1;
+  return cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
+}
+
+template <typename... Params, typename... Args>
+inline cudaError_t launch_dependent(void (*kernel)(Params...), dim3 grid, dim3 block, size_t shared,
+                                    cudaStream_t stream, Args... args) {
+  return launch_dependent_family(0xff, kernel, grid, block, shared, stream, args...);
 }
 
 }  // namespace distie

@@ -90,14 +90,17 @@ __global__ void __launch_bounds__(512) add_rmsnorm_vec_kernel(const DT* __restri
   const bool write_back = (delta != nullptr) && (rows_index == nullptr);
   const int chunks = hidden >> 2;
   float4 v[VPT], wv[VPT];
+  grid_dependency_release();
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {  // the norm's weight is written by no kernel: load it before the wait
+    const int ch = threadIdx.x + i * blockDim.x;
+    wv[i] = ch < chunks ? load4(weight + 4 * ch) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  grid_dependency_wait();
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const int ch = threadIdx.x + i * blockDim.x;
-    v[i] = wv[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (ch < chunks) {
-      v[i] = load4(res + 4 * ch);
-      wv[i] = load4(weight + 4 * ch);
-    }
+    v[i] = ch < chunks ? load4(res + 4 * ch) : make_float4(0.f, 0.f, 0.f, 0.f);
   }
   if (del) {
     // Four slices per round, all their loads issued before any sum: one round trip for up to four.
@@ -108,7 +111,7 @@ __global__ void __launch_bounds__(512) add_rmsnorm_vec_kernel(const DT* __restri
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
           const int ch = threadIdx.x + i * blockDim.x;
-          d[u][i] = (sp0 + u < splits && ch < chunks) ? load4(del + (sp0 + u) * split_stride + 4 * ch)
+          d[u][i] = (sp0 + u < splits && ch < chunks) ? load4_cg(del + (sp0 + u) * split_stride + 4 * ch)
                                                       : make_float4(0.f, 0.f, 0.f, 0.f);
         }
 #pragma unroll
@@ -250,6 +253,9 @@ __global__ void rope_kv_write_vec_kernel(const QT* in, int splits, size_t split_
                                          T* __restrict__ v_cache, int num_heads, int num_kv_heads, int head_dim,
                                          int page_size, int num_pages, int write_cache, int* __restrict__ error) {
   extern __shared__ float trig[];  // cos[head_dim/2], sin[head_dim/2]
+  // Positions, block tables and frequencies are inputs of the step, written by no kernel: the
+  // angles and the page are worked out before the wait for the projection.
+  grid_dependency_release();
   const int t = blockIdx.x;
   const int pos = positions[t];
   const int half = head_dim >> 1;
@@ -276,6 +282,7 @@ __global__ void rope_kv_write_vec_kernel(const QT* in, int splits, size_t split_
     }
   }
   __syncthreads();
+  grid_dependency_wait();
   const size_t cache_head_stride = (size_t)page_size * head_dim;
   const int pieces = half >> 3;  // pieces of 8 pairs per head
   const int rot_units = (num_heads + (write_cache ? num_kv_heads : 0)) * pieces;
@@ -286,13 +293,13 @@ __global__ void rope_kv_write_vec_kernel(const QT* in, int splits, size_t split_
 #pragma unroll
     for (int i = 0; i < 8; ++i) b[i] = 0.f;
     if (bias) load8(bias + offset, b);
-    load8(row + offset, dst);
+    load8_cg(row + offset, dst);
     for (int sp0 = 1; sp0 < splits; sp0 += 3) {  // up to three more slices per round, loads first
       float more[3][8];
 #pragma unroll
       for (int u = 0; u < 3; ++u) {
         if (sp0 + u < splits) {
-          load8(row + (sp0 + u) * split_stride + offset, more[u]);
+          load8_cg(row + (sp0 + u) * split_stride + offset, more[u]);
         } else {
 #pragma unroll
           for (int i = 0; i < 8; ++i) more[u][i] = 0.f;
@@ -403,14 +410,15 @@ extern "C" int distie_add_rmsnorm(const void* delta, float* residual, const floa
   if ((hidden & 3) == 0 && hidden <= 16 * 512 && aligned) {
     int threads = 128;
     while (threads * 16 < hidden) threads *= 2;
+    cudaError_t err;
     if (dtype == DISTIE_BF16)
-      add_rmsnorm_vec_kernel<<<rows, threads, 0, stream>>>((const __nv_bfloat16*)delta, 1, (size_t)0, residual,
-                                                           weight, (__nv_bfloat16*)out, rows_index, hidden, eps);
+      err = launch_dependent_family(2, add_rmsnorm_vec_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(rows), dim3(threads), 0, stream,
+                             (const __nv_bfloat16*)delta, 1, (size_t)0, residual, weight, (__nv_bfloat16*)out,
+                             rows_index, hidden, eps);
     else
-      add_rmsnorm_vec_kernel<<<rows, threads, 0, stream>>>((const float*)delta, 1, (size_t)0, residual, weight,
-                                                           (float*)out, rows_index, hidden, eps);
-    DISTIE_LAUNCH_CHECK();
-    return 0;
+      err = launch_dependent_family(2, add_rmsnorm_vec_kernel<float, float>, dim3(rows), dim3(threads), 0, stream,
+                             (const float*)delta, 1, (size_t)0, residual, weight, (float*)out, rows_index, hidden, eps);
+    return err == cudaSuccess ? 0 : (int)err;
   }
   const int threads = hidden >= 4096 ? 512 : (hidden >= 1024 ? 256 : 128);
   if (dtype == DISTIE_BF16)
@@ -484,14 +492,14 @@ extern "C" int distie_add_rmsnorm_split(const float* partials, int splits, long 
   if ((hidden & 3) || hidden > 16 * 512 || !aligned || (split_stride & 3)) return DISTIE_ERR_UNSUPPORTED;
   int threads = 128;
   while (threads * 16 < hidden) threads *= 2;
+  cudaError_t err;
   if (dtype == DISTIE_BF16)
-    add_rmsnorm_vec_kernel<<<rows, threads, 0, stream>>>(partials, splits, (size_t)split_stride, residual, weight,
-                                                         (__nv_bfloat16*)out, rows_index, hidden, eps);
+    err = launch_dependent_family(2, add_rmsnorm_vec_kernel<__nv_bfloat16, float>, dim3(rows), dim3(threads), 0, stream, partials,
+                           splits, (size_t)split_stride, residual, weight, (__nv_bfloat16*)out, rows_index, hidden, eps);
   else
-    add_rmsnorm_vec_kernel<<<rows, threads, 0, stream>>>(partials, splits, (size_t)split_stride, residual, weight,
-                                                         (float*)out, rows_index, hidden, eps);
-  DISTIE_LAUNCH_CHECK();
-  return 0;
+    err = launch_dependent_family(2, add_rmsnorm_vec_kernel<float, float>, dim3(rows), dim3(threads), 0, stream, partials, splits,
+                           (size_t)split_stride, residual, weight, (float*)out, rows_index, hidden, eps);
+  return err == cudaSuccess ? 0 : (int)err;
 }
 
 extern "C" int distie_rope_kv_write_split(const float* partials, int splits, long long split_stride, int row_stride,
@@ -515,18 +523,19 @@ extern "C" int distie_rope_kv_write_split(const float* partials, int splits, lon
   int threads = 64;
   while (threads < units && threads < 256) threads *= 2;
   const size_t bytes = (size_t)head_dim * sizeof(float);
+  cudaError_t err;
   if (dtype == DISTIE_BF16)
-    rope_kv_write_vec_kernel<<<tokens, threads, bytes, stream>>>(
-        partials, splits, (size_t)split_stride, row_stride, bias, (__nv_bfloat16*)q_out, q_out_stride, positions,
-        token_seq, seq_seat, block_table, table_width, inv_freq, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache,
-        num_heads, num_kv_heads, head_dim, page_size, num_pages, write_cache, error);
+    err = launch_dependent_family(4, rope_kv_write_vec_kernel<__nv_bfloat16, float>, dim3(tokens), dim3(threads), bytes, stream,
+                           partials, splits, (size_t)split_stride, row_stride, bias, (__nv_bfloat16*)q_out, q_out_stride,
+                           positions, token_seq, seq_seat, block_table, table_width, inv_freq, (__nv_bfloat16*)k_cache,
+                           (__nv_bfloat16*)v_cache, num_heads, num_kv_heads, head_dim, page_size, num_pages, write_cache,
+                           error);
   else
-    rope_kv_write_vec_kernel<<<tokens, threads, bytes, stream>>>(
-        partials, splits, (size_t)split_stride, row_stride, bias, (float*)q_out, q_out_stride, positions, token_seq,
-        seq_seat, block_table, table_width, inv_freq, (float*)k_cache, (float*)v_cache, num_heads, num_kv_heads,
-        head_dim, page_size, num_pages, write_cache, error);
-  DISTIE_LAUNCH_CHECK();
-  return 0;
+    err = launch_dependent_family(4, rope_kv_write_vec_kernel<float, float>, dim3(tokens), dim3(threads), bytes, stream, partials,
+                           splits, (size_t)split_stride, row_stride, bias, (float*)q_out, q_out_stride, positions,
+                           token_seq, seq_seat, block_table, table_width, inv_freq, (float*)k_cache, (float*)v_cache,
+                           num_heads, num_kv_heads, head_dim, page_size, num_pages, write_cache, error);
+  return err == cudaSuccess ? 0 : (int)err;
 }
 
 extern "C" int distie_swiglu(const void* gate_up, void* out, int tokens, int inter, int dtype, cudaStream_t stream) {

@@ -40,11 +40,9 @@ __device__ __forceinline__ uint4 load_stream(const void* p) {  // read once: kee
   return v;
 }
 
-__device__ __forceinline__ uint4 load_cached(const void* p) {  // the few rows of x: shared by all CTAs, keep cached
-  uint4 v;
-  asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-  return v;
-}
+// The few rows of x were written by the kernel before this one, which may still have been running
+// when this kernel started: read them through L2, not through the non-coherent path.
+__device__ __forceinline__ uint4 load_cached(const void* p) { return load16_cg(p); }
 
 __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                                uint32_t b0, uint32_t b1) {
@@ -61,6 +59,7 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bflo
                    float* __restrict__ partials, int* __restrict__ counters) {
   __shared__ float red[kSkinnyWarps][NT][4][32];
   __shared__ int ticket;
+  grid_dependency_release();  // the next kernel may start its own weight loads
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, c = lane & 3;
   const int tile = blockIdx.x;
@@ -97,6 +96,9 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bflo
   const int per_split = (k_blocks_all + splits - 1) / splits;
   const int k_blocks = min(k_blocks_all, (split + 1) * per_split);
   const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+  // The weights are written by no kernel: their first loads are issued before the wait for the
+  // kernel that produces x, so that they fly while that kernel is still running.
+  bool waited = false;
   for (int kb0 = split * per_split + warp; kb0 < k_blocks; kb0 += kSkinnyWarps * kSkinnyUnroll) {
     uint4 a0[kSkinnyUnroll], a1[kSkinnyUnroll], xv[NT][kSkinnyUnroll];
 #pragma unroll
@@ -106,6 +108,16 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bflo
       const bool in_k = kb < k_blocks && k0 + 8 <= K;  // K is a multiple of 8
       a0[u] = (in_k && ok_a) ? load_stream(wa + k0) : zero;
       a1[u] = (in_k && ok_b) ? load_stream(wb + k0) : zero;
+    }
+    if (!waited) {
+      grid_dependency_wait();
+      waited = true;
+    }
+#pragma unroll
+    for (int u = 0; u < kSkinnyUnroll; ++u) {
+      const int kb = kb0 + u * kSkinnyWarps;
+      const int k0 = kb * 32 + c * 8;
+      const bool in_k = kb < k_blocks && k0 + 8 <= K;
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt)
         xv[nt][u] = (in_k && ok_x[nt]) ? load_cached(xr[nt] + k0) : zero;
@@ -120,6 +132,7 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bflo
     }
   }
 
+  if (!waited) grid_dependency_wait();  // nothing is written before the earlier kernels are done
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
@@ -213,18 +226,18 @@ int launch_skinny(const void* x, int ldx, const void* w, const float* bias, void
   if (splits > 1 && (workspace == nullptr || (long long)tiles + (long long)tiles * splits * NT * 128 > workspace_floats))
     splits = 1;
   const dim3 grid(tiles, splits);
+  cudaError_t err;
   if (swiglu) {
-    skinny_gemm_kernel<NT, EPI_SWIGLU, __nv_bfloat16><<<grid, threads, 0, stream>>>(
-        xp, ldx, wp, nullptr, (__nv_bfloat16*)out, ldo, M, N, K, inter, partials, counters);
+    err = launch_dependent_family(1, skinny_gemm_kernel<NT, EPI_SWIGLU, __nv_bfloat16>, grid, dim3(threads), 0, stream, xp, ldx,
+                           wp, (const float*)nullptr, (__nv_bfloat16*)out, ldo, M, N, K, inter, partials, counters);
   } else if (out_dtype == DISTIE_F32) {
-    skinny_gemm_kernel<NT, EPI_STORE, float><<<grid, threads, 0, stream>>>(
-        xp, ldx, wp, bias, (float*)out, ldo, M, N, K, 0, partials, counters);
+    err = launch_dependent_family(1, skinny_gemm_kernel<NT, EPI_STORE, float>, grid, dim3(threads), 0, stream, xp, ldx, wp, bias,
+                           (float*)out, ldo, M, N, K, 0, partials, counters);
   } else {
-    skinny_gemm_kernel<NT, EPI_STORE, __nv_bfloat16><<<grid, threads, 0, stream>>>(
-        xp, ldx, wp, bias, (__nv_bfloat16*)out, ldo, M, N, K, 0, partials, counters);
+    err = launch_dependent_family(1, skinny_gemm_kernel<NT, EPI_STORE, __nv_bfloat16>, grid, dim3(threads), 0, stream, xp, ldx,
+                           wp, bias, (__nv_bfloat16*)out, ldo, M, N, K, 0, partials, counters);
   }
-  DISTIE_LAUNCH_CHECK();
-  return 0;
+  return err == cudaSuccess ? 0 : (int)err;
 }
 
 }  // namespace distie
@@ -270,12 +283,14 @@ extern "C" int distie_linear_skinny_partial(const void* x, int ldx, const void* 
   const int tiles = (N + 15) / 16;
   const dim3 grid(tiles, plan_splits(tiles, K, sm_count));
   const int threads = kSkinnyWarps * 32;
+  cudaError_t err;
   if (M <= 8)
-    skinny_gemm_kernel<1, EPI_PARTIAL, float><<<grid, threads, 0, stream>>>(
-        (const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)w, nullptr, out, N, M, N, K, 0, nullptr, nullptr);
+    err = launch_dependent_family(1, skinny_gemm_kernel<1, EPI_PARTIAL, float>, grid, dim3(threads), 0, stream,
+                           (const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)w, (const float*)nullptr, out, N, M, N,
+                           K, 0, (float*)nullptr, (int*)nullptr);
   else
-    skinny_gemm_kernel<2, EPI_PARTIAL, float><<<grid, threads, 0, stream>>>(
-        (const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)w, nullptr, out, N, M, N, K, 0, nullptr, nullptr);
-  DISTIE_LAUNCH_CHECK();
-  return 0;
+    err = launch_dependent_family(1, skinny_gemm_kernel<2, EPI_PARTIAL, float>, grid, dim3(threads), 0, stream,
+                           (const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)w, (const float*)nullptr, out, N, M, N,
+                           K, 0, (float*)nullptr, (int*)nullptr);
+  return err == cudaSuccess ? 0 : (int)err;
 }

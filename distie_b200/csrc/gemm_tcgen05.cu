@@ -1,7 +1,7 @@
 // Products of many rows (prompt portions) on the 5th-generation tensor cores:
 //   C[M, N] = A[M, K] (bfloat16 activations) x W[N, K]^T (bfloat16 weights), float32 accumulation.
 //
-// One CTA computes one 128 x BN tile of C.  Operands are staged in shared memory by
+// A CTA computes 128 x BN tiles of C, one after the other (persistent, one CTA per SM).  Operands are staged in shared memory by
 // TMA (cp.async.bulk.tensor, 128-byte swizzle, K-major boxes of 64 elements) through a
 // ring of stages; one elected thread issues tcgen05.mma (M = 128, N = BN, K = 16 per
 // instruction) with the accumulator in tensor memory; four warps read the accumulator
@@ -117,25 +117,31 @@ struct GemmShared {
   alignas(1024) unsigned char b[STAGES][BN * kGemmBK * 2];
   uint64_t full[STAGES];
   uint64_t empty[STAGES];
-  uint64_t accum;
+  uint64_t accum_full[2];
+  uint64_t accum_empty[2];
   uint32_t tmem_base;
   uint32_t failed;
 };
 
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// Persistent: a CTA walks the tiles blockIdx.x, blockIdx.x + gridDim.x, ...  The accumulator is
+// double-buffered in tensor memory (2 x 256 columns), so the epilogue of one tile runs while the
+// MMAs of the next fill the other buffer; the ring of shared-memory stages runs across tiles.
 template <int BN, int STAGES, int EPI>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                    void* __restrict__ out, int ldo, int M, int N, int K, int inter, int m_tiles,
+                    void* __restrict__ out, int ldo, int M, int N, int K, int inter, int m_tiles, int num_tiles,
                     int* __restrict__ error) {
   extern __shared__ unsigned char raw[];
   auto& sm = *reinterpret_cast<GemmShared<BN, STAGES>*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
-  constexpr uint32_t TMEM_COLS = BN <= 128 ? 128 : 256;
+  constexpr uint32_t TMEM_COLS = 512;   // two accumulators, the second at column 256
+  constexpr uint32_t ACC_STRIDE = 256;
   constexpr uint32_t STAGE_BYTES = (kGemmBM + BN) * kGemmBK * 2;
+  constexpr int PER_TILE = EPI == GEMM_EPI_SWIGLU ? BN / 2 : BN;  // output columns per tile
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = (blockIdx.x % m_tiles) * kGemmBM;
-  const int n_tile = blockIdx.x / m_tiles;
-  // Rows of W behind the tile's columns: [n0, n0 + BN), or with SwiGLU 128 gate rows and the 128 up rows.
-  const int n0 = EPI == GEMM_EPI_SWIGLU ? n_tile * (BN / 2) : n_tile * BN;
   const int k_blocks = (K + kGemmBK - 1) / kGemmBK;
 
   if (threadIdx.x == 0) {
@@ -143,7 +149,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       mbar_init(&sm.full[s], 1);
       mbar_init(&sm.empty[s], 1);
     }
-    mbar_init(&sm.accum, 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&sm.accum_full[b], 1);
+      mbar_init(&sm.accum_empty[b], 4);  // one arrival per epilogue warp
+    }
     sm.failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -160,51 +169,67 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   if (warp == 0) {
     // ---- producer ----------------------------------------------------------------------------------------
     if (lane == 0) {
-      int issued = 0;
-      for (int kb = 0; kb < k_blocks; ++kb) {
-        const int s = kb % STAGES;
-        const uint32_t round = kb / STAGES;
-        if (!mbar_wait(&sm.empty[s], (round & 1) ^ 1)) { atomicExch(&sm.failed, 1u); break; }
-        mbar_expect_tx(&sm.full[s], STAGE_BYTES);
-        tma_load_2d(sm.a[s], &map_a, &sm.full[s], kb * kGemmBK, m0);
-        if (EPI == GEMM_EPI_SWIGLU) {
-          tma_load_2d(sm.b[s], &map_b, &sm.full[s], kb * kGemmBK, n0);
-          tma_load_2d(sm.b[s] + (BN / 2) * kGemmBK * 2, &map_b, &sm.full[s], kb * kGemmBK, inter + n0);
-        } else {
-          tma_load_2d(sm.b[s], &map_b, &sm.full[s], kb * kGemmBK, n0);
+      uint32_t it = 0;  // stages filled so far, over all tiles
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % m_tiles) * kGemmBM;
+        const int n0 = (tile / m_tiles) * PER_TILE;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          if (!mbar_wait(&sm.empty[s], ((it / STAGES) & 1) ^ 1)) { atomicExch(&sm.failed, 1u); ok = false; break; }
+          mbar_expect_tx(&sm.full[s], STAGE_BYTES);
+          tma_load_2d(sm.a[s], &map_a, &sm.full[s], kb * kGemmBK, m0);
+          if (EPI == GEMM_EPI_SWIGLU) {
+            tma_load_2d(sm.b[s], &map_b, &sm.full[s], kb * kGemmBK, n0);
+            tma_load_2d(sm.b[s] + (BN / 2) * kGemmBK * 2, &map_b, &sm.full[s], kb * kGemmBK, inter + n0);
+          } else {
+            tma_load_2d(sm.b[s], &map_b, &sm.full[s], kb * kGemmBK, n0);
+          }
         }
-        issued = kb + 1;
       }
-      if (sm.failed) {
+      if (!ok) {
         // Copies already issued still land in shared memory: give them a bounded time before leaving.
-        for (int kb = max(0, issued - STAGES); kb < issued; ++kb) mbar_wait(&sm.full[kb % STAGES], (kb / STAGES) & 1);
+        for (uint32_t back = (it > (uint32_t)STAGES ? it - STAGES : 0); back < it; ++back)
+          mbar_wait(&sm.full[back % STAGES], (back / STAGES) & 1);
       }
     }
   } else if (warp == 1) {
     // ---- MMA issuer ----------------------------------------------------------------------------------------
     if (lane == 0) {
       constexpr uint32_t idesc = instr_desc(BN);
-      for (int kb = 0; kb < k_blocks; ++kb) {
-        const int s = kb % STAGES;
-        if (!mbar_wait(&sm.full[s], (kb / STAGES) & 1)) { atomicExch(&sm.failed, 1u); break; }
+      uint32_t it = 0, round = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++round) {
+        const uint32_t buffer = round & 1;
+        // The epilogue must have drained this accumulator (two tiles ago).
+        if (!mbar_wait(&sm.accum_empty[buffer], ((round >> 1) & 1) ^ 1)) { atomicExch(&sm.failed, 1u); break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint64_t a_desc = smem_desc(sm.a[s]), b_desc = smem_desc(sm.b[s]);
+        const uint32_t acc = tmem + buffer * ACC_STRIDE;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          if (!mbar_wait(&sm.full[s], (it / STAGES) & 1)) { atomicExch(&sm.failed, 1u); ok = false; break; }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint64_t a_desc = smem_desc(sm.a[s]), b_desc = smem_desc(sm.b[s]);
 #pragma unroll
-        for (int k = 0; k < kGemmBK / 16; ++k)  // 32 bytes further along K inside the swizzled row: +2 in the address field
-          umma_bf16(tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
-        umma_commit(&sm.empty[s]);  // arrives when these MMAs have read the stage
+          for (int k = 0; k < kGemmBK / 16; ++k)  // 32 bytes further along K inside the swizzled row: +2 in the address field
+            umma_bf16(acc, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          umma_commit(&sm.empty[s]);  // arrives when these MMAs have read the stage
+        }
+        umma_commit(&sm.accum_full[buffer]);  // arrives when the accumulator is complete
       }
-      umma_commit(&sm.accum);       // arrives when the accumulator is complete
     }
   } else {
     // ---- epilogue ------------------------------------------------------------------------------------------
-    const bool ready = mbar_wait(&sm.accum, 0);
-    if (!ready) atomicExch(&sm.failed, 1u);
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const int quadrant = warp & 3;
-    const int row = m0 + quadrant * 32 + lane;
-    const uint32_t lane_base = tmem + ((uint32_t)(quadrant * 32) << 16);
-    if (ready && !sm.failed) {
+    uint32_t round = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++round) {
+      const uint32_t buffer = round & 1;
+      if (!mbar_wait(&sm.accum_full[buffer], (round >> 1) & 1) || sm.failed) { atomicExch(&sm.failed, 1u); break; }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const int m0 = (tile % m_tiles) * kGemmBM;
+      const int n0 = (tile / m_tiles) * PER_TILE;
+      const int row = m0 + quadrant * 32 + lane;
+      const uint32_t lane_base = tmem + buffer * ACC_STRIDE + ((uint32_t)(quadrant * 32) << 16);
       if (EPI == GEMM_EPI_SWIGLU) {
         constexpr int HALF = BN / 2;
         for (int c0 = 0; c0 < HALF; c0 += 32) {
@@ -273,6 +298,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           }
         }
       }
+      // This warp has read its part of the accumulator: hand the buffer back to the MMA issuer.
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sm.accum_empty[buffer]);
     }
   }
 
@@ -317,7 +346,7 @@ static int make_map(CUtensorMap* map, const void* base, int rows, int K, int ld,
 
 template <int BN, int STAGES, int EPI>
 static int launch_gemm(const CUtensorMap& map_a, const CUtensorMap& map_b, void* out, int ldo, int M, int N, int K,
-                       int inter, int* error, cudaStream_t stream) {
+                       int inter, int sm_count, int* error, cudaStream_t stream) {
   const size_t shared = sizeof(GemmShared<BN, STAGES>) + 1024;
   static bool configured = false;
   if (!configured) {
@@ -329,11 +358,28 @@ static int launch_gemm(const CUtensorMap& map_a, const CUtensorMap& map_b, void*
   const int m_tiles = (M + kGemmBM - 1) / kGemmBM;
   const int columns = EPI == GEMM_EPI_SWIGLU ? inter : N;
   const int per_tile = EPI == GEMM_EPI_SWIGLU ? BN / 2 : BN;
-  const int n_tiles = (columns + per_tile - 1) / per_tile;
-  gemm_tcgen05_kernel<BN, STAGES, EPI><<<m_tiles * n_tiles, kGemmThreads, shared, stream>>>(
-      map_a, map_b, out, ldo, M, N, K, inter, m_tiles, error);
+  const int num_tiles = m_tiles * ((columns + per_tile - 1) / per_tile);
+  const int grid = num_tiles < sm_count ? num_tiles : sm_count;
+  gemm_tcgen05_kernel<BN, STAGES, EPI><<<grid, kGemmThreads, shared, stream>>>(
+      map_a, map_b, out, ldo, M, N, K, inter, m_tiles, num_tiles, error);
   DISTIE_LAUNCH_CHECK();
   return 0;
+}
+
+// Tile width (128, 192 or 256 columns): the one whose waves of `sm_count` tiles cost least.
+static int pick_tile_width(int M, int N, int sm_count) {
+  const int m_tiles = (M + kGemmBM - 1) / kGemmBM;
+  int best = 256;
+  long long best_cost = -1;
+  for (int width : {256, 192, 128}) {
+    const long long tiles = (long long)m_tiles * ((N + width - 1) / width);
+    const long long cost = ((tiles + sm_count - 1) / sm_count) * width;
+    if (best_cost < 0 || cost < best_cost) {
+      best = width;
+      best_cost = cost;
+    }
+  }
+  return best;
 }
 
 }  // namespace distie
@@ -344,32 +390,30 @@ using namespace distie;
 // out[M, inter] = silu(x Wg^T) * (x Wu^T) in bfloat16 (N = 2 * inter).  x and w are bfloat16 with row
 // strides ldx and K; K must be a multiple of 8 and the pointers 16-byte aligned.
 extern "C" int distie_gemm_tcgen05(const void* x, int ldx, const void* w, void* out, int ldo, int M, int N, int K,
-                                   int epi, int* error, cudaStream_t stream) {
+                                   int epi, int sm_count, int* error, cudaStream_t stream) {
   if (M <= 0) return 0;
   if (N < 1 || K < 8 || (K & 7) || (ldx & 7) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15))
     return DISTIE_ERR_UNSUPPORTED;
   if (epi == GEMM_EPI_SWIGLU && (N & 1)) return DISTIE_ERR_ARG;
+  if (sm_count < 1) sm_count = 148;
   CUtensorMap map_a, map_b;
   int status = make_map(&map_a, x, M, K, ldx, kGemmBM);
   if (status != 0) return status;
-  const int inter = N / 2;
   if (epi == GEMM_EPI_SWIGLU) {
     status = make_map(&map_b, w, N, K, K, 128);
     if (status != 0) return status;
-    return launch_gemm<256, 4, GEMM_EPI_SWIGLU>(map_a, map_b, out, ldo, M, N, K, inter, error, stream);
+    return launch_gemm<256, 4, GEMM_EPI_SWIGLU>(map_a, map_b, out, ldo, M, N, K, N / 2, sm_count, error, stream);
   }
-  // Tile width: 256 columns when that still gives every SM a tile, else 128.
-  const int m_tiles = (M + kGemmBM - 1) / kGemmBM;
-  const bool wide = (long long)m_tiles * ((N + 255) / 256) >= 148;
-  status = make_map(&map_b, w, N, K, K, wide ? 256 : 128);
+  if (epi != GEMM_EPI_F32 && epi != GEMM_EPI_BF16) return DISTIE_ERR_ARG;
+  const int width = pick_tile_width(M, N, sm_count);
+  status = make_map(&map_b, w, N, K, K, width);
   if (status != 0) return status;
-  if (epi == GEMM_EPI_F32) {
-    if (wide) return launch_gemm<256, 4, GEMM_EPI_F32>(map_a, map_b, out, ldo, M, N, K, 0, error, stream);
-    return launch_gemm<128, 6, GEMM_EPI_F32>(map_a, map_b, out, ldo, M, N, K, 0, error, stream);
-  }
-  if (epi == GEMM_EPI_BF16) {
-    if (wide) return launch_gemm<256, 4, GEMM_EPI_BF16>(map_a, map_b, out, ldo, M, N, K, 0, error, stream);
-    return launch_gemm<128, 6, GEMM_EPI_BF16>(map_a, map_b, out, ldo, M, N, K, 0, error, stream);
-  }
-  return DISTIE_ERR_ARG;
+#define DISTIE_GEMM(BNV, STAGESV)                                                                                   \
+  return epi == GEMM_EPI_F32                                                                                        \
+             ? launch_gemm<BNV, STAGESV, GEMM_EPI_F32>(map_a, map_b, out, ldo, M, N, K, 0, sm_count, error, stream) \
+             : launch_gemm<BNV, STAGESV, GEMM_EPI_BF16>(map_a, map_b, out, ldo, M, N, K, 0, sm_count, error, stream)
+  if (width == 256) { DISTIE_GEMM(256, 4); }
+  if (width == 192) { DISTIE_GEMM(192, 5); }
+  DISTIE_GEMM(128, 6);
+#undef DISTIE_GEMM
 }

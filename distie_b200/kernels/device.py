@@ -25,6 +25,7 @@ _CODE = {torch.float32: 0, torch.bfloat16: 1}
 _DECODE_HEAD_DIMS = (16, 32, 64, 128, 256)
 _PREFILL_HEAD_DIMS = (64, 128)  # tensor-core attention for portions of prompts (bfloat16)
 _SKINNY_ROWS = 16               # weight-streaming products take up to this many rows of x
+_TENSOR_CORE_ROWS = 128         # from here on the tcgen05 kernel's 128-row tiles are full; in between: the library
 
 _ERROR_TEXT = {
     1: "a token id outside the vocabulary reached the embedding",
@@ -156,15 +157,15 @@ class DeviceKernels(KernelSet):
         """Products of more rows than the weight-streaming kernel takes: the tcgen05 kernel."""
         return (
             self.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.dtype == torch.bfloat16
-            and x.shape[0] > _SKINNY_ROWS and weight.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and x.stride(1) == 1
-            and weight.is_contiguous()
+            and x.shape[0] >= _TENSOR_CORE_ROWS and weight.shape[1] % 8 == 0 and x.stride(0) % 8 == 0
+            and x.stride(1) == 1 and weight.is_contiguous()
         )
 
     def _gemm_tcgen05(self, x, weight, out, epi: int) -> None:
         check(
             function("distie_gemm_tcgen05")(
                 x.data_ptr(), x.stride(0), weight.data_ptr(), out.data_ptr(), out.stride(0), x.shape[0],
-                weight.shape[0], weight.shape[1], epi, self.error_flag.data_ptr(), self._stream(),
+                weight.shape[0], weight.shape[1], epi, self.sm_count, self.error_flag.data_ptr(), self._stream(),
             ),
             "gemm_tcgen05",
         )
