@@ -41,8 +41,13 @@ __device__ __forceinline__ uint4 load_stream(const void* p) {  // read once: kee
 }
 
 // The few rows of x were written by the kernel before this one, which may still have been running
-// when this kernel started: read them through L2, not through the non-coherent path.
-__device__ __forceinline__ uint4 load_cached(const void* p) { return load16_cg(p); }
+// when this kernel started: an ordinary coherent load (cached in L1, where the CTAs of an SM share
+// it), never the non-coherent path, which returned stale rows in that situation.
+__device__ __forceinline__ uint4 load_cached(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.ca.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
 
 __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                                uint32_t b0, uint32_t b1) {
