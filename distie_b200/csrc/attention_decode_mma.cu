@@ -12,13 +12,18 @@
 //          the columns, head_dim the reduction:  S[head, key] = q[head] . k[key]
 //   P V    the same heads are the rows, 16 keys the reduction, head_dim the columns
 //
-// Operands come straight from global memory in 16-byte pieces, without shared
-// memory: the reduction index of an mma may be enumerated in any order as long as
+// Operands come from global memory in 16-byte pieces that are already the lanes' mma
+// fragments, so nothing is rearranged on the way: the reduction index of an mma may be enumerated in any order as long as
 // both operands agree, and so may the columns of the output.  A lane therefore
 // loads 8 consecutive elements of a key row and uses them as its share of two
 // k-steps of S, and 2 * head_dim / 16 consecutive elements of 4 value rows, from
 // which it assembles its B fragments of P V with byte permutes; output column
 // (n-tile t, lane group g) stands for dimension g * head_dim / 8 + t.
+//
+// The pieces travel through a small ring in shared memory (cp.async, three groups of 16 keys per
+// warp): the copies of the next two groups are in flight while a group is computed, which is what
+// keeps enough bytes in the air with only eight warps per SM.  Each lane reads back exactly the
+// pieces it copied, so the ring needs no layout beyond [stage][load][lane].
 //
 // Softmax state (max, sum) is float32 per lane; the four warps and, with several
 // splits, the CTAs of a token are merged as in the other kernel (same scratch
@@ -28,6 +33,11 @@
 namespace distie {
 
 constexpr int kMmaDecodeWarps = 4;
+constexpr int kMmaDecodeStages = 3;
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
 
 // Keys and values are read once and the newest row was written by the kernel just before this one,
 // which may still have been running when this kernel started: through L2, past L1.
@@ -62,8 +72,12 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_row_strid
   constexpr int QC = D / 32;      // 16-byte pieces of a key row per lane (and of a query row)
   constexpr int NT = D / 8;       // output n-tiles
   constexpr int VW = D / 64;      // 16-byte pieces of a value row per lane
+  constexpr int LOADS = 2 * QC + 4 * VW;  // 16-byte pieces per lane and group of 16 keys
+  extern __shared__ __align__(16) unsigned char dyn[];
+  // The ring of the main loop and the merge area of the tail share the dynamic shared memory.
+  uint4* ring = reinterpret_cast<uint4*>(dyn);  // [warp][stage][load][lane]
+  float(*sh_o)[16][D + 1] = reinterpret_cast<float(*)[16][D + 1]>(dyn);
   __shared__ float sh_m[kMmaDecodeWarps][16], sh_l[kMmaDecodeWarps][16];
-  __shared__ float sh_o[kMmaDecodeWarps][16][D + 1];
 
   grid_dependency_release();
   const int t = blockIdx.x;
@@ -106,14 +120,16 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_row_strid
 
   const int lo16 = lo & ~15;
   const int groups = hi >= lo ? (hi - lo16) / 16 + 1 : 0;
-  for (int grp = warp; grp < groups; grp += kMmaDecodeWarps) {
+  uint4* my_ring = ring + (size_t)warp * kMmaDecodeStages * LOADS * 32;
+  // Issues the copies of one group of 16 keys into a stage of this warp's ring: 2 key rows (columns g
+  // and g + 8 of S) and 4 value rows (reduction slots 2c, 2c+1, 2c+8, 2c+9 of P V) per lane.
+  auto issue = [&](int grp, int stage) {
     const int base_key = lo16 + grp * 16;
-    // ---- loads: 2 key rows (columns g and g + 8 of S), 4 value rows (reduction slots of P V) ----
-    uint4 kr[2][QC], vr[4][VW];
+    uint4* dst = my_ring + (size_t)stage * LOADS * 32 + lane;
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       const int key = base_key + g + 8 * h;
-      bool ok = key >= lo && key <= hi;
+      bool ok = grp < groups && key >= lo && key <= hi;
       size_t at = 0;
       if (ok) {
         const int page = table[key / page_size];
@@ -125,12 +141,13 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_row_strid
         }
       }
 #pragma unroll
-      for (int j = 0; j < QC; ++j) kr[h][j] = ok ? load16(k_cache + at + 32 * j) : zero;
+      for (int j = 0; j < QC; ++j)
+        cp_async16((uint32_t)__cvta_generic_to_shared(dst + (h * QC + j) * 32), k_cache + at + 32 * j, ok ? 16 : 0);
     }
 #pragma unroll
     for (int s = 0; s < 4; ++s) {
-      const int key = base_key + 2 * c + (s & 1) + 8 * (s >> 1);  // slots 2c, 2c+1, 2c+8, 2c+9
-      bool ok = key >= lo && key <= hi;
+      const int key = base_key + 2 * c + (s & 1) + 8 * (s >> 1);
+      bool ok = grp < groups && key >= lo && key <= hi;
       size_t at = 0;
       if (ok) {
         const int page = table[key / page_size];
@@ -141,8 +158,32 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_row_strid
         }
       }
 #pragma unroll
-      for (int w = 0; w < VW; ++w) vr[s][w] = ok ? load16(v_cache + at + 8 * w) : zero;
+      for (int w = 0; w < VW; ++w)
+        cp_async16((uint32_t)__cvta_generic_to_shared(dst + (2 * QC + s * VW + w) * 32), v_cache + at + 8 * w,
+                   ok ? 16 : 0);
     }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+
+  issue(warp, 0);
+  issue(warp + kMmaDecodeWarps, 1);
+  int stage = 0;
+  for (int grp = warp; grp < groups; grp += kMmaDecodeWarps) {
+    const int base_key = lo16 + grp * 16;
+    issue(grp + 2 * kMmaDecodeWarps, (stage + 2) % kMmaDecodeStages);  // empty group past the end
+    asm volatile("cp.async.wait_group 2;" ::: "memory");
+    __syncwarp();
+    uint4 kr[2][QC], vr[4][VW];
+    const uint4* src = my_ring + (size_t)stage * LOADS * 32 + lane;
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+#pragma unroll
+      for (int j = 0; j < QC; ++j) kr[h][j] = src[(h * QC + j) * 32];
+#pragma unroll
+    for (int s = 0; s < 4; ++s)
+#pragma unroll
+      for (int w = 0; w < VW; ++w) vr[s][w] = src[(2 * QC + s * VW + w) * 32];
+    stage = (stage + 1) % kMmaDecodeStages;
 
     // ---- S = Q K^T for keys base..base+7 (s1) and base+8..base+15 (s2) ---------------------------
     float s1[4] = {0.f, 0.f, 0.f, 0.f}, s2[4] = {0.f, 0.f, 0.f, 0.f};
@@ -197,6 +238,8 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_row_strid
   }
 
   // ---- merge the warps ---------------------------------------------------------------------------------
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  __syncthreads();  // the ring is done with: its memory becomes the merge area
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     float l = row_sum[h];
@@ -283,8 +326,21 @@ extern "C" int distie_attention_decode_mma(const void* q, int q_row_stride, void
   float* scratch_ml = scratch ? scratch + (size_t)tokens * num_heads * num_splits * head_dim : nullptr;
   const float scale_log2 = scale * 1.4426950408889634f;
   cudaError_t err;
+  // Dynamic shared memory: the larger of the ring (warps x stages x loads x 512 bytes) and the merge area.
+  const size_t loads = 2 * (head_dim / 32) + 4 * (head_dim / 64);
+  const size_t ring_bytes = (size_t)kMmaDecodeWarps * kMmaDecodeStages * loads * 512;
+  const size_t merge_bytes = (size_t)kMmaDecodeWarps * 16 * (head_dim + 1) * sizeof(float);
+  const size_t shared = ring_bytes > merge_bytes ? ring_bytes : merge_bytes;
+  static bool configured = false;
+  if (!configured) {
+    err = cudaFuncSetAttribute(attention_decode_mma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+    if (err == cudaSuccess)
+      err = cudaFuncSetAttribute(attention_decode_mma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+    if (err != cudaSuccess) return (int)err;
+    configured = true;
+  }
 #define DISTIE_MMA_DECODE(DV)                                                                                      \
-  err = launch_dependent_family(8, attention_decode_mma_kernel<DV>, grid, dim3(kMmaDecodeWarps * 32), 0, stream,             \
+  err = launch_dependent_family(8, attention_decode_mma_kernel<DV>, grid, dim3(kMmaDecodeWarps * 32), shared, stream,        \
                          (const __nv_bfloat16*)q, q_row_stride, (__nv_bfloat16*)out, out_row_stride, scratch_o,     \
                          scratch_ml, positions, token_seq, seq_seat, block_table, table_width,                     \
                          (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, num_heads, group, chunks,   \
