@@ -45,7 +45,7 @@ __device__ __forceinline__ uint4 load_stream(const void* p) {  // read once: kee
 // it), never the non-coherent path, which returned stale rows in that situation.
 __device__ __forceinline__ uint4 load_cached(const void* p) {
   uint4 v;
-  asm volatile("ld.global.ca.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  asm volatile("ld.global.ca.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
   return v;
 }
 

@@ -192,6 +192,55 @@ def test_attention_part_alone(dtype, tol, window):
         assert len(cache.pages_held(seat)[0]) < -(-tokens // 8), "pages behind the window were meant to be given back"
 
 
+def test_position_encoding_part_alone():
+    """The rotary part hands the fused kernel the reference's inverse frequencies (model.py:98)."""
+    from distie_b200.config import PartSpec
+    from distie_b200.parts import POSITION_ENCODINGS, build_part
+
+    ctx = part_context(torch.float32, {}, 64)
+    table = build_part(POSITION_ENCODINGS, PartSpec("rotary", {"head_dim": 48, "theta": 12345.0}), ctx).rotary_table()
+    assert table.rotary_dim == 48 and not table.interleaved
+    assert torch.equal(table.inv_freq.cpu(), plain.rope_inverse_frequencies(48, 12345.0))
+    partial = build_part(POSITION_ENCODINGS, PartSpec("rotary", {"head_dim": 48, "theta": 10.0, "rotary_dim": 16}), ctx)
+    assert partial.rotary_table().inv_freq.shape == (8,)
+    assert build_part(POSITION_ENCODINGS, PartSpec("none", {}), ctx).rotary_table() is None
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-5), (torch.bfloat16, 3e-2)])
+def test_block_arrangement_alone(dtype, tol):
+    """One pre-norm block over a real cache: norms, mixer, feed-forward and both residual sums."""
+    from distie_b200.cache import CacheManager
+    from distie_b200.config import LayerSpec, PartSpec
+    from distie_b200.engine.batch import BatchEntry, StepStaging, lay_out
+    from distie_b200.parts import BLOCKS, MIXERS, LayerRun, ResidualStream
+
+    cfg = {"hidden_size": 64, "intermediate_size": 96, "num_attention_heads": 2, "num_key_value_heads": 1,
+           "rms_norm_eps": 1e-5, "rope_theta": 3000.0, "num_hidden_layers": 1, "vocab_size": 8}
+    w = {k: v.to(torch.bfloat16).float() for k, v in plain.random_weights(cfg, 11, std=0.25, norm_noise=0.05).items()}
+    p = "model.layers.0."
+    attn = PartSpec("gqa_attention", {"num_heads": 2, "num_kv_heads": 1, "head_dim": 32, "qkv_bias": True, "out_bias": False,
+                                      "window": None, "position": PartSpec("rotary", {"head_dim": 32, "theta": 3000.0})}, p + "self_attn.")
+    layer = LayerSpec("pre_norm", attn, PartSpec("swiglu", {"intermediate_size": 96}, p + "mlp."),
+                      {"input": PartSpec("rmsnorm", {"eps": 1e-5}, p + "input_layernorm."),
+                       "post_mixer": PartSpec("rmsnorm", {"eps": 1e-5}, p + "post_attention_layernorm.")})
+    ctx = part_context(dtype, w, 64)
+    block = BLOCKS.get("pre_norm").build(layer, ctx)
+    cache = CacheManager({0: MIXERS.get("gqa_attention").cache_need(attn)}, {}, num_pages=4, page_size=16, max_seats=1,
+                         max_tokens_per_request=64, dtype=dtype, device="cuda:0")
+    seat, tokens = cache.open_seat(), 19
+    cache.grow(seat, tokens)
+    h = torch.randn(tokens, 64)
+    layout = lay_out([BatchEntry(seat, [0] * tokens, 0)])
+    cache.upload_tables([seat])
+    step, _ = StepStaging(256, torch.device("cuda:0")).upload(layout)
+    stream = ResidualStream(h.cuda().clone())
+    block.forward(stream, LayerRun(step=step, seqs=layout.seqs, kv=cache.kv_slot(0)))
+    got = stream.settle().cpu()
+    ctx.kernels.check_errors()
+    want, _ = plain.decoder_layer(h, w, 0, torch.arange(tokens), cfg)
+    assert float((got - want).abs().max()) <= tol * float(want.abs().max())
+
+
 # -- a toy mixer with state of its own, registered from outside the package --------
 def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
     """A running-mean mixer defined here: state per request, no change to the framework's files."""
