@@ -68,7 +68,7 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_row_strid
                             const int* __restrict__ seq_seat, const int* __restrict__ block_table, int table_width,
                             const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
                             int num_heads, int group_size, int head_chunks, int num_kv_heads, int page_size,
-                            int num_pages, int window, float scale_log2, int* __restrict__ error) {
+                            int page_shift, int num_pages, int window, float scale_log2, int* __restrict__ error) {
   constexpr int QC = D / 32;      // 16-byte pieces of a key row per lane (and of a query row)
   constexpr int NT = D / 8;       // output n-tiles
   constexpr int VW = D / 64;      // 16-byte pieces of a value row per lane
@@ -132,12 +132,14 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_row_strid
       bool ok = grp < groups && key >= lo && key <= hi;
       size_t at = 0;
       if (ok) {
-        const int page = table[key / page_size];
+        // page_shift >= 0: the page size is a power of two, so no division per row.
+        const int page = table[page_shift >= 0 ? key >> page_shift : key / page_size];
+        const int within = page_shift >= 0 ? key & (page_size - 1) : key % page_size;
         if (page < 0 || page >= num_pages) {
           if (error) atomicExch(error, 4);
           ok = false;
         } else {
-          at = (((size_t)page * num_kv_heads + kv_head) * page_size + key % page_size) * D + 8 * c;
+          at = (((size_t)page * num_kv_heads + kv_head) * page_size + within) * D + 8 * c;
         }
       }
 #pragma unroll
@@ -150,11 +152,12 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_row_strid
       bool ok = grp < groups && key >= lo && key <= hi;
       size_t at = 0;
       if (ok) {
-        const int page = table[key / page_size];
+        const int page = table[page_shift >= 0 ? key >> page_shift : key / page_size];
+        const int within = page_shift >= 0 ? key & (page_size - 1) : key % page_size;
         if (page < 0 || page >= num_pages) {
           ok = false;
         } else {
-          at = (((size_t)page * num_kv_heads + kv_head) * page_size + key % page_size) * D + g * (D / 8);
+          at = (((size_t)page * num_kv_heads + kv_head) * page_size + within) * D + g * (D / 8);
         }
       }
 #pragma unroll
@@ -325,6 +328,10 @@ extern "C" int distie_attention_decode_mma(const void* q, int q_row_stride, void
   float* scratch_o = scratch;
   float* scratch_ml = scratch ? scratch + (size_t)tokens * num_heads * num_splits * head_dim : nullptr;
   const float scale_log2 = scale * 1.4426950408889634f;
+  int page_shift = -1;
+  if ((page_size & (page_size - 1)) == 0)
+    for (page_shift = 0; (1 << page_shift) < page_size; ++page_shift) {
+    }
   cudaError_t err;
   // Dynamic shared memory: the larger of the ring (warps x stages x loads x 512 bytes) and the merge area.
   const size_t loads = 2 * (head_dim / 32) + 4 * (head_dim / 64);
@@ -344,7 +351,7 @@ extern "C" int distie_attention_decode_mma(const void* q, int q_row_stride, void
                          (const __nv_bfloat16*)q, q_row_stride, (__nv_bfloat16*)out, out_row_stride, scratch_o,     \
                          scratch_ml, positions, token_seq, seq_seat, block_table, table_width,                     \
                          (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, num_heads, group, chunks,   \
-                         num_kv_heads, page_size, num_pages, window, scale_log2, error)
+                         num_kv_heads, page_size, page_shift, num_pages, window, scale_log2, error)
   if (head_dim == 64) DISTIE_MMA_DECODE(64);
   else DISTIE_MMA_DECODE(128);
 #undef DISTIE_MMA_DECODE

@@ -64,8 +64,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, 
                          const int* __restrict__ token_seq, const int* __restrict__ seq_seat,
                          const int* __restrict__ block_table, int table_width,
                          const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
-                         int group_size, int num_kv_heads, int page_size, int num_pages, int window,
-                         float scale_log2, int* __restrict__ error) {
+                         int group_size, int num_kv_heads, int page_size, int page_shift, int num_pages,
+                         int window, float scale_log2, int* __restrict__ error) {
   constexpr int CHUNKS = D / 8;                       // 16-byte chunks per row
   constexpr int TILE_BYTES = kTileN * D * 2;
   constexpr int ROWS_PER_PASS = kPrefillWarps * 32 / CHUNKS;
@@ -109,12 +109,15 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, 
       bool ok = key <= p_last;
       size_t at = 0;
       if (ok) {
-        const int page = table[key / page_size];
+        // page_shift >= 0: the page size is a power of two, so no division per row.
+        const int column = page_shift >= 0 ? key >> page_shift : key / page_size;
+        const int within = page_shift >= 0 ? key & (page_size - 1) : key % page_size;
+        const int page = table[column];
         if (page < 0 || page >= num_pages) {
           if (error) atomicExch(error, 5);
           ok = false;
         } else {
-          at = (((size_t)page * num_kv_heads + kv_head) * page_size + key % page_size) * D + my_chunk * 8;
+          at = (((size_t)page * num_kv_heads + kv_head) * page_size + within) * D + my_chunk * 8;
         }
       }
       const uint32_t off = stage * TILE_BYTES + tile_offset<D>(r, my_chunk);
@@ -172,37 +175,49 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, 
     }
 
     // ---- mask, online softmax (base-2 exponentials of scale * log2(e) * S) ------------------
+    // Only blocks that touch the diagonal or the window's edge need the per-element test: a block
+    // is wholly visible to this warp when its last key is no later than the warp's first row and
+    // its first key is inside the window of the warp's last row.
     const int kb = kb_start + block * kTileN;
+    const int warp_first = p0 + warp * 16, warp_last = warp_first + 15;
+    const bool whole = kb + kTileN - 1 <= warp_first && (window <= 0 || kb > warp_last - window);
     float tile_max[2] = {-INFINITY, -INFINITY};
+    if (whole) {
 #pragma unroll
-    for (int i = 0; i < kTileN / 8; ++i) {
+      for (int i = 0; i < kTileN / 8; ++i)
 #pragma unroll
-      for (int r = 0; r < 4; ++r) {
-        const int key = kb + i * 8 + 2 * c + (r & 1);
-        const int p = pos_row[r >> 1];
-        const bool seen = key <= p && (window <= 0 || key > p - window);
-        const float v = seen ? s[i][r] * scale_log2 : -INFINITY;
-        s[i][r] = v;
-        tile_max[r >> 1] = fmaxf(tile_max[r >> 1], v);
+        for (int r = 0; r < 4; ++r) tile_max[r >> 1] = fmaxf(tile_max[r >> 1], s[i][r]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < kTileN / 8; ++i) {
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          const int key = kb + i * 8 + 2 * c + (r & 1);
+          const int p = pos_row[r >> 1];
+          const bool seen = key <= p && (window <= 0 || key > p - window);
+          s[i][r] = seen ? s[i][r] : -INFINITY;
+          tile_max[r >> 1] = fmaxf(tile_max[r >> 1], s[i][r]);
+        }
       }
     }
-    float corr[2];
+    // row_max holds scale_log2 * (largest raw score so far); the scale is positive, so the order is the same.
+    float corr[2], shift[2];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       float m = tile_max[h];
       m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
       m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
-      const float m_new = fmaxf(row_max[h], m);
+      const float m_new = fmaxf(row_max[h], m * scale_log2);
       corr[h] = (m_new == -INFINITY) ? 1.f : exp2f(row_max[h] - m_new);
       row_max[h] = m_new;
       row_sum[h] *= corr[h];
+      shift[h] = m_new == -INFINITY ? 0.f : -m_new;
     }
-    const float base[2] = {row_max[0] == -INFINITY ? 0.f : row_max[0], row_max[1] == -INFINITY ? 0.f : row_max[1]};
 #pragma unroll
     for (int i = 0; i < kTileN / 8; ++i) {
 #pragma unroll
       for (int r = 0; r < 4; ++r) {
-        const float p = exp2f(s[i][r] - base[r >> 1]);  // exp2(-inf) = 0 for hidden keys
+        const float p = exp2f(fmaf(s[i][r], scale_log2, shift[r >> 1]));  // exp2(-inf) = 0 for hidden keys
         s[i][r] = p;
         row_sum[r >> 1] += p;
       }
@@ -264,11 +279,16 @@ int launch_prefill(const void* q, int q_row_stride, void* out, int out_row_strid
     if (err != cudaSuccess) return (int)err;
     configured = true;
   }
+  int page_shift = -1;
+  if ((page_size & (page_size - 1)) == 0)
+    for (page_shift = 0; (1 << page_shift) < page_size; ++page_shift) {
+    }
   const dim3 grid(num_tiles, num_heads);
   attention_prefill_kernel<D><<<grid, kPrefillWarps * 32, shared, stream>>>(
       (const __nv_bfloat16*)q, q_row_stride, (__nv_bfloat16*)out, out_row_stride, q_tiles, positions, token_seq,
       seq_seat, block_table, table_width, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
-      num_heads / num_kv_heads, num_kv_heads, page_size, num_pages, window, scale * 1.4426950408889634f, error);
+      num_heads / num_kv_heads, num_kv_heads, page_size, page_shift, num_pages, window,
+      scale * 1.4426950408889634f, error);
   DISTIE_LAUNCH_CHECK();
   return 0;
 }
