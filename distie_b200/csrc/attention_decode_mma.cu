@@ -34,6 +34,7 @@ namespace distie {
 
 constexpr int kMmaDecodeWarps = 4;
 constexpr int kMmaDecodeStages = 3;
+constexpr int kMmaDecodeClusterSplits = 8;  // splits that one cluster can hold (portable cluster size)
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
@@ -68,7 +69,8 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_row_strid
                             const int* __restrict__ seq_seat, const int* __restrict__ block_table, int table_width,
                             const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
                             int num_heads, int group_size, int head_chunks, int num_kv_heads, int page_size,
-                            int page_shift, int num_pages, int window, float scale_log2, int* __restrict__ error) {
+                            int page_shift, int num_pages, int window, float scale_log2, int cluster_merge,
+                            int* __restrict__ error) {
   constexpr int QC = D / 32;      // 16-byte pieces of a key row per lane (and of a query row)
   constexpr int NT = D / 8;       // output n-tiles
   constexpr int VW = D / 64;      // 16-byte pieces of a value row per lane
@@ -78,6 +80,7 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_row_strid
   uint4* ring = reinterpret_cast<uint4*>(dyn);  // [warp][stage][load][lane]
   float(*sh_o)[16][D + 1] = reinterpret_cast<float(*)[16][D + 1]>(dyn);
   __shared__ float sh_m[kMmaDecodeWarps][16], sh_l[kMmaDecodeWarps][16];
+  __shared__ float cl_o[16][D], cl_m[16], cl_l[16];  // this split's result, read by the other CTAs of a cluster
 
   grid_dependency_release();
   const int t = blockIdx.x;
@@ -97,19 +100,6 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_row_strid
   const int pages_per_split = (pages + num_splits - 1) / num_splits;
   const int lo = max(first, (first_page + split * pages_per_split) * page_size);
   const int hi = min(pos, (first_page + (split + 1) * pages_per_split) * page_size - 1);
-
-  // Positions, seats and tables are inputs of the step; q and the newest key and value come from
-  // the kernel before this one.
-  grid_dependency_wait();
-  // Query fragments: rows g and g + 8 of the head chunk, 8 consecutive dims per piece.
-  uint4 qa[QC], qb[QC];
-  const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
-#pragma unroll
-  for (int j = 0; j < QC; ++j) {
-    const __nv_bfloat16* base = q + (size_t)t * q_row_stride + 32 * j + 8 * c;
-    qa[j] = g < heads_here ? load16_cg(base + (size_t)(head0 + g) * D) : zero;
-    qb[j] = g + 8 < heads_here ? load16_cg(base + (size_t)(head0 + g + 8) * D) : zero;
-  }
 
   float o[NT][4];
 #pragma unroll
@@ -168,8 +158,25 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_row_strid
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
 
-  issue(warp, 0);
-  issue(warp + kMmaDecodeWarps, 1);
+  // Positions, seats and tables are inputs of the step.  Of the cache only the row of the newest
+  // position comes from the kernel before this one (every other row was written in an earlier step),
+  // so groups of keys that end before it are requested before the wait; q comes after it.
+  const bool early0 = lo16 + warp * 16 + 15 < pos;
+  const bool early1 = early0 && lo16 + (warp + kMmaDecodeWarps) * 16 + 15 < pos;
+  if (early0) issue(warp, 0);
+  if (early1) issue(warp + kMmaDecodeWarps, 1);
+  grid_dependency_wait();
+  if (!early0) issue(warp, 0);
+  if (!early1) issue(warp + kMmaDecodeWarps, 1);
+  // Query fragments: rows g and g + 8 of the head chunk, 8 consecutive dims per piece.
+  uint4 qa[QC], qb[QC];
+  const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+  for (int j = 0; j < QC; ++j) {
+    const __nv_bfloat16* base = q + (size_t)t * q_row_stride + 32 * j + 8 * c;
+    qa[j] = g < heads_here ? load16_cg(base + (size_t)(head0 + g) * D) : zero;
+    qb[j] = g + 8 < heads_here ? load16_cg(base + (size_t)(head0 + g + 8) * D) : zero;
+  }
   int stage = 0;
   for (int grp = warp; grp < groups; grp += kMmaDecodeWarps) {
     const int base_key = lo16 + grp * 16;
@@ -271,6 +278,9 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_row_strid
     const int head = head0 + hd;
     if (num_splits == 1) {
       out[(size_t)t * out_row_stride + (size_t)head * D + e] = __float2bfloat16_rn(l_all > 0.f ? acc / l_all : 0.f);
+    } else if (cluster_merge) {
+      cl_o[hd][e] = acc;
+      if (e == 0) { cl_m[hd] = m_all; cl_l[hd] = l_all; }
     } else {
       const size_t row = ((size_t)t * num_heads + head) * num_splits + split;
       scratch_o[row * D + e] = acc;
@@ -279,6 +289,28 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_row_strid
         scratch_ml[row * 2 + 1] = l_all;
       }
     }
+  }
+  if (num_splits > 1 && cluster_merge) {
+    // The splits of a (token, head chunk) are the CTAs of one cluster: each combines its share of the
+    // output elements from every CTA's shared memory, splits in order, as the merge kernel would.
+    cluster_barrier();
+    const int total = heads_here * D;
+    const int share = (total + num_splits - 1) / num_splits;
+    const int end = min(total, (split + 1) * share);
+    for (int idx = split * share + threadIdx.x; idx < end; idx += kMmaDecodeWarps * 32) {
+      const int hd = idx / D, e = idx % D;
+      float m_all = -INFINITY;
+      for (int s = 0; s < num_splits; ++s) m_all = fmaxf(m_all, cluster_load(&cl_m[hd], s));
+      float l_all = 0.f, acc = 0.f;
+      for (int s = 0; s < num_splits; ++s) {
+        const float ms = cluster_load(&cl_m[hd], s);
+        const float weight = ms == -INFINITY ? 0.f : exp2f(ms - m_all);
+        l_all += cluster_load(&cl_l[hd], s) * weight;
+        acc += cluster_load(&cl_o[hd][e], s) * weight;
+      }
+      out[(size_t)t * out_row_stride + (size_t)(head0 + hd) * D + e] = __float2bfloat16_rn(l_all > 0.f ? acc / l_all : 0.f);
+    }
+    cluster_barrier();  // no CTA leaves while another may still read its shared memory
   }
 }
 
@@ -319,7 +351,7 @@ extern "C" int distie_attention_decode_mma(const void* q, int q_row_stride, void
                                            float scale, int num_splits, int* error, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (num_heads < 1 || num_kv_heads < 1 || num_heads % num_kv_heads != 0 || page_size < 1 || table_width < 1 ||
-      num_splits < 1 || num_splits > 65535 || (num_splits > 1 && scratch == nullptr) || (q_row_stride & 7))
+      num_splits < 1 || num_splits > 65535 || (num_splits > kMmaDecodeClusterSplits && scratch == nullptr) || (q_row_stride & 7))
     return DISTIE_ERR_ARG;
   if (head_dim != 64 && head_dim != 128) return DISTIE_ERR_UNSUPPORTED;
   const int group = num_heads / num_kv_heads;
@@ -346,17 +378,20 @@ extern "C" int distie_attention_decode_mma(const void* q, int q_row_stride, void
     if (err != cudaSuccess) return (int)err;
     configured = true;
   }
+  // Up to 8 splits (the portable cluster size) are merged inside the kernel, through the cluster's shared memory.
+  const int cluster_merge = (num_splits > 1 && num_splits <= kMmaDecodeClusterSplits) ? 1 : 0;
+  const dim3 cluster = cluster_merge ? dim3(1, 1, num_splits) : dim3(0, 0, 0);
 #define DISTIE_MMA_DECODE(DV)                                                                                      \
-  err = launch_dependent_family(8, attention_decode_mma_kernel<DV>, grid, dim3(kMmaDecodeWarps * 32), shared, stream,        \
-                         (const __nv_bfloat16*)q, q_row_stride, (__nv_bfloat16*)out, out_row_stride, scratch_o,     \
+  err = launch_dependent_cluster(8, cluster, attention_decode_mma_kernel<DV>, grid, dim3(kMmaDecodeWarps * 32), shared, \
+                         stream, (const __nv_bfloat16*)q, q_row_stride, (__nv_bfloat16*)out, out_row_stride, scratch_o, \
                          scratch_ml, positions, token_seq, seq_seat, block_table, table_width,                     \
                          (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, num_heads, group, chunks,   \
-                         num_kv_heads, page_size, page_shift, num_pages, window, scale_log2, error)
+                         num_kv_heads, page_size, page_shift, num_pages, window, scale_log2, cluster_merge, error)
   if (head_dim == 64) DISTIE_MMA_DECODE(64);
   else DISTIE_MMA_DECODE(128);
 #undef DISTIE_MMA_DECODE
   if (err != cudaSuccess) return (int)err;
-  if (num_splits > 1) {
+  if (num_splits > 1 && !cluster_merge) {
     const dim3 merge_grid(tokens, num_heads);
     err = launch_dependent_family(8, attention_decode_mma_merge_kernel, merge_grid, dim3(head_dim >= 128 ? 128 : 64), 0, stream,
                            (const float*)scratch_o, (const float*)scratch_ml, (__nv_bfloat16*)out, out_row_stride,

@@ -166,9 +166,26 @@ __device__ __forceinline__ void store4(__nv_bfloat16* p, float4 v) {
   *reinterpret_cast<uint2*>(p) = raw;
 }
 
+// ---- thread-block clusters: barrier and reads of another CTA's shared memory -----------------------------------
+__device__ __forceinline__ void cluster_barrier() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// The float at `local` (an address in this CTA's shared memory) as CTA `rank` of the cluster holds it.
+__device__ __forceinline__ float cluster_load(const float* local, uint32_t rank) {
+  uint32_t remote;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"((uint32_t)__cvta_generic_to_shared(local)), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+  return v;
+}
+
+// A launch that may start before the kernel ahead of it in the stream has finished (the kernel calls
+// grid_dependency_wait() before it touches what that kernel writes), optionally as thread-block
+// clusters of `cluster` CTAs (cluster.x == 0: no clusters).
 template <typename... Params, typename... Args>
-inline cudaError_t launch_dependent_family(int family, void (*kernel)(Params...), dim3 grid, dim3 block, size_t shared,
-                                           cudaStream_t stream, Args... args) {
+inline cudaError_t launch_dependent_cluster(int family, dim3 cluster, void (*kernel)(Params...), dim3 grid, dim3 block,
+                                            size_t shared, cudaStream_t stream, Args... args) {
   cudaLaunchConfig_t config = {};
   config.gridDim = grid;
   config.blockDim = block;
@@ -180,12 +197,25 @@ inline cudaError_t launch_dependent_family(int family, void (*kernel)(Params...)
     return flag == nullptr ? 0xff : atoi(flag);
   }();
   const bool enabled = (mask & family) != 0;
-  cudaLaunchAttribute attribute[1];
+  cudaLaunchAttribute attribute[2];
   attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attribute[0].val.programmaticStreamSerializationAllowed = enabled ? 1 : 0;
   config.attrs = attribute;
   config.numAttrs = 1;
+  if (cluster.x > 0) {
+    attribute[1].id = cudaLaunchAttributeClusterDimension;
+    attribute[1].val.clusterDim.x = cluster.x;
+    attribute[1].val.clusterDim.y = cluster.y;
+    attribute[1].val.clusterDim.z = cluster.z;
+    config.numAttrs = 2;
+  }
   return cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
+}
+
+template <typename... Params, typename... Args>
+inline cudaError_t launch_dependent_family(int family, void (*kernel)(Params...), dim3 grid, dim3 block, size_t shared,
+                                           cudaStream_t stream, Args... args) {
+  return launch_dependent_cluster(family, dim3(0, 0, 0), kernel, grid, block, shared, stream, args...);
 }
 
 template <typename... Params, typename... Args>

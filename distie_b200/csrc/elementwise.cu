@@ -75,12 +75,12 @@ __global__ void add_rmsnorm_kernel(const T* __restrict__ delta, float* __restric
 // per loop iteration) and keeps the summed residual in registers for the second pass.
 // `delta` may also be the float32 partial sums of a product whose K was split over several CTAs:
 // `splits` slices, `split_stride` elements apart, which are added up here in a fixed order.
-template <typename T, typename DT>
+template <typename T, typename DT, int VPT>
 __global__ void __launch_bounds__(512) add_rmsnorm_vec_kernel(const DT* __restrict__ delta, int splits, size_t split_stride,
                                        float* __restrict__ residual, const float* __restrict__ weight,
                                        T* __restrict__ out, const int* __restrict__ rows_index, int hidden,
                                        float eps) {
-  constexpr int VPT = 4;
+  constexpr int ROUND = 16 / VPT;  // slices whose loads are in flight together
   __shared__ float scratch[32];
   const int out_row = blockIdx.x;
   const int row = rows_index ? rows_index[out_row] : out_row;
@@ -103,11 +103,11 @@ __global__ void __launch_bounds__(512) add_rmsnorm_vec_kernel(const DT* __restri
     v[i] = ch < chunks ? load4(res + 4 * ch) : make_float4(0.f, 0.f, 0.f, 0.f);
   }
   if (del) {
-    // Four slices per round, all their loads issued before any sum: one round trip for up to four.
-    for (int sp0 = 0; sp0 < splits; sp0 += 4) {
-      float4 d[4][VPT];
+    // ROUND slices per round, all their loads issued before any sum: one round trip for a whole round.
+    for (int sp0 = 0; sp0 < splits; sp0 += ROUND) {
+      float4 d[ROUND][VPT];
 #pragma unroll
-      for (int u = 0; u < 4; ++u)
+      for (int u = 0; u < ROUND; ++u)
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
           const int ch = threadIdx.x + i * blockDim.x;
@@ -115,7 +115,7 @@ __global__ void __launch_bounds__(512) add_rmsnorm_vec_kernel(const DT* __restri
                                                       : make_float4(0.f, 0.f, 0.f, 0.f);
         }
 #pragma unroll
-      for (int u = 0; u < 4; ++u)  // fixed order: slice 0 first
+      for (int u = 0; u < ROUND; ++u)  // fixed order: slice 0 first
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
           v[i].x += d[u][i].x; v[i].y += d[u][i].y; v[i].z += d[u][i].z; v[i].w += d[u][i].w;
@@ -142,6 +142,25 @@ __global__ void __launch_bounds__(512) add_rmsnorm_vec_kernel(const DT* __restri
     y.w = wv[i].w * to_float(from_float<T>(v[i].w * rstd));
     store4(dst + 4 * ch, y);
   }
+}
+
+// Threads and elements per thread for a row of `hidden` (a multiple of 4, at most 8192): as few
+// elements per thread as 512 threads allow, so that a short batch still has many loads in flight.
+template <typename T, typename DT>
+static cudaError_t launch_add_rmsnorm_vec(const DT* delta, int splits, size_t split_stride, float* residual,
+                                          const float* weight, T* out, const int* rows_index, int rows, int hidden,
+                                          float eps, cudaStream_t stream) {
+  const int chunks = hidden >> 2;
+  const int vpt = chunks <= 512 ? 1 : (chunks <= 1024 ? 2 : 4);
+  const int threads = (((chunks + vpt - 1) / vpt) + 31) & ~31;
+  if (vpt == 1)
+    return launch_dependent_family(2, add_rmsnorm_vec_kernel<T, DT, 1>, dim3(rows), dim3(threads), 0, stream, delta, splits,
+                                   split_stride, residual, weight, out, rows_index, hidden, eps);
+  if (vpt == 2)
+    return launch_dependent_family(2, add_rmsnorm_vec_kernel<T, DT, 2>, dim3(rows), dim3(threads), 0, stream, delta, splits,
+                                   split_stride, residual, weight, out, rows_index, hidden, eps);
+  return launch_dependent_family(2, add_rmsnorm_vec_kernel<T, DT, 4>, dim3(rows), dim3(threads), 0, stream, delta, splits,
+                                 split_stride, residual, weight, out, rows_index, hidden, eps);
 }
 
 // ---------------------------------------------------------------------------
@@ -237,7 +256,7 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict_
 }
 
 // The common case (rotate-half over the whole head, head_dim a multiple of 16, rows aligned to
-// 16 bytes) in pieces of 8 elements: a thread loads the 8 low and the 8 matching high elements of
+// 16 bytes) in pieces of 4 elements: a thread loads the 4 low and the 4 matching high elements of
 // one head, rotates them and stores them (q in place, k to its page); the values are copied in
 // pieces of 8.  All loads of a thread come before its stores.
 // The input may be the product itself (QT = T; q is then rotated in place when q_out is the input)
@@ -284,57 +303,62 @@ __global__ void rope_kv_write_vec_kernel(const QT* in, int splits, size_t split_
   __syncthreads();
   grid_dependency_wait();
   const size_t cache_head_stride = (size_t)page_size * head_dim;
-  const int pieces = half >> 3;  // pieces of 8 pairs per head
+  const int pieces = half >> 2;  // pieces of 4 pairs per head
   const int rot_units = (num_heads + (write_cache ? num_kv_heads : 0)) * pieces;
   const int v_units = write_cache ? num_kv_heads * (head_dim >> 3) : 0;
-  // Eight elements of the input row at `offset`, summed over the splits, plus the bias.
-  auto gather8 = [&](int offset, float (&dst)[8]) {
-    float b[8];
+  // Two pieces of 4 elements of the input row, each summed over the splits in slice order, plus the
+  // bias.  The loads of up to eight slices are issued before any sum: one round trip for all of them.
+  constexpr int ROUND = 8;
+  auto gather = [&](int first, int second, float4& a, float4& b) {
+    a = make_float4(0.f, 0.f, 0.f, 0.f);
+    b = a;
+    for (int sp0 = 0; sp0 < splits; sp0 += ROUND) {
+      float4 da[ROUND], db[ROUND];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) b[i] = 0.f;
-    if (bias) load8(bias + offset, b);
-    load8_cg(row + offset, dst);
-    for (int sp0 = 1; sp0 < splits; sp0 += 3) {  // up to three more slices per round, loads first
-      float more[3][8];
-#pragma unroll
-      for (int u = 0; u < 3; ++u) {
+      for (int u = 0; u < ROUND; ++u) {
         if (sp0 + u < splits) {
-          load8_cg(row + (sp0 + u) * split_stride + offset, more[u]);
+          const QT* slice = row + (sp0 + u) * split_stride;
+          da[u] = load4_cg(slice + first);
+          db[u] = load4_cg(slice + second);
         } else {
-#pragma unroll
-          for (int i = 0; i < 8; ++i) more[u][i] = 0.f;
+          da[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+          db[u] = da[u];
         }
       }
 #pragma unroll
-      for (int u = 0; u < 3; ++u)
-#pragma unroll
-        for (int i = 0; i < 8; ++i) dst[i] += more[u][i];
+      for (int u = 0; u < ROUND; ++u) {
+        a.x += da[u].x; a.y += da[u].y; a.z += da[u].z; a.w += da[u].w;
+        b.x += db[u].x; b.y += db[u].y; b.z += db[u].z; b.w += db[u].w;
+      }
     }
-#pragma unroll
-    for (int i = 0; i < 8; ++i) dst[i] += b[i];
+    if (bias) {
+      const float4 ba = load4(bias + first), bb = load4(bias + second);
+      a.x += ba.x; a.y += ba.y; a.z += ba.z; a.w += ba.w;
+      b.x += bb.x; b.y += bb.y; b.z += bb.z; b.w += bb.w;
+    }
   };
   for (int unit = threadIdx.x; unit < rot_units + v_units; unit += blockDim.x) {
     if (unit < rot_units) {
-      const int head = unit / pieces, j0 = (unit % pieces) * 8;
-      float lo[8], hi[8], out_lo[8], out_hi[8];
-      gather8(head * head_dim + j0, lo);
-      gather8(head * head_dim + half + j0, hi);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float c = trig[j0 + i], s = trig[half + j0 + i];
-        out_lo[i] = lo[i] * c - hi[i] * s;
-        out_hi[i] = hi[i] * c + lo[i] * s;
-      }
+      const int head = unit / pieces, j0 = (unit % pieces) * 4;
+      float4 lo, hi;
+      gather(head * head_dim + j0, head * head_dim + half + j0, lo, hi);
+      const float4 c = *reinterpret_cast<const float4*>(trig + j0), sn = *reinterpret_cast<const float4*>(trig + half + j0);
+      const float4 out_lo = make_float4(lo.x * c.x - hi.x * sn.x, lo.y * c.y - hi.y * sn.y, lo.z * c.z - hi.z * sn.z,
+                                        lo.w * c.w - hi.w * sn.w);
+      const float4 out_hi = make_float4(hi.x * c.x + lo.x * sn.x, hi.y * c.y + lo.y * sn.y, hi.z * c.z + lo.z * sn.z,
+                                        hi.w * c.w + lo.w * sn.w);
       T* dst = head < num_heads ? q_out + (size_t)t * q_out_stride + (size_t)head * head_dim
                                 : k_dst + (size_t)(head - num_heads) * cache_head_stride;
-      store8(dst + j0, out_lo);
-      store8(dst + half + j0, out_hi);
+      store4(dst + j0, out_lo);
+      store4(dst + half + j0, out_hi);
     } else {
       const int piece = unit - rot_units;
       const int head = piece / (head_dim >> 3), j0 = (piece % (head_dim >> 3)) * 8;
-      float v[8];
-      gather8((num_heads + num_kv_heads + head) * head_dim + j0, v);
-      store8(v_dst + (size_t)head * cache_head_stride + j0, v);
+      float4 first, second;
+      const int offset = (num_heads + num_kv_heads + head) * head_dim + j0;
+      gather(offset, offset + 4, first, second);
+      store4(v_dst + (size_t)head * cache_head_stride + j0, first);
+      store4(v_dst + (size_t)head * cache_head_stride + j0 + 4, second);
     }
   }
 }
@@ -408,16 +432,13 @@ extern "C" int distie_add_rmsnorm(const void* delta, float* residual, const floa
   if (dtype != DISTIE_BF16 && dtype != DISTIE_F32) return DISTIE_ERR_UNSUPPORTED;
   const bool aligned = (((uintptr_t)delta | (uintptr_t)residual | (uintptr_t)weight | (uintptr_t)out) & 15) == 0;
   if ((hidden & 3) == 0 && hidden <= 16 * 512 && aligned) {
-    int threads = 128;
-    while (threads * 16 < hidden) threads *= 2;
     cudaError_t err;
     if (dtype == DISTIE_BF16)
-      err = launch_dependent_family(2, add_rmsnorm_vec_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(rows), dim3(threads), 0, stream,
-                             (const __nv_bfloat16*)delta, 1, (size_t)0, residual, weight, (__nv_bfloat16*)out,
-                             rows_index, hidden, eps);
+      err = launch_add_rmsnorm_vec((const __nv_bfloat16*)delta, 1, (size_t)0, residual, weight, (__nv_bfloat16*)out,
+                                   rows_index, rows, hidden, eps, stream);
     else
-      err = launch_dependent_family(2, add_rmsnorm_vec_kernel<float, float>, dim3(rows), dim3(threads), 0, stream,
-                             (const float*)delta, 1, (size_t)0, residual, weight, (float*)out, rows_index, hidden, eps);
+      err = launch_add_rmsnorm_vec((const float*)delta, 1, (size_t)0, residual, weight, (float*)out, rows_index, rows,
+                                   hidden, eps, stream);
     return err == cudaSuccess ? 0 : (int)err;
   }
   const int threads = hidden >= 4096 ? 512 : (hidden >= 1024 ? 256 : 128);
@@ -444,9 +465,8 @@ extern "C" int distie_rope_kv_write(void* qkv, const int* positions, const int* 
   const bool aligned = (((uintptr_t)qkv | (uintptr_t)k_cache | (uintptr_t)v_cache) & 31) == 0;
   if ((inv_freq == nullptr || rotary_dim == head_dim) && !interleaved && (head_dim & 15) == 0 &&
       (row_stride & 7) == 0 && aligned) {
-    const int units = (num_heads + num_kv_heads) * (head_dim >> 4) + num_kv_heads * (head_dim >> 3);
-    int threads = 64;
-    while (threads < units && threads < 256) threads *= 2;
+    const int units = (num_heads + num_kv_heads) * (head_dim >> 3) + num_kv_heads * (head_dim >> 3);
+    const int threads = units >= 512 ? 512 : ((units + 31) & ~31);
     const size_t bytes = (size_t)head_dim * sizeof(float);
     if (dtype == DISTIE_BF16)
       rope_kv_write_vec_kernel<<<tokens, threads, bytes, stream>>>(
@@ -490,15 +510,13 @@ extern "C" int distie_add_rmsnorm_split(const float* partials, int splits, long 
   if (dtype != DISTIE_BF16 && dtype != DISTIE_F32) return DISTIE_ERR_UNSUPPORTED;
   const bool aligned = (((uintptr_t)partials | (uintptr_t)residual | (uintptr_t)weight | (uintptr_t)out) & 15) == 0;
   if ((hidden & 3) || hidden > 16 * 512 || !aligned || (split_stride & 3)) return DISTIE_ERR_UNSUPPORTED;
-  int threads = 128;
-  while (threads * 16 < hidden) threads *= 2;
   cudaError_t err;
   if (dtype == DISTIE_BF16)
-    err = launch_dependent_family(2, add_rmsnorm_vec_kernel<__nv_bfloat16, float>, dim3(rows), dim3(threads), 0, stream, partials,
-                           splits, (size_t)split_stride, residual, weight, (__nv_bfloat16*)out, rows_index, hidden, eps);
+    err = launch_add_rmsnorm_vec(partials, splits, (size_t)split_stride, residual, weight, (__nv_bfloat16*)out, rows_index,
+                                 rows, hidden, eps, stream);
   else
-    err = launch_dependent_family(2, add_rmsnorm_vec_kernel<float, float>, dim3(rows), dim3(threads), 0, stream, partials, splits,
-                           (size_t)split_stride, residual, weight, (float*)out, rows_index, hidden, eps);
+    err = launch_add_rmsnorm_vec(partials, splits, (size_t)split_stride, residual, weight, (float*)out, rows_index, rows,
+                                 hidden, eps, stream);
   return err == cudaSuccess ? 0 : (int)err;
 }
 
@@ -519,9 +537,8 @@ extern "C" int distie_rope_kv_write_split(const float* partials, int splits, lon
   if (!((inv_freq == nullptr || rotary_dim == head_dim) && !interleaved && (head_dim & 15) == 0 &&
         (row_stride & 7) == 0 && (q_out_stride & 7) == 0 && (split_stride & 7) == 0 && aligned))
     return DISTIE_ERR_UNSUPPORTED;
-  const int units = (num_heads + num_kv_heads) * (head_dim >> 4) + num_kv_heads * (head_dim >> 3);
-  int threads = 64;
-  while (threads < units && threads < 256) threads *= 2;
+  const int units = (num_heads + num_kv_heads) * (head_dim >> 3) + num_kv_heads * (head_dim >> 3);
+  const int threads = units >= 512 ? 512 : ((units + 31) & ~31);
   const size_t bytes = (size_t)head_dim * sizeof(float);
   cudaError_t err;
   if (dtype == DISTIE_BF16)

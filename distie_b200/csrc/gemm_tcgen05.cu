@@ -313,6 +313,193 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   if (threadIdx.x == 0 && sm.failed && error) atomicExch(error, 6);
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// The same machinery turned around for few rows of x (decoding): the weights are the 128-row operand and
+// stream through a deep ring of TMA stages (16 KB each), the rows of x are the narrow operand
+// (N = 16, 32 or 64), and the accumulator is D[weight row, row of x].  A product like this is bound by
+// reading W once; what it needs is many bytes in flight per SM, which the ring gives without spending
+// registers.  K may be split over gridDim.y CTAs: each then writes its float32 slice [M, N] and the
+// consumer adds the slices up.
+//
+//   EPI_SLICE   out is [splits, M, N] float32 (row stride N), no bias
+//   EPI_STORE   out is [M, N] bfloat16 or float32 with bias (one split)
+//   EPI_SWIGLU  W is [2 * inter, K]; a tile holds 64 gate rows and the 64 matching up rows; out[M, inter]
+//
+// Launched as a dependent kernel: the producer warp issues the first weight stages before it waits for
+// the kernel that writes x.
+// ---------------------------------------------------------------------------------------------------------------
+constexpr int SKINNY_EPI_SLICE = 0;
+constexpr int SKINNY_EPI_STORE = 1;
+constexpr int SKINNY_EPI_SWIGLU = 2;
+
+template <int BN, int STAGES>
+struct SkinnyShared {
+  alignas(1024) unsigned char w[STAGES][kGemmBM * kGemmBK * 2];
+  alignas(1024) unsigned char x[STAGES][BN * kGemmBK * 2];
+  float exchange[kGemmBM][BN + 1];  // SwiGLU: gate and up rows meet here
+  uint64_t full[STAGES];
+  uint64_t empty[STAGES];
+  uint64_t accum;
+  uint32_t tmem_base;
+  uint32_t failed;
+};
+
+__device__ __forceinline__ void tmem_load_16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+}
+
+template <int BN, int STAGES, int EPI, typename OutT>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tcgen05_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                           const float* __restrict__ bias, OutT* __restrict__ out, int ldo, int M, int N, int K,
+                           int inter, int* __restrict__ error) {
+  extern __shared__ unsigned char raw[];
+  auto& sm = *reinterpret_cast<SkinnyShared<BN, STAGES>*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
+  constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+  constexpr uint32_t W_BYTES = kGemmBM * kGemmBK * 2, X_BYTES = BN * kGemmBK * 2;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile = blockIdx.x, split = blockIdx.y, splits = gridDim.y;
+  const int k_blocks_all = (K + kGemmBK - 1) / kGemmBK;
+  const int per_split = (k_blocks_all + splits - 1) / splits;
+  const int kb_begin = split * per_split;
+  const int kb_end = min(k_blocks_all, kb_begin + per_split);
+  const int k_blocks = max(0, kb_end - kb_begin);
+  // Weight rows of the tile: [r0, r0 + 128), or with SwiGLU 64 gate rows and the 64 matching up rows.
+  const int r0 = EPI == SKINNY_EPI_SWIGLU ? tile * 64 : tile * kGemmBM;
+
+  grid_dependency_release();
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&sm.full[s], 1);
+      mbar_init(&sm.empty[s], 1);
+    }
+    mbar_init(&sm.accum, 1);
+    sm.failed = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)),
+                 "r"(TMEM_COLS));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = sm.tmem_base;
+
+  if (warp == 0) {
+    // ---- producer ----------------------------------------------------------------------------------------
+    if (lane == 0) {
+      auto load_w = [&](int kb, int s) {
+        const int k = (kb_begin + kb) * kGemmBK;
+        if (EPI == SKINNY_EPI_SWIGLU) {
+          tma_load_2d(sm.w[s], &map_w, &sm.full[s], k, r0);
+          tma_load_2d(sm.w[s] + 64 * kGemmBK * 2, &map_w, &sm.full[s], k, inter + r0);
+        } else {
+          tma_load_2d(sm.w[s], &map_w, &sm.full[s], k, r0);
+        }
+      };
+      // The weights are written by no kernel: the first ring of stages starts before the wait.
+      const int early = min(k_blocks, STAGES);
+      for (int kb = 0; kb < early; ++kb) {
+        mbar_expect_tx(&sm.full[kb], W_BYTES + X_BYTES);
+        load_w(kb, kb);
+      }
+      grid_dependency_wait();
+      for (int kb = 0; kb < early; ++kb) tma_load_2d(sm.x[kb], &map_x, &sm.full[kb], (kb_begin + kb) * kGemmBK, 0);
+      int issued = early;
+      for (int kb = early; kb < k_blocks; ++kb) {
+        const int s = kb % STAGES;
+        if (!mbar_wait(&sm.empty[s], ((kb / STAGES) & 1) ^ 1)) { atomicExch(&sm.failed, 1u); break; }
+        mbar_expect_tx(&sm.full[s], W_BYTES + X_BYTES);
+        load_w(kb, s);
+        tma_load_2d(sm.x[s], &map_x, &sm.full[s], (kb_begin + kb) * kGemmBK, 0);
+        issued = kb + 1;
+      }
+      if (sm.failed) {
+        for (int kb = max(0, issued - STAGES); kb < issued; ++kb) mbar_wait(&sm.full[kb % STAGES], (kb / STAGES) & 1);
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer ----------------------------------------------------------------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = instr_desc(BN);
+      for (int kb = 0; kb < k_blocks; ++kb) {
+        const int s = kb % STAGES;
+        if (!mbar_wait(&sm.full[s], (kb / STAGES) & 1)) { atomicExch(&sm.failed, 1u); break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint64_t a_desc = smem_desc(sm.w[s]), b_desc = smem_desc(sm.x[s]);
+#pragma unroll
+        for (int k = 0; k < kGemmBK / 16; ++k)
+          umma_bf16(tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+        umma_commit(&sm.empty[s]);
+      }
+      umma_commit(&sm.accum);
+    }
+  } else {
+    // ---- epilogue: lane = weight row of the tile, columns = rows of x --------------------------------------
+    grid_dependency_wait();  // nothing is written before the earlier kernels are done
+    const bool ready = mbar_wait(&sm.accum, 0);
+    if (!ready) atomicExch(&sm.failed, 1u);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const int quadrant = warp & 3;
+    const int local_row = quadrant * 32 + lane;
+    const uint32_t lane_base = tmem + ((uint32_t)(quadrant * 32) << 16);
+    float acc[BN];
+    if (ready && !sm.failed && k_blocks > 0) {
+#pragma unroll
+      for (int c0 = 0; c0 < BN; c0 += 16) {
+        uint32_t v[16];
+        tmem_load_16(lane_base + c0, v);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+        for (int j = 0; j < 16; ++j) acc[c0 + j] = __uint_as_float(v[j]);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < BN; ++j) acc[j] = 0.f;
+    }
+    if (EPI == SKINNY_EPI_SWIGLU) {
+#pragma unroll
+      for (int j = 0; j < BN; ++j) sm.exchange[local_row][j] = acc[j];
+      asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps only
+      if (local_row < 64) {
+        const int col = r0 + local_row;
+        if (col < inter) {
+#pragma unroll
+          for (int j = 0; j < BN; ++j) {
+            if (j < M) {
+              const float g = sm.exchange[local_row][j], u = sm.exchange[64 + local_row][j];
+              out[(size_t)j * ldo + col] = from_float<OutT>(g / (1.f + __expf(-g)) * u);
+            }
+          }
+        }
+      }
+    } else {
+      const int row = r0 + local_row;
+      if (row < N) {
+        OutT* dst = out + (EPI == SKINNY_EPI_SLICE ? (size_t)split * M * ldo : 0) + row;
+        const float b = (EPI == SKINNY_EPI_STORE && bias) ? bias[row] : 0.f;
+#pragma unroll
+        for (int j = 0; j < BN; ++j)
+          if (j < M) dst[(size_t)j * ldo] = from_float<OutT>(acc[j] + b);
+      }
+    }
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS));
+  }
+  if (threadIdx.x == 0 && sm.failed && error) atomicExch(error, 6);
+}
+
 // ---- host side ---------------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -416,4 +603,88 @@ extern "C" int distie_gemm_tcgen05(const void* x, int ldx, const void* w, void* 
   if (width == 192) { DISTIE_GEMM(192, 5); }
   DISTIE_GEMM(128, 6);
 #undef DISTIE_GEMM
+}
+
+// ---- few rows of x: the weight-streaming orientation ------------------------------------------------------------
+namespace distie {
+
+static int skinny_splits(int tiles, int K, int sm_count) {
+  const int k_blocks = (K + kGemmBK - 1) / kGemmBK;
+  int splits = sm_count / tiles;                 // one CTA per SM at most: a second wave would wait for the first
+  splits = min(splits, max(1, k_blocks / 2));    // at least two K blocks per CTA
+  return max(1, min(splits, 8));                 // the consumers sum up to eight slices in one round of loads
+}
+
+template <int BN, int STAGES, int EPI, typename OutT>
+static int launch_skinny_tc(const CUtensorMap& map_w, const CUtensorMap& map_x, const float* bias, OutT* out, int ldo,
+                            int M, int N, int K, int inter, int tiles, int splits, int* error, cudaStream_t stream) {
+  const size_t shared = sizeof(SkinnyShared<BN, STAGES>) + 1024;
+  static bool configured = false;
+  if (!configured) {
+    const cudaError_t err = cudaFuncSetAttribute(gemm_tcgen05_skinny_kernel<BN, STAGES, EPI, OutT>,
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+    if (err != cudaSuccess) return (int)err;
+    configured = true;
+  }
+  const cudaError_t err =
+      launch_dependent_family(16, gemm_tcgen05_skinny_kernel<BN, STAGES, EPI, OutT>, dim3(tiles, splits),
+                              dim3(kGemmThreads), shared, stream, map_w, map_x, bias, out, ldo, M, N, K, inter, error);
+  return err == cudaSuccess ? 0 : (int)err;
+}
+
+template <int EPI, typename OutT>
+static int dispatch_skinny_tc(const CUtensorMap& map_w, const void* x, int ldx, const float* bias, OutT* out, int ldo,
+                              int M, int N, int K, int inter, int tiles, int splits, int* error, cudaStream_t stream) {
+  CUtensorMap map_x;
+  int status;
+  if (M <= 16) {
+    if ((status = make_map(&map_x, x, M, K, ldx, 16)) != 0) return status;
+    return launch_skinny_tc<16, 10, EPI, OutT>(map_w, map_x, bias, out, ldo, M, N, K, inter, tiles, splits, error, stream);
+  }
+  if (M <= 32) {
+    if ((status = make_map(&map_x, x, M, K, ldx, 32)) != 0) return status;
+    return launch_skinny_tc<32, 9, EPI, OutT>(map_w, map_x, bias, out, ldo, M, N, K, inter, tiles, splits, error, stream);
+  }
+  if ((status = make_map(&map_x, x, M, K, ldx, 64)) != 0) return status;
+  return launch_skinny_tc<64, 7, EPI, OutT>(map_w, map_x, bias, out, ldo, M, N, K, inter, tiles, splits, error, stream);
+}
+
+}  // namespace distie
+
+// Slices the call below writes for these sizes (mode 0).
+extern "C" int distie_gemm_tcgen05_skinny_splits(int N, int K, int sm_count) {
+  return skinny_splits((N + kGemmBM - 1) / kGemmBM, K, sm_count < 1 ? 148 : sm_count);
+}
+
+// x[M <= 64, K] (bfloat16, row stride ldx) against w[N, K] (bfloat16, contiguous).
+//   mode 0: out[splits, M, N] float32 slices (ldo = N); their sum is x w^T
+//   mode 1: out[M, N] bfloat16 (out_dtype 1) or float32 (0) = x w^T + bias
+//   mode 2: w is [2 * inter, K]; out[M, inter] bfloat16 = silu(x Wg^T) * (x Wu^T)
+extern "C" int distie_gemm_tcgen05_skinny(const void* x, int ldx, const void* w, const float* bias, void* out, int ldo,
+                                          int M, int N, int K, int mode, int out_dtype, int sm_count, int* error,
+                                          cudaStream_t stream) {
+  if (M <= 0) return 0;
+  if (M > 64 || N < 1 || K < 8 || (K & 7) || (ldx & 7) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15))
+    return DISTIE_ERR_UNSUPPORTED;
+  if (sm_count < 1) sm_count = 148;
+  CUtensorMap map_w;
+  int status;
+  if (mode == 2) {
+    if (N & 1) return DISTIE_ERR_ARG;
+    const int inter = N / 2;
+    if ((status = make_map(&map_w, w, N, K, K, 64)) != 0) return status;
+    return dispatch_skinny_tc<SKINNY_EPI_SWIGLU, __nv_bfloat16>(map_w, x, ldx, nullptr, (__nv_bfloat16*)out, ldo, M, N, K,
+                                                                 inter, (inter + 63) / 64, 1, error, stream);
+  }
+  if ((status = make_map(&map_w, w, N, K, K, kGemmBM)) != 0) return status;
+  const int tiles = (N + kGemmBM - 1) / kGemmBM;
+  if (mode == 0)
+    return dispatch_skinny_tc<SKINNY_EPI_SLICE, float>(map_w, x, ldx, nullptr, (float*)out, N, M, N, K, 0, tiles,
+                                                       skinny_splits(tiles, K, sm_count), error, stream);
+  if (mode != 1) return DISTIE_ERR_ARG;
+  if (out_dtype == DISTIE_F32)
+    return dispatch_skinny_tc<SKINNY_EPI_STORE, float>(map_w, x, ldx, bias, (float*)out, ldo, M, N, K, 0, tiles, 1, error,
+                                                       stream);
+  return dispatch_skinny_tc<SKINNY_EPI_STORE, __nv_bfloat16>(map_w, x, ldx, bias, (__nv_bfloat16*)out, ldo, M, N, K, 0,
+                                                             tiles, 1, error, stream);
 }

@@ -24,7 +24,8 @@ from .library import KernelError, check, function
 _CODE = {torch.float32: 0, torch.bfloat16: 1}
 _DECODE_HEAD_DIMS = (16, 32, 64, 128, 256)
 _PREFILL_HEAD_DIMS = (64, 128)  # tensor-core attention for portions of prompts (bfloat16)
-_SKINNY_ROWS = 16               # weight-streaming products take up to this many rows of x
+_SKINNY_ROWS = 64               # weight-streaming products (tcgen05, weights as the 128-row operand) take up to 64 rows
+_CLUSTER_SPLITS = 8             # splits of a decode attention that one cluster of CTAs merges itself
 _TENSOR_CORE_ROWS = 128         # from here on the tcgen05 kernel's 128-row tiles are full; in between: the library
 
 _ERROR_TEXT = {
@@ -119,15 +120,9 @@ class DeviceKernels(KernelSet):
     def linear_split(self, x, weight):
         if self._skinny(x, weight):
             m, n, k = x.shape[0], weight.shape[0], weight.shape[1]
-            splits = function("distie_linear_skinny_splits")(m, n, k, self.sm_count)
+            splits = function("distie_gemm_tcgen05_skinny_splits")(n, k, self.sm_count)
             out = torch.empty((splits, m, n), dtype=torch.float32, device=x.device)
-            check(
-                function("distie_linear_skinny_partial")(
-                    x.data_ptr(), x.stride(0), weight.data_ptr(), out.data_ptr(), m, n, k, self.sm_count, self._stream()
-                ),
-                "linear_skinny_partial",
-            )
-            self.launches += 1
+            self._stream_weights(x, weight, None, out, 0)
             return out
         return super().linear_split(x, weight)
 
@@ -140,7 +135,7 @@ class DeviceKernels(KernelSet):
             return y if out_dtype == torch.float32 else self._bias_cast(y, None, out_dtype)
         if self._skinny(x, weight):
             out = torch.empty((x.shape[0], weight.shape[0]), dtype=out_dtype, device=x.device)
-            self._linear_skinny(x, weight, bias, out, 0)
+            self._stream_weights(x, weight, bias, out, 1)
             return out
         if self._tensor_core(x, weight) and (bias is None or out_dtype == torch.float32):
             out = torch.empty((x.shape[0], weight.shape[0]), dtype=out_dtype, device=x.device)
@@ -175,7 +170,20 @@ class DeviceKernels(KernelSet):
         return (
             self.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.dtype == torch.bfloat16
             and x.shape[0] <= _SKINNY_ROWS and weight.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and x.stride(1) == 1
+            and weight.is_contiguous()
         )
+
+    def _stream_weights(self, x, weight, bias, out, mode: int) -> None:
+        """mode 0: float32 slices; 1: x W^T + bias; 2: fused SwiGLU (see gemm_tcgen05.cu)."""
+        check(
+            function("distie_gemm_tcgen05_skinny")(
+                x.data_ptr(), x.stride(0), weight.data_ptr(), bias.data_ptr() if bias is not None else None,
+                out.data_ptr(), out.stride(-2), x.shape[0], weight.shape[0], weight.shape[1], mode,
+                _CODE.get(out.dtype, 0), self.sm_count, self.error_flag.data_ptr(), self._stream(),
+            ),
+            "gemm_tcgen05_skinny",
+        )
+        self.launches += 1
 
     def _linear_skinny(self, x, weight, bias, out, swiglu: int) -> None:
         check(
@@ -189,9 +197,9 @@ class DeviceKernels(KernelSet):
         self.launches += 1
 
     def linear_swiglu(self, x, weight):
-        if self._skinny(x, weight):
+        if self._skinny(x, weight) and weight.shape[0] % 2 == 0:
             out = torch.empty((x.shape[0], weight.shape[0] // 2), dtype=self.dtype, device=x.device)
-            self._linear_skinny(x, weight, None, out, 1)
+            self._stream_weights(x, weight, None, out, 2)
             return out
         if self._tensor_core(x, weight) and weight.shape[0] % 2 == 0:
             out = torch.empty((x.shape[0], weight.shape[0] // 2), dtype=self.dtype, device=x.device)
@@ -279,8 +287,12 @@ class DeviceKernels(KernelSet):
         element = qkv.element_size()
         if n_dec > 0:
             splits = self.plan_splits(n_dec, num_heads, num_kv_heads, step.max_kv_len)
+            tensor_cores = self.dtype == torch.bfloat16 and head_dim in _PREFILL_HEAD_DIMS
+            if tensor_cores and splits <= 2 * _CLUSTER_SPLITS:
+                splits = min(splits, _CLUSTER_SPLITS)  # merged inside the kernel, by a cluster of CTAs
+            in_kernel_merge = splits == 1 or (tensor_cores and splits <= _CLUSTER_SPLITS)
             scratch = None
-            if splits > 1:
+            if not in_kernel_merge:
                 floats = function("distie_attention_decode_scratch_floats")(n_dec, num_heads, head_dim, splits)
                 scratch = torch.empty(floats, dtype=torch.float32, device=qkv.device)
             head = [
@@ -290,7 +302,7 @@ class DeviceKernels(KernelSet):
                 kv.block_table.shape[-1], kv.k.data_ptr(), kv.v.data_ptr(), n_dec, num_heads, num_kv_heads,
                 head_dim, kv.page_size, kv.num_pages, window, float(scale), splits,
             ]
-            if self.dtype == torch.bfloat16 and head_dim in _PREFILL_HEAD_DIMS:
+            if tensor_cores:
                 check(
                     function("distie_attention_decode_mma")(*head, self.error_flag.data_ptr(), self._stream()),
                     "attention_decode_mma",
@@ -300,7 +312,7 @@ class DeviceKernels(KernelSet):
                     function("distie_attention_decode")(*head, self.code, self.error_flag.data_ptr(), self._stream()),
                     "attention_decode",
                 )
-            self.launches += 1 if splits == 1 else 2
+            self.launches += 1 if in_kernel_merge else 2
         rest = step.num_tokens - n_dec
         if rest > 0 and self.dtype == torch.bfloat16 and head_dim in _PREFILL_HEAD_DIMS and step.num_q_tiles and n_dec == step.num_decode_tokens:
             check(

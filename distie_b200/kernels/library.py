@@ -37,6 +37,8 @@ _SIGNATURES: dict[str, tuple[str, list]] = {
     "distie_attention_prefill_tile": ("bf16", []),
     "distie_attention_decode_mma": ("bf16", [P, I, P, I, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, F, I, P, P]),
     "distie_gemm_tcgen05": ("bf16", [P, I, P, P, I, I, I, I, I, I, P, P]),
+    "distie_gemm_tcgen05_skinny_splits": ("bf16", [I, I, I]),
+    "distie_gemm_tcgen05_skinny": ("bf16", [P, I, P, P, P, I, I, I, I, I, I, I, P, P]),
     "distie_linear_skinny": ("bf16", [P, I, P, P, P, I, I, I, I, I, I, P, L, I, P]),
     "distie_linear_skinny_max_rows": ("bf16", []),
     "distie_linear_skinny_splits": ("bf16", [I, I, I, I]),

@@ -194,6 +194,35 @@ def test_tensor_core_product(kernel_sets, m, k, n):
         close(out, torch.nn.functional.silu(want[:, :inter]) * want[:, inter:], torch.bfloat16, "tcgen05 product with SwiGLU")
 
 
+@pytest.mark.parametrize(
+    "m,k,n", [(1, 64, 128), (8, 1536, 2048), (16, 200, 1000), (17, 96, 40), (3, 8960, 1536), (40, 1536, 264),
+              (64, 72, 130), (33, 4096, 512), (5, 8, 6)]
+)
+def test_weight_streaming_product(kernel_sets, m, k, n):
+    """The tcgen05 kernel for few rows alone: slices, stored result with bias, and SwiGLU, ragged everywhere."""
+    ks = kernel_sets[torch.bfloat16]
+    backing = torch.randn(m, k + 8, device="cuda").to(torch.bfloat16)
+    x = backing[:, :k]  # a row stride that is not K
+    w = (torch.randn(n, k, device="cuda") * 0.1).to(torch.bfloat16)
+    b = torch.randn(n, device="cuda")
+    want = torch.nn.functional.linear(x.double(), w.double())
+    slices = ks.linear_split(x, w)
+    ks.check_errors()
+    assert slices.dim() == 3 and slices.dtype == torch.float32
+    close(slices.sum(0), want, torch.float32, "weight streaming, slices")
+    for out_dtype in (torch.bfloat16, torch.float32):
+        out = torch.full((m, n), float("nan"), dtype=out_dtype, device="cuda")
+        ks._stream_weights(x, w, b, out, 1)
+        ks.check_errors()
+        close(out, want + b.double(), out_dtype, "weight streaming, stored with bias")
+    if n % 2 == 0:
+        inter = n // 2
+        out = torch.full((m, inter), float("nan"), dtype=torch.bfloat16, device="cuda")
+        ks._stream_weights(x, w, None, out, 2)
+        ks.check_errors()
+        close(out, torch.nn.functional.silu(want[:, :inter]) * want[:, inter:], torch.bfloat16, "weight streaming, SwiGLU")
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("m,k,inter", [(3, 96, 100), (8, 1536, 8960), (13, 200, 57), (40, 96, 224), (1, 64, 8)])
 def test_linear_swiglu(kernel_sets, dtype, m, k, inter):
@@ -283,6 +312,24 @@ def test_attention_mixed_batch(kernel_sets, dtype, heads, kv_heads, head_dim, pa
     ks.check_errors()
     want = ref.attention(qkv, step, kv, heads, kv_heads, head_dim, window, head_dim**-0.5)
     close(out, want, dtype, "attention")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("head_dim,heads,kv_heads", [(128, 12, 2), (64, 6, 1), (128, 40, 2)])
+@pytest.mark.parametrize("splits", [1, 2, 3, 8, 13, 17, 40])
+def test_decode_attention_at_every_split_count(kernel_sets, dtype, head_dim, heads, kv_heads, splits, monkeypatch):
+    """Single tokens with the keys cut into a given number of splits: merged by one CTA, by a cluster, by the merge kernel."""
+    ks = kernel_sets[dtype]
+    pasts = [699, 32, 1499, 0, 15]
+    kv = filled_cache_for(dtype, kv_heads, head_dim, 16, [p + 1 for p in pasts], seed=11)
+    step = step_of([1] * len(pasts), pasts, list(range(len(pasts))))
+    monkeypatch.setattr(ks, "plan_splits", lambda *args: splits)
+    qkv = torch.randn(step.num_tokens, (heads + 2 * kv_heads) * head_dim, device="cuda").to(dtype)
+    out = torch.zeros(step.num_tokens, heads * head_dim, dtype=dtype, device="cuda")
+    ks.attention(qkv, out, step, kv, heads, kv_heads, head_dim, None, head_dim**-0.5)
+    ks.check_errors()
+    want = ref.attention(qkv, step, kv, heads, kv_heads, head_dim, None, head_dim**-0.5)
+    close(out, want, dtype, f"decode attention in {splits} splits")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
