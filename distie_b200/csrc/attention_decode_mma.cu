@@ -35,6 +35,7 @@ namespace distie {
 constexpr int kMmaDecodeWarps = 4;
 constexpr int kMmaDecodeStages = 3;
 constexpr int kMmaDecodeClusterSplits = 8;  // splits that one cluster can hold (portable cluster size)
+constexpr int kMmaDecodePages = 1024;       // page ids of a split that are kept in shared memory
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
@@ -81,6 +82,7 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_row_strid
   float(*sh_o)[16][D + 1] = reinterpret_cast<float(*)[16][D + 1]>(dyn);
   __shared__ float sh_m[kMmaDecodeWarps][16], sh_l[kMmaDecodeWarps][16];
   __shared__ float cl_o[16][D], cl_m[16], cl_l[16];  // this split's result, read by the other CTAs of a cluster
+  __shared__ int sh_pages[kMmaDecodePages];           // the split's part of the block table
 
   grid_dependency_release();
   const int t = blockIdx.x;
@@ -98,8 +100,25 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_row_strid
   const int first_page = first / page_size;
   const int pages = pos / page_size - first_page + 1;
   const int pages_per_split = (pages + num_splits - 1) / num_splits;
-  const int lo = max(first, (first_page + split * pages_per_split) * page_size);
-  const int hi = min(pos, (first_page + (split + 1) * pages_per_split) * page_size - 1);
+  const int split_page = first_page + split * pages_per_split;
+  const int lo = max(first, split_page * page_size);
+  const int hi = min(pos, (split_page + pages_per_split) * page_size - 1);
+  // The split's page ids come into shared memory in one round of loads (requested here, stored after
+  // the first copies are on their way); a row of keys then costs no dependent global load before its
+  // copy can be issued.  Until they are there (`staged_ready`), the table itself is read.
+  constexpr int kStagedPerThread = kMmaDecodePages / (kMmaDecodeWarps * 32);
+  int staged[kStagedPerThread];
+#pragma unroll
+  for (int u = 0; u < kStagedPerThread; ++u) {
+    const int i = threadIdx.x + u * kMmaDecodeWarps * 32;
+    staged[u] = (i < pages_per_split && split_page + i < table_width) ? table[split_page + i] : -1;
+  }
+  bool staged_ready = false;
+  auto page_of = [&](int key) {
+    const int column = page_shift >= 0 ? key >> page_shift : key / page_size;
+    const int i = column - split_page;
+    return (staged_ready && i < kMmaDecodePages) ? sh_pages[i] : table[column];
+  };
 
   float o[NT][4];
 #pragma unroll
@@ -123,7 +142,7 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_row_strid
       size_t at = 0;
       if (ok) {
         // page_shift >= 0: the page size is a power of two, so no division per row.
-        const int page = table[page_shift >= 0 ? key >> page_shift : key / page_size];
+        const int page = page_of(key);
         const int within = page_shift >= 0 ? key & (page_size - 1) : key % page_size;
         if (page < 0 || page >= num_pages) {
           if (error) atomicExch(error, 4);
@@ -142,7 +161,7 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_row_strid
       bool ok = grp < groups && key >= lo && key <= hi;
       size_t at = 0;
       if (ok) {
-        const int page = table[page_shift >= 0 ? key >> page_shift : key / page_size];
+        const int page = page_of(key);
         const int within = page_shift >= 0 ? key & (page_size - 1) : key % page_size;
         if (page < 0 || page >= num_pages) {
           ok = false;
@@ -177,6 +196,10 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_row_strid
     qa[j] = g < heads_here ? load16_cg(base + (size_t)(head0 + g) * D) : zero;
     qb[j] = g + 8 < heads_here ? load16_cg(base + (size_t)(head0 + g + 8) * D) : zero;
   }
+#pragma unroll
+  for (int u = 0; u < kStagedPerThread; ++u) sh_pages[threadIdx.x + u * kMmaDecodeWarps * 32] = staged[u];
+  __syncthreads();
+  staged_ready = true;
   int stage = 0;
   for (int grp = warp; grp < groups; grp += kMmaDecodeWarps) {
     const int base_key = lo16 + grp * 16;

@@ -24,7 +24,7 @@ from .library import KernelError, check, function
 _CODE = {torch.float32: 0, torch.bfloat16: 1}
 _DECODE_HEAD_DIMS = (16, 32, 64, 128, 256)
 _PREFILL_HEAD_DIMS = (64, 128)  # tensor-core attention for portions of prompts (bfloat16)
-_SKINNY_ROWS = 64               # weight-streaming products (tcgen05, weights as the 128-row operand) take up to 64 rows
+_SKINNY_ROWS = 32               # weight-streaming products (tcgen05, weights as the 128-row operand) take up to 64 rows
 _CLUSTER_SPLITS = 8             # splits of a decode attention that one cluster of CTAs merges itself
 _TENSOR_CORE_ROWS = 128         # from here on the tcgen05 kernel's 128-row tiles are full; in between: the library
 
@@ -277,7 +277,7 @@ class DeviceKernels(KernelSet):
         group = num_heads // num_kv_heads
         chunks = (group + 7) // 8 if group > 8 else 1
         blocks = max(1, tokens * num_kv_heads * chunks)
-        by_machine = -(-2 * self.sm_count // blocks)
+        by_machine = max(1, 2 * self.sm_count // blocks)  # two CTAs fit an SM; a second wave would wait for the first
         by_length = max(1, max_kv_len // 256)
         return max(1, min(by_machine, by_length, 64))
 
