@@ -75,12 +75,16 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, 
   unsigned char* q_s = v_s + TILE_BYTES;              // the query tile borrows stage 1 of V: it is read into
                                                       // registers before the first load into that stage
 
-  // Tiles late in a request see the most keys and take longest: start them first.
-  const int tile = gridDim.x - 1 - blockIdx.x, head = blockIdx.y;
+  // Tiles late in a request see the most keys and take longest: start them first.  A tile of the list
+  // holds up to 2 * kTileM rows: two CTAs take its halves.
+  const int slot = gridDim.x - 1 - blockIdx.x, head = blockIdx.y;
+  const int tile = slot >> 1, half = slot & 1;
   const int kv_head = head / group_size;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, c = lane & 3;
-  const int t0 = q_tiles[2 * tile], rows = q_tiles[2 * tile + 1];
+  const int t0 = q_tiles[2 * tile] + half * kTileM;
+  const int rows = min(kTileM, q_tiles[2 * tile + 1] - half * kTileM);
+  if (rows <= 0) return;
   const int p0 = positions[t0];
   const int seat = seq_seat[token_seq[t0]];
   const int* table = block_table + (size_t)seat * table_width;
@@ -283,7 +287,7 @@ int launch_prefill(const void* q, int q_row_stride, void* out, int out_row_strid
   if ((page_size & (page_size - 1)) == 0)
     for (page_shift = 0; (1 << page_shift) < page_size; ++page_shift) {
     }
-  const dim3 grid(num_tiles, num_heads);
+  const dim3 grid(2 * num_tiles, num_heads);
   attention_prefill_kernel<D><<<grid, kPrefillWarps * 32, shared, stream>>>(
       (const __nv_bfloat16*)q, q_row_stride, (__nv_bfloat16*)out, out_row_stride, q_tiles, positions, token_seq,
       seq_seat, block_table, table_width, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
@@ -298,7 +302,7 @@ int launch_prefill(const void* q, int q_row_stride, void* out, int out_row_strid
 using namespace distie;
 
 // Tokens per tile of `q_tiles` ([num_tiles, 2] int32: first token of the tile, number of rows).
-extern "C" int distie_attention_prefill_tile(void) { return kTileM; }
+extern "C" int distie_attention_prefill_tile(void) { return 2 * kTileM; }
 
 extern "C" int distie_attention_prefill(const void* q, int q_row_stride, void* out, int out_row_stride,
                                         const int* q_tiles, int num_tiles, const int* positions,

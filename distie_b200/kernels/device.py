@@ -15,6 +15,8 @@ There is no CPU path here and no fallback: a missing library raises.
 
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import library
@@ -314,7 +316,10 @@ class DeviceKernels(KernelSet):
                 )
             self.launches += 1 if in_kernel_merge else 2
         rest = step.num_tokens - n_dec
-        if rest > 0 and self.dtype == torch.bfloat16 and head_dim in _PREFILL_HEAD_DIMS and step.num_q_tiles and n_dec == step.num_decode_tokens:
+        tiled = rest > 0 and self.dtype == torch.bfloat16 and head_dim in _PREFILL_HEAD_DIMS and step.num_q_tiles and n_dec == step.num_decode_tokens
+        if tiled and self._attention_tcgen05(qkv, out, step, kv, num_heads, num_kv_heads, head_dim, window, scale):
+            pass
+        elif tiled:
             check(
                 function("distie_attention_prefill")(
                     qkv.data_ptr(), qkv.stride(0), out.data_ptr(), out.stride(0), step.q_tiles.data_ptr(),
@@ -339,6 +344,23 @@ class DeviceKernels(KernelSet):
                 "attention_generic",
             )
             self.launches += 1
+
+    def _attention_tcgen05(self, qkv, out, step, kv, num_heads, num_kv_heads, head_dim, window, scale) -> bool:
+        """Prompt portions on the tcgen05 kernel; False when it refuses the page size or an alignment."""
+        if os.environ.get("DISTIE_PREFILL_ATTENTION") == "mma":
+            return False
+        code = function("distie_attention_prefill_tcgen05")(
+            qkv.data_ptr(), qkv.stride(0), out.data_ptr(), out.stride(0), step.q_tiles.data_ptr(), step.num_q_tiles,
+            step.positions.data_ptr(), step.token_seq.data_ptr(), step.seq_seat.data_ptr(),
+            kv.block_table.data_ptr(), kv.block_table.shape[-1], kv.k.data_ptr(), kv.v.data_ptr(), qkv.shape[0],
+            num_heads, num_kv_heads, head_dim, kv.page_size, kv.num_pages, window, float(scale),
+            self.error_flag.data_ptr(), self._stream(),
+        )
+        if code == -2:
+            return False
+        check(code, "attention_prefill_tcgen05")
+        self.launches += 1
+        return True
 
     def sample(self, logits, temperatures, uniforms, out_tokens) -> None:
         check(

@@ -24,7 +24,7 @@ from dataclasses import dataclass
 import torch
 
 
-Q_TILE = 64  # tokens per tile of StepTensors.q_tiles
+Q_TILE = 128  # tokens per tile of StepTensors.q_tiles
 
 
 @dataclass

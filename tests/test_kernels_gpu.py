@@ -28,7 +28,7 @@ def close(got, want, dtype, what=""):
 
 def step_of(tokens_per_seq, pasts, seats, device="cuda"):
     """StepTensors for a batch in which request i brings tokens_per_seq[i] tokens after pasts[i] cached ones."""
-    from distie_b200.kernels.interface import StepTensors
+    from distie_b200.kernels.interface import Q_TILE, StepTensors
 
     positions, token_seq = [], []
     order = sorted(range(len(tokens_per_seq)), key=lambda i: (tokens_per_seq[i] != 1, i))
@@ -41,7 +41,7 @@ def step_of(tokens_per_seq, pasts, seats, device="cuda"):
     for i in order:
         n = tokens_per_seq[i]
         if n > 1:
-            tiles += [(start + at, min(64, n - at)) for at in range(0, n, 64)]
+            tiles += [(start + at, min(Q_TILE, n - at)) for at in range(0, n, Q_TILE)]
         start += n
     step = StepTensors(
         token_ids=torch.zeros(total, dtype=torch.int32, device=device),
