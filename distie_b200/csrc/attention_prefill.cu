@@ -77,7 +77,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, 
 
   // Tiles late in a request see the most keys and take longest: start them first.  A tile of the list
   // holds up to 2 * kTileM rows: two CTAs take its halves.
-  const int slot = gridDim.x - 1 - blockIdx.x, head = blockIdx.y;
+  const int slot = gridDim.y - 1 - blockIdx.y, head = blockIdx.x;
   const int tile = slot >> 1, half = slot & 1;
   const int kv_head = head / group_size;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -287,7 +287,7 @@ int launch_prefill(const void* q, int q_row_stride, void* out, int out_row_strid
   if ((page_size & (page_size - 1)) == 0)
     for (page_shift = 0; (1 << page_shift) < page_size; ++page_shift) {
     }
-  const dim3 grid(2 * num_tiles, num_heads);
+  const dim3 grid(num_heads, 2 * num_tiles);
   attention_prefill_kernel<D><<<grid, kPrefillWarps * 32, shared, stream>>>(
       (const __nv_bfloat16*)q, q_row_stride, (__nv_bfloat16*)out, out_row_stride, q_tiles, positions, token_seq,
       seq_seat, block_table, table_width, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
@@ -312,7 +312,7 @@ extern "C" int distie_attention_prefill(const void* q, int q_row_stride, void* o
                                         float scale, int* error, cudaStream_t stream) {
   if (num_tiles <= 0) return 0;
   if (num_heads < 1 || num_kv_heads < 1 || num_heads % num_kv_heads != 0 || page_size < 1 || table_width < 1 ||
-      num_heads > 65535 || (q_row_stride & 7) || (out_row_stride & 1))
+      2 * num_tiles > 65535 || (q_row_stride & 7) || (out_row_stride & 1))
     return DISTIE_ERR_ARG;
 #define DISTIE_PREFILL(DV)                                                                                        \
   return launch_prefill<DV>(q, q_row_stride, out, out_row_stride, q_tiles, num_tiles, positions, token_seq,       \

@@ -83,6 +83,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem = sm.tmem_base;
+  // Launched as a dependent kernel: everything up to here overlaps the end of the kernel before this
+  // one; its results (the activations) are read, and anything is written, only after this wait.
+  grid_dependency_release();
+  grid_dependency_wait();
 
   if (warp == 0) {
     // ---- producer ----------------------------------------------------------------------------------------
@@ -426,10 +430,10 @@ static int launch_gemm(const CUtensorMap& map_a, const CUtensorMap& map_b, void*
   const int per_tile = EPI == GEMM_EPI_SWIGLU ? BN / 2 : BN;
   const int num_tiles = m_tiles * ((columns + per_tile - 1) / per_tile);
   const int grid = num_tiles < sm_count ? num_tiles : sm_count;
-  gemm_tcgen05_kernel<BN, STAGES, EPI><<<grid, kGemmThreads, shared, stream>>>(
-      map_a, map_b, out, ldo, M, N, K, inter, m_tiles, num_tiles, error);
-  DISTIE_LAUNCH_CHECK();
-  return 0;
+  const cudaError_t err =
+      launch_dependent_family(64, gemm_tcgen05_kernel<BN, STAGES, EPI>, dim3(grid), dim3(kGemmThreads), shared, stream,
+                              map_a, map_b, out, ldo, M, N, K, inter, m_tiles, num_tiles, error);
+  return err == cudaSuccess ? 0 : (int)err;
 }
 
 // Tile width (128, 192 or 256 columns): the one whose waves of `sm_count` tiles cost least.
