@@ -10,8 +10,8 @@
 //   warp 0      producer: waits for a free stage, arms its mbarrier with the byte count, issues the TMA loads
 //   warp 1      allocates tensor memory; one lane issues the MMAs of each stage as its barrier completes and
 //               commits them to the stage's "empty" barrier, at the end to the "accumulator ready" barrier
-//   warps 2..5  epilogue: warp w reads TMEM lanes 32 * (w % 4) .. + 31 (its rows of the tile), 32 columns at a
-//               time, and writes bfloat16, float32, or silu(gate) * up
+//   warps 2..9  epilogue: warps w and w + 4 read TMEM lanes 32 * (w % 4) .. + 31 (their rows of the tile), half
+//               of the columns each, 32 at a time, and write bfloat16, float32, or silu(gate) * up
 //
 // With the SwiGLU epilogue the weight is [2 * inter, K] (gate rows, then up rows) and a tile holds 128
 // gate rows and the 128 matching up rows (two TMA loads per stage), so gate and up of one output
@@ -27,13 +27,14 @@ namespace distie {
 
 constexpr int kGemmBM = 128;
 constexpr int kGemmBK = 64;
-constexpr int kGemmThreads = 192;
+constexpr int kGemmThreads = 192;      // the weight-streaming kernel: producer, MMA issuer, four epilogue warps
+constexpr int kGemmWideThreads = 320;  // the tile kernels: producer, MMA issuer, eight epilogue warps
 
 constexpr int GEMM_EPI_BF16 = 0;
 constexpr int GEMM_EPI_F32 = 1;
 constexpr int GEMM_EPI_SWIGLU = 2;
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, bool STAGING>
 struct GemmShared {
   alignas(1024) unsigned char a[STAGES][kGemmBM * kGemmBK * 2];
   alignas(1024) unsigned char b[STAGES][BN * kGemmBK * 2];
@@ -43,18 +44,102 @@ struct GemmShared {
   uint64_t accum_empty[2];
   uint32_t tmem_base;
   uint32_t failed;
+  float stage[STAGING ? 8 : 1][32 * 33];  // a 32 x 32 block per epilogue warp (float32 results), see store_block
 };
+
+constexpr int kStagePitch = 33;  // floats per row of a warp's 32 x 32 staging block: conflict-free both ways
+
+// A 32 x 32 block of results, one row per lane in `v`, to out[row0 + r][col0 + c]: through the warp's
+// staging block in shared memory, so that a store instruction writes 32 consecutive elements of one row
+// (whole 128-byte lines) instead of 32 pieces in 32 rows.
+template <typename OutT>
+__device__ __forceinline__ void store_block(float* stage, const float (&v)[32], OutT* __restrict__ out, int ldo,
+                                            int row0, int rows_valid, int col0, int cols_valid, int lane) {
+#pragma unroll
+  for (int j = 0; j < 32; ++j) stage[lane * kStagePitch + j] = v[j];
+  __syncwarp();
+  if (lane < cols_valid) {
+    OutT* dst = out + (size_t)row0 * ldo + col0 + lane;
+    const int rows = rows_valid < 32 ? rows_valid : 32;
+#pragma unroll 8
+    for (int r = 0; r < rows; ++r) dst[(size_t)r * ldo] = from_float<OutT>(stage[r * kStagePitch + lane]);
+  }
+  __syncwarp();
+}
+
+// 32 consecutive bfloat16 results of one row: 64 bytes per thread, whole sectors, in pieces of 16 bytes
+// when the row allows it.
+__device__ __forceinline__ void store_row_bf16(const float (&v)[32], __nv_bfloat16* __restrict__ dst, int cols_valid,
+                                               bool aligned) {
+#pragma unroll
+  for (int j = 0; j < 32; j += 8) {
+    if (j + 8 <= cols_valid && aligned) {
+      float piece[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) piece[e] = v[j + e];
+      store8(dst + j, piece);
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e)
+        if (j + e < cols_valid) dst[j + e] = __float2bfloat16_rn(v[j + e]);
+    }
+  }
+}
+
+// The epilogue of one warp: its 32 rows (from row `row0` of the output) of a 128 x BN accumulator
+// (tensor-memory address `lane_base`, first output column `n0`) to global memory as bfloat16, float32, or
+// silu(gate) * up with the gate in columns [0, BN / 2) and the up values in [BN / 2, BN).
+// Two warps share a quarter of the rows: `part` (0 or 1) selects this warp's half of the output columns.
+template <int BN, int EPI>
+__device__ __forceinline__ void store_accumulator(uint32_t lane_base, float* stage, int row0, int lane, int n0,
+                                                  void* __restrict__ out, int ldo, int M, int N, int inter, int part) {
+  const int rows_valid = M - row0;
+  if (EPI == GEMM_EPI_SWIGLU) {
+    constexpr int HALF = BN / 2;
+    for (int c0 = part * (HALF / 2); c0 < (part + 1) * (HALF / 2); c0 += 32) {
+      uint32_t gate[32], up[32];
+      tmem_load_32(lane_base + c0, gate);
+      tmem_load_32(lane_base + HALF + c0, up);
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      float v[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const float g = __uint_as_float(gate[j]), u = __uint_as_float(up[j]);
+        v[j] = __fdividef(g * u, 1.f + __expf(-g));
+      }
+      const int col = n0 + c0;
+      if (lane < rows_valid && col < inter)
+        store_row_bf16(v, (__nv_bfloat16*)out + (size_t)(row0 + lane) * ldo + col, inter - col, ((ldo | col) & 7) == 0);
+    }
+  } else {
+    for (int c0 = part * (BN / 2); c0 < (part + 1) * (BN / 2); c0 += 32) {
+      uint32_t acc[32];
+      tmem_load_32(lane_base + c0, acc);
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      float v[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(acc[j]);
+      const int col = n0 + c0;
+      if (rows_valid > 0 && col < N) {
+        if (EPI == GEMM_EPI_F32)
+          store_block(stage, v, (float*)out, ldo, row0, rows_valid, col, N - col, lane);
+        else if (lane < rows_valid)
+          store_row_bf16(v, (__nv_bfloat16*)out + (size_t)(row0 + lane) * ldo + col, N - col, ((ldo | col) & 7) == 0);
+      }
+    }
+  }
+}
 
 // Persistent: a CTA walks the tiles blockIdx.x, blockIdx.x + gridDim.x, ...  The accumulator is
 // double-buffered in tensor memory (2 x 256 columns), so the epilogue of one tile runs while the
 // MMAs of the next fill the other buffer; the ring of shared-memory stages runs across tiles.
 template <int BN, int STAGES, int EPI>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(kGemmWideThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     void* __restrict__ out, int ldo, int M, int N, int K, int inter, int m_tiles, int num_tiles,
                     int* __restrict__ error) {
   extern __shared__ unsigned char raw[];
-  auto& sm = *reinterpret_cast<GemmShared<BN, STAGES>*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
+  auto& sm = *reinterpret_cast<GemmShared<BN, STAGES, EPI == GEMM_EPI_F32>*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
   constexpr uint32_t TMEM_COLS = 512;   // two accumulators, the second at column 256
   constexpr uint32_t ACC_STRIDE = 256;
   constexpr uint32_t STAGE_BYTES = (kGemmBM + BN) * kGemmBK * 2;
@@ -69,7 +154,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&sm.accum_full[b], 1);
-      mbar_init(&sm.accum_empty[b], 4);  // one arrival per epilogue warp
+      mbar_init(&sm.accum_empty[b], 8);  // one arrival per epilogue warp
     }
     sm.failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -141,8 +226,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       }
     }
   } else {
-    // ---- epilogue ------------------------------------------------------------------------------------------
-    const int quadrant = warp & 3;
+    // ---- epilogue: warps w and w + 4 share rows 32 * (w % 4) .. + 31 and take half of the columns each ------
+    const int quadrant = warp & 3, part = (warp - 2) >> 2;
     uint32_t round = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++round) {
       const uint32_t buffer = round & 1;
@@ -150,76 +235,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int m0 = (tile % m_tiles) * kGemmBM;
       const int n0 = (tile / m_tiles) * PER_TILE;
-      const int row = m0 + quadrant * 32 + lane;
       const uint32_t lane_base = tmem + buffer * ACC_STRIDE + ((uint32_t)(quadrant * 32) << 16);
-      if (EPI == GEMM_EPI_SWIGLU) {
-        constexpr int HALF = BN / 2;
-        for (int c0 = 0; c0 < HALF; c0 += 32) {
-          uint32_t gate[32], up[32];
-          tmem_load_32(lane_base + c0, gate);
-          tmem_load_32(lane_base + HALF + c0, up);
-          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-          const int col = n0 + c0;
-          if (row < M) {
-            __nv_bfloat16* dst = (__nv_bfloat16*)out + (size_t)row * ldo + col;
-#pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              float v[8];
-#pragma unroll
-              for (int e = 0; e < 8; ++e) {
-                const float g = __uint_as_float(gate[j + e]), u = __uint_as_float(up[j + e]);
-                v[e] = g / (1.f + __expf(-g)) * u;
-              }
-              if (col + j + 8 <= inter && ((ldo | col) & 7) == 0) {
-                store8(dst + j, v);
-              } else {
-#pragma unroll
-                for (int e = 0; e < 8; ++e)
-                  if (col + j + e < inter) dst[j + e] = __float2bfloat16_rn(v[e]);
-              }
-            }
-          }
-        }
-      } else {
-        for (int c0 = 0; c0 < BN; c0 += 32) {
-          uint32_t acc[32];
-          tmem_load_32(lane_base + c0, acc);
-          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-          const int col = n0 + c0;
-          if (row < M && col < N) {
-            if (EPI == GEMM_EPI_F32) {
-              float* dst = (float*)out + (size_t)row * ldo + col;
-#pragma unroll
-              for (int j = 0; j < 32; j += 4) {
-                if (col + j + 4 <= N && ((ldo | col) & 3) == 0) {
-                  *reinterpret_cast<float4*>(dst + j) =
-                      make_float4(__uint_as_float(acc[j]), __uint_as_float(acc[j + 1]), __uint_as_float(acc[j + 2]),
-                                  __uint_as_float(acc[j + 3]));
-                } else {
-#pragma unroll
-                  for (int e = 0; e < 4; ++e)
-                    if (col + j + e < N) dst[j + e] = __uint_as_float(acc[j + e]);
-                }
-              }
-            } else {
-              __nv_bfloat16* dst = (__nv_bfloat16*)out + (size_t)row * ldo + col;
-#pragma unroll
-              for (int j = 0; j < 32; j += 8) {
-                float v[8];
-#pragma unroll
-                for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(acc[j + e]);
-                if (col + j + 8 <= N && ((ldo | col) & 7) == 0) {
-                  store8(dst + j, v);
-                } else {
-#pragma unroll
-                  for (int e = 0; e < 8; ++e)
-                    if (col + j + e < N) dst[j + e] = __float2bfloat16_rn(v[e]);
-                }
-              }
-            }
-          }
-        }
-      }
+      store_accumulator<BN, EPI>(lane_base, sm.stage[EPI == GEMM_EPI_F32 ? warp - 2 : 0], m0 + quadrant * 32, lane, n0, out, ldo, M, N, inter, part);
       // This warp has read its part of the accumulator: hand the buffer back to the MMA issuer.
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
@@ -231,6 +248,166 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   __syncthreads();
   if (warp == 1) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS));
+  }
+  if (threadIdx.x == 0 && sm.failed && error) atomicExch(error, 6);
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// The same product on pairs of CTAs (clusters of two, tcgen05 with cta_group::2): a pair computes 256 x BN
+// tiles.  Each CTA stages its own 128 rows of A and half of the tile's rows of W, so a stage costs a CTA
+// 16 KB + BN / 2 * 128 bytes instead of 16 KB + BN * 128 for the same number of MMA cycles: the product
+// is bound by what an SM can pull out of L2, and this is where the pair wins.  The MMA is issued by the
+// first CTA of the pair for both; it reads both CTAs' shared memory and writes 128 rows of the
+// accumulator into each CTA's tensor memory, which each CTA's epilogue warps store.
+//
+//   full[s]          in the first CTA: armed there with the bytes of both CTAs; both CTAs' copies count on it
+//   empty[s]         in each CTA: tcgen05.commit of the stage's MMAs arrives on both
+//   accum_full[b]    in each CTA: tcgen05.commit after a tile's last MMA arrives on both
+//   accum_empty[b]   in the first CTA: the sixteen epilogue warps of the pair arrive on it
+// ---------------------------------------------------------------------------------------------------------------
+template <int BN, int STAGES, int KB, bool STAGING>
+struct PairShared {
+  alignas(1024) unsigned char a[STAGES][KB][kGemmBM * kGemmBK * 2];  // KB boxes of 64 along K per stage
+  alignas(1024) unsigned char b[STAGES][KB][(BN / 2) * kGemmBK * 2];
+  uint64_t full[STAGES];
+  uint64_t empty[STAGES];
+  uint64_t accum_full[2];
+  uint64_t accum_empty[2];
+  uint32_t tmem_base;
+  uint32_t failed;
+  float stage[STAGING ? 8 : 1][32 * 33];  // a 32 x 32 block per epilogue warp (float32 results), see store_block
+};
+
+template <int BN, int STAGES, int KB, int EPI>
+__global__ void __launch_bounds__(kGemmWideThreads, 1)
+gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                         void* __restrict__ out, int ldo, int M, int N, int K, int inter, int m_tiles, int num_tiles,
+                         int* __restrict__ error) {
+  extern __shared__ unsigned char raw[];
+  auto& sm = *reinterpret_cast<PairShared<BN, STAGES, KB, EPI == GEMM_EPI_F32>*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
+  constexpr uint32_t TMEM_COLS = 512;   // two accumulators, the second at column 256
+  constexpr uint32_t ACC_STRIDE = 256;
+  constexpr uint32_t STAGE_BYTES_PAIR = 2 * KB * (kGemmBM + BN / 2) * kGemmBK * 2;
+  constexpr int STAGE_K = KB * kGemmBK;
+  constexpr int PER_TILE = EPI == GEMM_EPI_SWIGLU ? BN / 2 : BN;  // output columns per tile
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int k_blocks = (K + STAGE_K - 1) / STAGE_K;
+  const uint32_t rank = cluster_cta_rank();       // 0: issues the MMAs
+  const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&sm.full[s], 1);
+      mbar_init(&sm.empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&sm.accum_full[b], 1);
+      mbar_init(&sm.accum_empty[b], 16);  // one arrival per epilogue warp of the pair
+    }
+    sm.failed = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)),
+                 "r"(TMEM_COLS));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::);
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  cluster_barrier();  // both CTAs' barriers are initialised and tensor memory is allocated
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = sm.tmem_base;
+  grid_dependency_release();
+  grid_dependency_wait();
+
+  if (warp == 0) {
+    // ---- producer (both CTAs) -------------------------------------------------------------------------------
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += pairs) {
+        const int m0 = (tile % m_tiles) * 2 * kGemmBM + (int)rank * kGemmBM;
+        const int n_tile = (tile / m_tiles) * PER_TILE;
+        // Rows of W this CTA stages: with SwiGLU the first CTA takes the gate rows, the second the up rows.
+        const int w0 = EPI == GEMM_EPI_SWIGLU ? (rank == 0 ? n_tile : inter + n_tile) : n_tile + (int)rank * (BN / 2);
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          if (!mbar_wait_unless(&sm.empty[s], ((it / STAGES) & 1) ^ 1, &sm.failed)) { ok = false; break; }
+          if (rank == 0) mbar_expect_tx(&sm.full[s], STAGE_BYTES_PAIR);
+          const uint32_t full_addr = cluster_address(&sm.full[s], 0);
+#pragma unroll
+          for (int box = 0; box < KB; ++box) {  // a box past K is filled with zeros and still counted
+            tma_load_2d_pair(sm.a[s][box], &map_a, full_addr, kb * STAGE_K + box * kGemmBK, m0);
+            tma_load_2d_pair(sm.b[s][box], &map_b, full_addr, kb * STAGE_K + box * kGemmBK, w0);
+          }
+        }
+      }
+      if (!ok) {
+        atomicExch(&sm.failed, 1u);
+        // Copies already issued still land in shared memory: the first CTA, whose barriers count them,
+        // gives them a bounded time before the pair leaves.
+        if (rank == 0)
+          for (uint32_t back = (it > (uint32_t)STAGES ? it - STAGES : 0); back < it; ++back)
+            mbar_wait(&sm.full[back % STAGES], (back / STAGES) & 1);
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer (first CTA only) --------------------------------------------------------------------------
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = instr_desc_pair(BN);
+      uint32_t it = 0, round = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += pairs, ++round) {
+        const uint32_t buffer = round & 1;
+        if (!mbar_wait_unless(&sm.accum_empty[buffer], ((round >> 1) & 1) ^ 1, &sm.failed)) { ok = false; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t acc = tmem + buffer * ACC_STRIDE;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          if (!mbar_wait_unless(&sm.full[s], (it / STAGES) & 1, &sm.failed)) { ok = false; break; }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+          for (int box = 0; box < KB; ++box) {
+            const uint64_t a_desc = smem_desc(sm.a[s][box]), b_desc = smem_desc(sm.b[s][box]);
+#pragma unroll
+            for (int k = 0; k < kGemmBK / 16; ++k)
+              umma_bf16_pair(acc, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb > 0 || box > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit_pair(&sm.empty[s], 3);
+        }
+        if (ok) umma_commit_pair(&sm.accum_full[buffer], 3);
+      }
+      if (!ok) atomicExch(&sm.failed, 1u);
+    }
+  } else {
+    // ---- epilogue (both CTAs, each its own 128 rows; two warps per quarter of the rows, half the columns each) --
+    const int quadrant = warp & 3, part = (warp - 2) >> 2;
+    uint32_t round = 0;
+    for (int tile = pair; tile < num_tiles; tile += pairs, ++round) {
+      const uint32_t buffer = round & 1;
+      const bool ready = __all_sync(0xffffffffu, mbar_wait_unless(&sm.accum_full[buffer], (round >> 1) & 1, &sm.failed));
+      if (!ready) { atomicExch(&sm.failed, 1u); break; }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const int m0 = (tile % m_tiles) * 2 * kGemmBM + (int)rank * kGemmBM;
+      const int n0 = (tile / m_tiles) * PER_TILE;
+      const uint32_t lane_base = tmem + buffer * ACC_STRIDE + ((uint32_t)(quadrant * 32) << 16);
+      store_accumulator<BN, EPI>(lane_base, sm.stage[EPI == GEMM_EPI_F32 ? warp - 2 : 0], m0 + quadrant * 32, lane, n0, out, ldo, M, N, inter, part);
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(cluster_address(&sm.accum_empty[buffer], 0));
+    }
+  }
+
+  // Neither CTA may leave while the other can still reach its shared memory, barriers or tensor memory.
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (sm.failed && threadIdx.x == 0) {
+    // Tell the other CTA, so that its waits end at once, and give copies in flight time to land.
+    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_address(&sm.failed, rank ^ 1)), "r"(1u) : "memory");
+    __nanosleep(20000);
+  }
+  cluster_barrier();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS));
   }
   if (threadIdx.x == 0 && sm.failed && error) atomicExch(error, 6);
 }
@@ -417,7 +594,7 @@ gemm_tcgen05_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
 template <int BN, int STAGES, int EPI>
 static int launch_gemm(const CUtensorMap& map_a, const CUtensorMap& map_b, void* out, int ldo, int M, int N, int K,
                        int inter, int sm_count, int* error, cudaStream_t stream) {
-  const size_t shared = sizeof(GemmShared<BN, STAGES>) + 1024;
+  const size_t shared = sizeof(GemmShared<BN, STAGES, EPI == GEMM_EPI_F32>) + 1024;
   static bool configured = false;
   if (!configured) {
     const cudaError_t err =
@@ -431,19 +608,57 @@ static int launch_gemm(const CUtensorMap& map_a, const CUtensorMap& map_b, void*
   const int num_tiles = m_tiles * ((columns + per_tile - 1) / per_tile);
   const int grid = num_tiles < sm_count ? num_tiles : sm_count;
   const cudaError_t err =
-      launch_dependent_family(64, gemm_tcgen05_kernel<BN, STAGES, EPI>, dim3(grid), dim3(kGemmThreads), shared, stream,
+      launch_dependent_family(64, gemm_tcgen05_kernel<BN, STAGES, EPI>, dim3(grid), dim3(kGemmWideThreads), shared, stream,
                               map_a, map_b, out, ldo, M, N, K, inter, m_tiles, num_tiles, error);
   return err == cudaSuccess ? 0 : (int)err;
 }
 
+template <int BN, int STAGES, int KB, int EPI>
+static int launch_gemm_pair(const CUtensorMap& map_a, const CUtensorMap& map_b, void* out, int ldo, int M, int N, int K,
+                            int inter, int sm_count, int* error, cudaStream_t stream) {
+  const size_t shared = sizeof(PairShared<BN, STAGES, KB, EPI == GEMM_EPI_F32>) + 1024;
+  static bool configured = false;
+  static int resident_pairs = 0;  // pairs that can run at the same time (an SM left over in a GPC hosts none)
+  if (!configured) {
+    cudaError_t err = cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<BN, STAGES, KB, EPI>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+    if (err != cudaSuccess) return (int)err;
+    cudaLaunchConfig_t probe = {};
+    probe.gridDim = dim3(2 * (sm_count / 2));
+    probe.blockDim = dim3(kGemmWideThreads);
+    probe.dynamicSmemBytes = shared;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeClusterDimension;
+    attribute[0].val.clusterDim.x = 2;
+    attribute[0].val.clusterDim.y = 1;
+    attribute[0].val.clusterDim.z = 1;
+    probe.attrs = attribute;
+    probe.numAttrs = 1;
+    err = cudaOccupancyMaxActiveClusters(&resident_pairs, gemm_tcgen05_pair_kernel<BN, STAGES, KB, EPI>, &probe);
+    if (err != cudaSuccess) return (int)err;
+    if (resident_pairs < 1) return DISTIE_ERR_UNSUPPORTED;
+    configured = true;
+  }
+  const int m_tiles = (M + 2 * kGemmBM - 1) / (2 * kGemmBM);
+  const int columns = EPI == GEMM_EPI_SWIGLU ? inter : N;
+  const int per_tile = EPI == GEMM_EPI_SWIGLU ? BN / 2 : BN;
+  const int num_tiles = m_tiles * ((columns + per_tile - 1) / per_tile);
+  const int slots = resident_pairs < sm_count / 2 ? resident_pairs : sm_count / 2;
+  const int pairs = num_tiles < slots ? num_tiles : slots;
+  const cudaError_t err = launch_dependent_cluster(64, dim3(2, 1, 1), gemm_tcgen05_pair_kernel<BN, STAGES, KB, EPI>,
+                                                   dim3(2 * pairs), dim3(kGemmWideThreads), shared, stream, map_a, map_b, out,
+                                                   ldo, M, N, K, inter, m_tiles, num_tiles, error);
+  return err == cudaSuccess ? 0 : (int)err;
+}
+
 // Tile width (128, 192 or 256 columns): the one whose waves of `sm_count` tiles cost least.
-static int pick_tile_width(int M, int N, int sm_count) {
-  const int m_tiles = (M + kGemmBM - 1) / kGemmBM;
+static int pick_tile_width(int M, int N, int tile_rows, int slots) {
+  const int m_tiles = (M + tile_rows - 1) / tile_rows;
   int best = 256;
   long long best_cost = -1;
   for (int width : {256, 192, 128}) {
     const long long tiles = (long long)m_tiles * ((N + width - 1) / width);
-    const long long cost = ((tiles + sm_count - 1) / sm_count) * width;
+    const long long cost = ((tiles + slots - 1) / slots) * width;
     if (best_cost < 0 || cost < best_cost) {
       best = width;
       best_cost = cost;
@@ -469,18 +684,38 @@ extern "C" int distie_gemm_tcgen05(const void* x, int ldx, const void* w, void* 
   CUtensorMap map_a, map_b;
   int status = make_map(&map_a, x, M, K, ldx, kGemmBM);
   if (status != 0) return status;
+  static const bool pairs_enabled = [] { const char* v = getenv("DISTIE_GEMM_PAIRS"); return v == nullptr || atoi(v) != 0; }();
+  if (M >= 2 * kGemmBM && sm_count >= 2 && pairs_enabled) {
+    // Pairs of CTAs on 256-row tiles; each CTA stages half of the tile's rows of W.
+    if (epi == GEMM_EPI_SWIGLU) {
+      if ((status = make_map(&map_b, w, N, K, K, 128)) != 0) return status;
+      return launch_gemm_pair<256, 6, 1, GEMM_EPI_SWIGLU>(map_a, map_b, out, ldo, M, N, K, N / 2, sm_count, error, stream);
+    }
+    if (epi != GEMM_EPI_F32 && epi != GEMM_EPI_BF16) return DISTIE_ERR_ARG;
+    const int width = pick_tile_width(M, N, 2 * kGemmBM, sm_count / 2);
+    if ((status = make_map(&map_b, w, N, K, K, width / 2)) != 0) return status;
+#define DISTIE_GEMM_PAIR(BNV, STAGESV)                                                                                   \
+  return epi == GEMM_EPI_F32                                                                                             \
+             ? launch_gemm_pair<BNV, STAGESV - 1, 1, GEMM_EPI_F32>(map_a, map_b, out, ldo, M, N, K, 0, sm_count, error, stream) \
+             : launch_gemm_pair<BNV, STAGESV, 1, GEMM_EPI_BF16>(map_a, map_b, out, ldo, M, N, K, 0, sm_count, error, stream)
+    if (width == 256) { DISTIE_GEMM_PAIR(256, 6); }
+    if (width == 192) { DISTIE_GEMM_PAIR(192, 7); }
+    DISTIE_GEMM_PAIR(128, 8);
+#undef DISTIE_GEMM_PAIR
+  }
   if (epi == GEMM_EPI_SWIGLU) {
     status = make_map(&map_b, w, N, K, K, 128);
     if (status != 0) return status;
     return launch_gemm<256, 4, GEMM_EPI_SWIGLU>(map_a, map_b, out, ldo, M, N, K, N / 2, sm_count, error, stream);
   }
   if (epi != GEMM_EPI_F32 && epi != GEMM_EPI_BF16) return DISTIE_ERR_ARG;
-  const int width = pick_tile_width(M, N, sm_count);
+  const int width = pick_tile_width(M, N, kGemmBM, sm_count);
   status = make_map(&map_b, w, N, K, K, width);
   if (status != 0) return status;
-#define DISTIE_GEMM(BNV, STAGESV)                                                                                   \
-  return epi == GEMM_EPI_F32                                                                                        \
-             ? launch_gemm<BNV, STAGESV, GEMM_EPI_F32>(map_a, map_b, out, ldo, M, N, K, 0, sm_count, error, stream) \
+  // (the float32 epilogue stages its stores in shared memory: one stage of operands fewer)
+#define DISTIE_GEMM(BNV, STAGESV)                                                                                       \
+  return epi == GEMM_EPI_F32                                                                                            \
+             ? launch_gemm<BNV, STAGESV - 1, GEMM_EPI_F32>(map_a, map_b, out, ldo, M, N, K, 0, sm_count, error, stream) \
              : launch_gemm<BNV, STAGESV, GEMM_EPI_BF16>(map_a, map_b, out, ldo, M, N, K, 0, sm_count, error, stream)
   if (width == 256) { DISTIE_GEMM(256, 4); }
   if (width == 192) { DISTIE_GEMM(192, 5); }
