@@ -204,7 +204,7 @@ __global__ void __launch_bounds__(256) add_rmsnorm_rows_kernel(const DT* __restr
   }
 }
 
-constexpr int kNormRowsThreshold = 64;  // from this many rows on, a warp per row
+constexpr int kNormRowsThreshold = 1024;  // from this many rows on, a warp per row (fewer rows: a CTA per row)
 
 // Threads and elements per thread for a row of `hidden` (a multiple of 4, at most 8192): as few
 // elements per thread as 512 threads allow, so that a short batch still has many loads in flight.
@@ -214,7 +214,7 @@ static cudaError_t launch_add_rmsnorm_vec(const DT* delta, int splits, size_t sp
                                           float eps, cudaStream_t stream) {
   const int chunks = hidden >> 2;
   if (rows >= kNormRowsThreshold && hidden <= 128 * 32) {
-    const dim3 grid((rows + 7) / 8), block(256);
+    const dim3 grid((rows + 3) / 4), block(128);
     if (hidden <= 128 * 8)
       return launch_dependent_family(2, add_rmsnorm_rows_kernel<T, DT, 8>, grid, block, 0, stream, delta, splits,
                                      split_stride, residual, weight, out, rows_index, rows, hidden, eps);
