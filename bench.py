@@ -237,6 +237,7 @@ def time_e2e(engine, batch: int, steps: int, warmup: int) -> dict:
     elapsed = time.perf_counter() - started
     for b in range(batch):
         engine.scheduler.abort(f"e2e-{b}")
+    engine.drain()
     engine.scheduler.schedule()
     size = engine.runner.bucket_for(batch)
     return {

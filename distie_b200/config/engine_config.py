@@ -45,6 +45,7 @@ class EngineConfig:
     max_model_len: int | None = None
     dtype: str = "bfloat16"
     decode_graphs: bool = True
+    decode_ahead: bool = True  # launch a decode step before the tokens of the one ahead of it reached the host
     step_stats: int = 0
     device: str = "cuda:0"
 
@@ -65,6 +66,7 @@ class EngineConfig:
             max_seqs=_env_int("WORKER_MAX_SEQS", DEFAULT_MAX_SEQS),
             token_budget=_env_int("WORKER_TOKEN_BUDGET", DEFAULT_TOKEN_BUDGET),
             decode_graphs=_env_bool("WORKER_DECODE_GRAPHS", True),
+            decode_ahead=_env_bool("WORKER_DECODE_AHEAD", True),
             step_stats=_env_int("WORKER_STEP_STATS", 0, minimum=0),
         )
         given = {k: v for k, v in overrides.items() if v is not None}

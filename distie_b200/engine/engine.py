@@ -87,6 +87,8 @@ class Engine:
         self.stats = StepStats(config.step_stats) if config.step_stats else None
         self._serial = 0
         self.steps = 0
+        self._in_flight = None  # (plan, handle) of a launched decode step whose tokens are still on the device
+        self._planned = None    # a plan made by the pipelined path for the plain path to run
 
     # -- construction ---------------------------------------------------------
     @classmethod
@@ -94,7 +96,7 @@ class Engine:
         """Build an engine for the model folder ``model`` (``config.json`` + safetensors).
 
         ``knobs``: ``num_blocks``, ``page_size``, ``max_seqs``, ``token_budget``,
-        ``prefill_chunk``, ``max_model_len``, ``decode_graphs``, ``step_stats``; the
+        ``prefill_chunk``, ``max_model_len``, ``decode_graphs``, ``decode_ahead``, ``step_stats``; the
         reference's ``WORKER_*`` environment variables give the defaults.
         """
         if device == "cuda":
@@ -171,12 +173,13 @@ class Engine:
             self.scheduler.submit(seq)
             seqs[req.request_id] = seq
         try:
-            while self.scheduler.has_work():
+            while self.has_work():
                 for emission in self.step():
                     self._deliver(emission, results, started, on_token)
         except BaseException:
             for request_id in seqs:  # a failed step drops every request and returns their pages
                 self.scheduler.abort(request_id)
+            self._in_flight = self._planned = None
             self.scheduler.schedule()
             raise
         for request_id, seq in seqs.items():
@@ -188,9 +191,19 @@ class Engine:
         return [results[req.request_id] for req in requests]
 
     def step(self) -> list[Emission]:
-        """One scheduler step: plan, run, sample, complete."""
+        """One scheduler step: plan, run, sample, complete.
+
+        Decode steps run a step ahead when they can (``EngineConfig.decode_ahead``): the step is
+        launched, the next one is planned and launched on the strength of it, and only then are its
+        tokens waited for, so the host's share of a step and the launch of the graph overlap the
+        GPU's work on the step before.  A call still returns the emissions of exactly one step.
+        """
+        if self._in_flight is not None or (self.config.decode_ahead and self.stats is None):
+            ahead = self._step_ahead()
+            if ahead is not None:
+                return ahead
         t0 = time.perf_counter()
-        plan = self.scheduler.schedule()
+        plan, self._planned = self._planned or self.scheduler.schedule(), None
         if not plan.items:
             if self.scheduler.has_work():
                 raise CacheExhausted("no request can run: waiting requests do not fit the free pages and nothing is running")
@@ -216,6 +229,48 @@ class Engine:
                 sched=(t1 - t0) * 1e3, gpu=(t2 - t1) * 1e3, emit=(t3 - t2) * 1e3,
             )
         return emissions
+
+    def _step_ahead(self) -> list[Emission] | None:
+        """The pipelined form of ``step`` for decode steps; None when this step has to run the plain way."""
+        runner, scheduler = self.runner, self.scheduler
+        if self._in_flight is None:
+            plan = scheduler.schedule()
+            if not plan.items:
+                if scheduler.has_work():
+                    raise CacheExhausted("no request can run: waiting requests do not fit the free pages and nothing is running")
+                return []
+            if not runner.can_launch_decode(plan.items):
+                self._planned = plan  # a step with prompt portions: the plain path runs this very plan
+                return None
+            self._in_flight = (plan, runner.launch_decode(plan.items))
+        plan, handle = self._in_flight
+        self._in_flight = None
+        if scheduler.can_look_ahead(plan):
+            scheduler.assume(plan)
+            following = scheduler.schedule()
+            same_rows = len(following.items) == len(plan.items) and all(
+                a.seq is b.seq and len(b.token_ids) == 1 for a, b in zip(plan.items, following.items)
+            )
+            if same_rows and runner.can_launch_decode(following.items):
+                self._in_flight = (following, runner.launch_decode(following.items, ids_on_device=True))
+            # otherwise the step after this one is planned again once these tokens are known
+            emissions = scheduler.resolve(plan, runner.fetch_decode(handle))
+        else:
+            emissions = scheduler.complete(plan, runner.fetch_decode(handle))
+        self.steps += 1
+        return emissions
+
+    def drain(self) -> None:
+        """Waits for a launched step, if any, and drops its tokens (after requests were aborted)."""
+        if self._in_flight is not None:
+            _, handle = self._in_flight
+            self._in_flight = None
+            self.runner.fetch_decode(handle)
+        self._planned = None
+
+    def has_work(self) -> bool:
+        """Requests waiting or running, or a launched step whose tokens have not been collected."""
+        return self.scheduler.has_work() or self._in_flight is not None
 
     def _deliver(self, emission: Emission, results, started: float, on_token) -> None:
         result = results.get(emission.seq.request_id)

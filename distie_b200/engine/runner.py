@@ -53,13 +53,22 @@ class _Bucket:
         self.host_floats = torch.zeros(2 * size, dtype=torch.float32, pin_memory=pin)
         self.layout = StepLayout([], size, size, size, size, 0, np.zeros(0, dtype=np.int32))
         self.copied = torch.cuda.Event() if pin else None  # the pinned buffers wait for it before they change
+        # Sampled tokens and the kernels' error word on their way back, two sets used in turn: a step may be
+        # launched before the one ahead of it has been read.
+        self.result_host = [torch.zeros(size + 1, dtype=torch.int32, pin_memory=pin) for _ in range(2)]
+        self.result_ready = [torch.cuda.Event() if pin else None for _ in range(2)]
+        self.turn = 0
 
     def before_write(self) -> None:
         if self.copied is not None:
             self.copied.synchronize()
 
-    def upload(self) -> None:
-        self.ints.copy_(self.host_ints, non_blocking=True)
+    def upload(self, ids_on_device: bool = False) -> None:
+        """Host staging to the device; with ``ids_on_device`` the token ids the last replay left there stay."""
+        if ids_on_device:
+            self.ints[self.size :].copy_(self.host_ints[self.size :], non_blocking=True)
+        else:
+            self.ints.copy_(self.host_ints, non_blocking=True)
         self.floats.copy_(self.host_floats, non_blocking=True)
         if self.copied is not None:
             self.copied.record()
@@ -152,6 +161,22 @@ class ModelRunner:
         return self._sizes[bisect.bisect_left(self._sizes, rows)]
 
     def _graph_step(self, items) -> list[int]:
+        return self.fetch_decode(self.launch_decode(items))
+
+    def can_launch_decode(self, items) -> bool:
+        """Whether ``launch_decode`` takes these items: graphs on, one token each, a bucket large enough."""
+        return bool(
+            self.use_graphs and items and len(items) <= self._sizes[-1] and all(len(i.token_ids) == 1 for i in items)
+        )
+
+    @torch.inference_mode()
+    def launch_decode(self, items, ids_on_device: bool = False):
+        """Starts a decode step (graph replay) and returns a handle for ``fetch_decode``; does not wait.
+
+        With ``ids_on_device`` the rows' token ids are the tokens that the previous replay of
+        the same bucket sampled for the same rows (they never left the device); everything
+        else -- positions, seats, block tables, sampling numbers -- comes from the host as usual.
+        """
         rows = len(items)
         size = self.bucket_for(rows)
         bucket = self._buckets.get(size)
@@ -170,22 +195,44 @@ class ModelRunner:
         logit_rows[:] = np.arange(size, dtype=np.int32)
         floats[:] = 0.0
         for row, item in enumerate(items):
-            ids[row] = item.token_ids[0]
+            ids[row] = max(0, item.token_ids[0])
             positions[row] = item.past_len
             seats[row] = item.seq.seat
-            floats[row] = max(0.0, float(item.seq.temperature))
-            floats[size + row] = uniform(item.seq.seed, len(item.seq.output_ids))
+            if item.seq.temperature > 0:
+                floats[row] = float(item.seq.temperature)
+                floats[size + row] = uniform(item.seq.seed, len(item.seq.output_ids))
         self.cache.upload_tables([item.seq.seat for item in items])
-        bucket.upload()
+        bucket.upload(ids_on_device and bucket.graph is not None)
         if bucket.graph is None:
+            if ids_on_device:
+                raise RuntimeError("token ids on the device need a replay of the same bucket before")
             self._capture(bucket)
         else:
             bucket.graph.replay()
             self.graph_replays += 1
         self.steps += 1
-        tokens = bucket.tokens[:rows].tolist()
-        self.finish_step()
-        return [token for token, item in zip(tokens, items) if item.samples]
+        turn = bucket.turn
+        bucket.turn ^= 1
+        host = bucket.result_host[turn]
+        host[:size].copy_(bucket.tokens, non_blocking=True)
+        flag = getattr(self.kernels, "error_flag", None)
+        if flag is not None:
+            host[size:].copy_(flag, non_blocking=True)
+        else:
+            host[size:] = 0
+        if bucket.result_ready[turn] is not None:
+            bucket.result_ready[turn].record()
+        return bucket, turn, [item.samples for item in items]
+
+    def fetch_decode(self, handle) -> list[int]:
+        """The sampled tokens of a launched decode step (waits for them), after the device-side checks."""
+        bucket, turn, samples = handle
+        if bucket.result_ready[turn] is not None:
+            bucket.result_ready[turn].synchronize()
+        host = bucket.result_host[turn].tolist()
+        if host[bucket.size]:
+            self.kernels.check_errors()  # raises with the code's text and clears the word
+        return [token for token, wanted in zip(host, samples) if wanted]
 
     @torch.inference_mode()
     def decode_burst(self, items, steps: int) -> torch.Tensor:
@@ -227,8 +274,7 @@ class ModelRunner:
         for k in range(steps):
             bucket.graph.replay()
             out[k].copy_(bucket.tokens)
-            bucket.ints[:size].copy_(bucket.tokens)
-            bucket.ints[size : 2 * size].add_(advance)
+            bucket.ints[size : 2 * size].add_(advance)  # the token ids were fed back inside the graph
         self.graph_replays += steps
         self.steps += steps
         return out[:, :rows]
@@ -240,13 +286,17 @@ class ModelRunner:
         bucket.logits = self.model.forward(step, (), self.cache, rows)
         size = bucket.size
         self.sampler.pick(bucket.logits, bucket.floats[:size], bucket.floats[size:], bucket.tokens)
+        # The sampled tokens are also the next step's token ids, should it be launched before they reach the host.
+        bucket.ints[:size].copy_(bucket.tokens)
 
     def _capture(self, bucket: _Bucket) -> None:
         # Warm up on a side stream (library workspaces, lazy kernel loading), then capture.
         side = torch.cuda.Stream(device=self.device)
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
+            ids = bucket.ints[: bucket.size].clone()
             self._forward_bucket(bucket)
+            bucket.ints[: bucket.size].copy_(ids)  # the warm-up fed its tokens back; the replay starts from the step's own ids
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize(self.device)
         if self._graph_pool is None:

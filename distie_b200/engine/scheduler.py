@@ -181,7 +181,7 @@ class Scheduler:
             token = int(next(tokens)) if item.samples else None
             seq = item.seq
             if seq.request_id in self._aborted or seq.state is not SeqState.RUNNING:
-                continue
+                continue  # aborted, preempted or finished while the step was in flight
             seq.num_cached = item.past_len + len(item.token_ids)
             self._cache.trim(seq.seat, seq.num_cached)
             if token is None:
@@ -194,6 +194,64 @@ class Scheduler:
             finished = seq.finish_reason is not None
             if finished:
                 self._finish(seq)
+            out.append(Emission(seq=seq, token_id=token, finished=finished))
+        return out
+
+    # -- a step ahead ---------------------------------------------------------
+    # A decode step may be launched before the tokens of the step ahead of it have reached the host: the
+    # device feeds them to it directly.  The scheduler then books the earlier step provisionally
+    # (``assume``: one more cached token, a placeholder for the token nobody has seen yet), plans the next
+    # step as usual, and fills the tokens in when they arrive (``resolve``).  A request that turns out to
+    # have ended with that token is finished then; its row in the step already launched is ignored.
+    PLACEHOLDER = -1
+
+    def can_look_ahead(self, plan: StepPlan) -> bool:
+        """True when the step after ``plan`` can be planned without ``plan``'s tokens: decoding only,
+        nobody waiting or aborted, and no request that this step ends by length."""
+        if self._waiting or self._aborted or not plan.items:
+            return False
+        for item in plan.items:
+            seq = item.seq
+            if len(item.token_ids) != 1 or not item.samples or seq.state is not SeqState.RUNNING:
+                return False
+            if len(seq.output_ids) + 1 >= seq.max_new_tokens:
+                return False
+        return len(plan.items) == len(self._running)
+
+    def assume(self, plan: StepPlan) -> None:
+        for item in plan.items:
+            seq = item.seq
+            seq.num_cached = item.past_len + len(item.token_ids)
+            self._cache.trim(seq.seat, seq.num_cached)
+            seq.output_ids.append(self.PLACEHOLDER)
+
+    def resolve(self, plan: StepPlan, sampled: SequenceT[int]) -> list[Emission]:
+        """The tokens of a step booked with ``assume``: replaces the placeholders, finishes what ended."""
+        if len(sampled) != len(plan.items):
+            raise ValueError(f"the plan samples {len(plan.items)} tokens, got {len(sampled)}")
+        out: list[Emission] = []
+        for item, token in zip(plan.items, sampled):
+            seq = item.seq
+            index = item.past_len + 1 - len(seq.prompt_ids)  # where this step's token sits among the outputs
+            if seq.state is SeqState.FINISHED or index >= len(seq.output_ids) or seq.output_ids[index] != self.PLACEHOLDER:
+                continue
+            token = int(token)
+            seq.output_ids[index] = token
+            if seq.request_id in self._aborted:
+                continue
+            if seq.eos_id is not None and token == seq.eos_id:
+                seq.finish_reason = "eos"
+            elif index + 1 >= seq.max_new_tokens:
+                seq.finish_reason = "length"
+            finished = seq.finish_reason is not None
+            if finished:
+                del seq.output_ids[index + 1 :]  # a placeholder of the step launched meanwhile
+                if seq.state is SeqState.RUNNING:
+                    self._finish(seq)
+                else:  # preempted meanwhile: it waits, holding nothing
+                    self._waiting.remove(seq)
+                    seq.state = SeqState.FINISHED
+                    self._ids.pop(seq.request_id, None)
             out.append(Emission(seq=seq, token_id=token, finished=finished))
         return out
 

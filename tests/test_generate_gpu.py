@@ -41,6 +41,30 @@ def test_greedy_generation_float32(tiny_model, graphs):
     assert engine.cache.free_pages() == engine.cache.total_pages()
 
 
+@pytest.mark.parametrize("temperature", [0.0, 0.9])
+def test_decoding_a_step_ahead_changes_nothing(tiny_model, temperature):
+    """Steps launched before the tokens of the step ahead are known: same tokens, same ends, an end by EOS
+    in the middle included (the request's row in the step already launched is dropped)."""
+    from distie_b200.engine.engine import Engine
+
+    folder, cfg, page, _ = tiny_model
+    prompts = [helpers.random_ids(cfg["vocab_size"], n, 70 + n) for n in (3, 9, 20, 6)]
+    outcomes = {}
+    for ahead in (False, True):
+        engine = Engine.load(folder, dtype="float32", num_blocks=64, page_size=page, max_seqs=4, decode_ahead=ahead)
+        free = engine.generate(prompts, max_new_tokens=24, temperature=temperature, seed=5, ignore_eos=True)
+        # Make the token that request 1 produces as its 8th output the end-of-sequence id: it ends there, the
+        # others wherever they meet that id or at their length.
+        eos = free[1].token_ids[7]
+        stopped = engine.generate(prompts, max_new_tokens=24, temperature=temperature, seed=5, eos_id=eos)
+        outcomes[ahead] = [(r.token_ids, r.finish_reason) for r in free + stopped]
+        assert stopped[1].finish_reason == "eos" and len(stopped[1].token_ids) <= 8
+        assert engine.cache.free_pages() == engine.cache.total_pages()
+        if ahead:
+            assert engine.runner.graph_replays > 0
+    assert outcomes[True] == outcomes[False]
+
+
 def test_first_tokens_of_a_sequence(tiny_model):
     """Positions 0, 1, 2: a one-token prompt and the tokens right after it."""
     from distie_b200.engine.engine import Engine

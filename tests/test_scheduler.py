@@ -180,3 +180,69 @@ def test_complete_checks_the_number_of_tokens():
     plan = sched.schedule()
     with pytest.raises(ValueError):
         sched.complete(plan, [])
+
+
+# -- a step ahead: the bookkeeping of a decode step launched before the tokens of the one before are known ----
+def _token_for(seq, index):
+    """A stand-in for the model: the token at output position `index` of a request (deterministic)."""
+    return (sum(map(ord, seq.request_id)) * 31 + index * 7) % 50 + 1
+
+
+def _drive(pipelined, specs, pages=24, eos=None):
+    """Runs requests to the end, the plain way or a step ahead, and returns every emission in order."""
+    sched, cache = make(pages=pages, page_size=4, max_seqs=4, budget=16)
+    for name, prompt_len, new in specs:
+        sched.submit(seq(name, prompt_len, new=new, eos_id=eos))
+    emitted, in_flight = [], None
+
+    def tokens_of(plan):
+        # What the device would hand back: a token per sampling row, computed from the row's position alone.
+        return [_token_for(i.seq, i.past_len + len(i.token_ids) - len(i.seq.prompt_ids)) for i in plan.items if i.samples]
+
+    guard = 0
+    while sched.has_work() or in_flight is not None:
+        guard += 1
+        assert guard < 500
+        if in_flight is None:
+            plan = sched.schedule()
+            if not plan.items:
+                continue
+            if not pipelined or plan.kind != "decode":
+                emitted += [(e.seq.request_id, e.token_id, e.finished) for e in sched.complete(plan, tokens_of(plan))]
+                continue
+            in_flight = plan
+        plan, in_flight = in_flight, None
+        if sched.can_look_ahead(plan):
+            sched.assume(plan)
+            following = sched.schedule()
+            same = len(following.items) == len(plan.items) and all(
+                a.seq is b.seq and len(b.token_ids) == 1 for a, b in zip(plan.items, following.items))
+            if same:
+                assert all(b.token_ids == [Scheduler.PLACEHOLDER] for b in following.items)
+                in_flight = following
+            out = sched.resolve(plan, tokens_of(plan))
+        else:
+            out = sched.complete(plan, tokens_of(plan))
+        emitted += [(e.seq.request_id, e.token_id, e.finished) for e in out]
+    assert cache.free_pages() == pages
+    return emitted
+
+
+@pytest.mark.parametrize("eos", [None, 17, 33])
+def test_a_step_ahead_emits_what_the_plain_loop_emits(eos):
+    specs = [("a", 5, 9), ("b", 3, 4), ("c", 11, 12), ("d", 2, 1)]
+    plain = _drive(False, specs, eos=eos)
+    ahead = _drive(True, specs, eos=eos)
+    by_request = lambda out, r: [(t, f) for name, t, f in out if name == r]  # noqa: E731
+    for name, _, _ in specs:
+        assert by_request(ahead, name) == by_request(plain, name), name
+    assert sum(1 for _, _, finished in ahead if finished) == len(specs)
+
+
+def test_a_step_ahead_survives_preemption():
+    # So few pages that the newest request is preempted while steps are in flight; nothing is emitted twice.
+    specs = [("a", 6, 10), ("b", 6, 10), ("c", 6, 10)]
+    plain = _drive(False, specs, pages=9)
+    ahead = _drive(True, specs, pages=9)
+    for name, _, _ in specs:
+        assert [t for n, t, _ in ahead if n == name] == [t for n, t, _ in plain if n == name]
