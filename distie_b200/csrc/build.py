@@ -44,7 +44,7 @@ CUDA_UNITS: dict[str, list[str]] = {
     # every model needs these
     "base": ["elementwise.cu", "attention_generic.cu", "attention_decode.cu", "sampling.cu"],
     # bfloat16 serving only: tensor-core attention for prompts, weight-streaming products for decoding
-    "bf16": ["attention_prefill.cu", "attention_decode_mma.cu", "gemm_skinny.cu", "gemm_tcgen05.cu", "attention_prefill_tcgen05.cu"],
+    "bf16": ["attention_prefill.cu", "attention_decode_mma.cu", "gemm_tcgen05.cu", "attention_prefill_tcgen05.cu"],
 }
 _HEADERS = ["common.cuh", "tcgen05.cuh", "no_alloc.h"]
 

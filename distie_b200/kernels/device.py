@@ -63,8 +63,6 @@ class DeviceKernels(KernelSet):
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.error_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.launches = 0  # own kernels launched (library products are not counted)
-        # Counters and partial sums of products that split K over several CTAs; zero between launches.
-        self.split_workspace = torch.zeros(2 * 1024 * 1024, dtype=torch.float32, device=self.device)
 
     # -- helpers ------------------------------------------------------------
     @staticmethod
@@ -184,17 +182,6 @@ class DeviceKernels(KernelSet):
                 _CODE.get(out.dtype, 0), self.sm_count, self.error_flag.data_ptr(), self._stream(),
             ),
             "gemm_tcgen05_skinny",
-        )
-        self.launches += 1
-
-    def _linear_skinny(self, x, weight, bias, out, swiglu: int) -> None:
-        check(
-            function("distie_linear_skinny")(
-                x.data_ptr(), x.stride(0), weight.data_ptr(), bias.data_ptr() if bias is not None else None,
-                out.data_ptr(), out.stride(0), x.shape[0], weight.shape[0], weight.shape[1], _CODE[out.dtype],
-                swiglu, self.split_workspace.data_ptr(), self.split_workspace.numel(), self.sm_count, self._stream(),
-            ),
-            "linear_skinny",
         )
         self.launches += 1
 

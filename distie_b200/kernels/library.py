@@ -42,10 +42,6 @@ _SIGNATURES: dict[str, tuple[str, list]] = {
     "distie_gemm_tcgen05": ("bf16", [P, I, P, P, I, I, I, I, I, I, P, P]),
     "distie_gemm_tcgen05_skinny_splits": ("bf16", [I, I, I]),
     "distie_gemm_tcgen05_skinny": ("bf16", [P, I, P, P, P, I, I, I, I, I, I, I, P, P]),
-    "distie_linear_skinny": ("bf16", [P, I, P, P, P, I, I, I, I, I, I, P, L, I, P]),
-    "distie_linear_skinny_max_rows": ("bf16", []),
-    "distie_linear_skinny_splits": ("bf16", [I, I, I, I]),
-    "distie_linear_skinny_partial": ("bf16", [P, I, P, P, I, I, I, I, P]),
 }
 _RESULT = {"distie_attention_decode_scratch_floats": c_longlong}
 
