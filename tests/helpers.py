@@ -214,9 +214,9 @@ class Bf16Budget:
     of the logit scale among thousands already doubles the pooled rms.
     """
 
-    def __init__(self, requests: dict, weights: dict, cfg: dict, expected: dict, skip: int = 0) -> None:
+    def __init__(self, requests: dict, weights: dict, cfg: dict, expected: dict, skip: int = 0, order=None) -> None:
         low = {k: v.to(torch.bfloat16) for k, v in weights.items()}
-        rough = {rid: plain.forward_logits(ids, low, cfg)[skip:] for rid, ids in requests.items()}
+        rough = {rid: plain.forward_logits(ids, low, cfg, order=order)[skip:] for rid, ids in requests.items()}
         self.max_error, self.rms_error, self.top1 = pooled_stats(rough, {r: expected[r][-rough[r].shape[0]:] for r in rough})
 
     def check(self, got: dict, expected: dict, what: str = "") -> None:
@@ -246,3 +246,27 @@ def error_stats(have: torch.Tensor, want: torch.Tensor) -> tuple[float, float, f
     diff = (have.float() - want).abs() / plain.logit_scale(want)
     top1 = float((have.argmax(-1) == want.argmax(-1)).float().mean())
     return float(diff.max()), float(diff.pow(2).mean().sqrt()), top1
+
+
+# -- a toy arrangement of the architecture's own parts: the run order as data -----------------------
+TOY_WINDOW = 9
+# (layer, window of its attention, call whose keys and values it reads instead of writing its own)
+TOY_ORDER = [(0, None, None), (1, TOY_WINDOW, None), (0, None, None), (2, TOY_WINDOW, 1)]
+
+
+def toy_arrangement_spec(cfg: dict):
+    """Configuration B's parts arranged differently: layer 1 and 2 attend through a window, layer 0 runs
+    twice (each call with a cache slot of its own), and layer 2 reads the keys and values that layer 1
+    wrote instead of writing any.  The plain counterpart is ``plain.forward_logits(order=TOY_ORDER)``."""
+    from dataclasses import replace
+
+    from distie_b200.config import LayerCall, PartSpec, get_architecture
+
+    arch = get_architecture(cfg["architectures"][0])
+    spec = arch.recipe(arch.config_cls.from_dict(cfg))
+    layers = list(spec.layers)
+    for index in (1, 2):
+        mixer = layers[index].mixer
+        layers[index] = replace(layers[index], mixer=PartSpec(mixer.kind, {**mixer.params, "window": TOY_WINDOW}, mixer.prefix))
+    order = (LayerCall(0, 0, True), LayerCall(1, 1, True), LayerCall(0, 2, True), LayerCall(2, 1, False))
+    return replace(spec, layers=tuple(layers), order=order)

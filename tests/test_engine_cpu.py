@@ -128,3 +128,31 @@ def test_corrupted_cache_is_detected():
     got = session.run_step([{"id": "x", "tokens": ids[30:], "want": list(range(10))}], ["x"])
     want = plain.forward_logits(ids, weights, cfg)[30:]
     assert float((torch.as_tensor(got) - want).abs().max()) > 100 * helpers.FP32_TOL * plain.logit_scale(want)
+
+
+@pytest.mark.parametrize("mode", ["whole", "portions", "mixed"])
+def test_run_order_is_data(mode):
+    """A layer run twice, a layer that reads another layer's keys and values, windows on some layers only:
+    the model is built from the same parts by a different list, and every way of cutting still matches."""
+    from distie_b200.engine.engine import build_cache
+    from distie_b200.engine.runner import ModelRunner
+    from distie_b200.models.decoder import DecoderModel, model_tensor_specs
+    from distie_b200.weights import open_weights
+
+    cfg, page, weights = helpers.tiny("B")
+    spec = helpers.toy_arrangement_spec(cfg)
+    requests = requests_for(cfg, [40, 67, 33, 90, 50, 36], seed=40)
+    steps = {"whole": helpers.schedule_whole, "portions": helpers.schedule_portions, "mixed": helpers.schedule_mixed}[mode](requests)
+    kernels = RefKernels(torch.float32)
+    config = EngineConfig(num_blocks=helpers.peak_tokens(steps) // page, page_size=page, max_seqs=8, dtype="float32",
+                          decode_graphs=False, device="cpu", token_budget=4096)
+    store = open_weights(weights, model_tensor_specs(spec), spec.tolerated, kernels.dtype, kernels.device)
+    model = DecoderModel(spec, kernels, store)
+    cache = build_cache(spec, config, kernels.dtype, kernels.device)
+    assert len(cache.groups) == 2, "full and windowed layers keep pages of their own"
+    engine = Engine(model, cache, config)
+    got = helpers.collect(steps, helpers.run_schedule(TraceSession(engine), steps))
+    expected = {rid: plain.forward_logits(ids, weights, cfg, order=helpers.TOY_ORDER) for rid, ids in requests.items()}
+    error, rid, at = helpers.worst_error(got, expected)
+    assert error <= helpers.FP32_TOL, f"{mode}: request {rid} position {at} off by {error:.2e} of the logit scale"
+    assert cache.free_pages() == cache.total_pages() and cache.free_seats == cache.max_seats

@@ -82,3 +82,36 @@ def test_trace_run_program(model, tmp_path):
     got = helpers.collect(steps, outputs)
     error, rid, at = helpers.worst_error(got, model["expected"])
     assert error <= helpers.FP32_TOL, f"request {rid} position {at} off by {error:.2e}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("mode", ["whole", "tail", "mixed"])
+def test_run_order_is_data_on_the_gpu(mode, dtype):
+    """The toy arrangement (a layer twice, a layer reading another's keys and values, windows on some
+    layers): built from the same parts by a different list, replayed with the CUDA kernels."""
+    from distie_b200.config import EngineConfig
+    from distie_b200.engine.engine import Engine, build_cache
+    from distie_b200.engine.trace_replay import TraceSession
+    from distie_b200.kernels import make_kernels
+    from distie_b200.models.decoder import DecoderModel, model_tensor_specs
+    from distie_b200.weights import open_weights
+
+    cfg, page, weights = helpers.tiny("B")
+    weights = helpers.bf16_rounded(weights)
+    spec = helpers.toy_arrangement_spec(cfg)
+    requests = {f"r{i}": helpers.random_ids(cfg["vocab_size"], n, 60 + i) for i, n in enumerate([40, 67, 33, 150, 50, 36])}
+    steps = MODES[mode](requests)
+    kernels = make_kernels(torch.float32 if dtype == "float32" else torch.bfloat16, "cuda:0")
+    config = EngineConfig(num_blocks=helpers.peak_tokens(steps) // page, page_size=page, max_seqs=8, dtype=dtype,
+                          device="cuda:0", token_budget=4096)
+    store = open_weights(weights, model_tensor_specs(spec), spec.tolerated, kernels.dtype, kernels.device)
+    cache = build_cache(spec, config, kernels.dtype, kernels.device)
+    engine = Engine(DecoderModel(spec, kernels, store), cache, config)
+    got = helpers.collect(steps, helpers.run_schedule(TraceSession(engine), steps))
+    expected = {rid: plain.forward_logits(ids, weights, cfg, order=helpers.TOY_ORDER) for rid, ids in requests.items()}
+    if dtype == "float32":
+        error, rid, at = helpers.worst_error(got, expected)
+        assert error <= helpers.FP32_TOL, f"{mode}: request {rid} position {at} off by {error:.2e} of the logit scale"
+    else:
+        helpers.Bf16Budget(requests, weights, cfg, expected, order=helpers.TOY_ORDER).check(got, expected, mode)
+    assert cache.free_pages() == cache.total_pages() and cache.free_seats == cache.max_seats
