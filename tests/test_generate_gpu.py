@@ -357,3 +357,140 @@ def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
     finally:
         MIXERS.unregister("test_running_mean")
         unregister_architecture("ToyRunningMean")
+
+
+# -- a toy feed-forward with routing and a toy position encoding, registered from outside the package ------
+def test_toy_routed_feed_forward_and_position_encoding(tmp_path):
+    """Two experts chosen per token by a router, and a rotation with frequencies of its own: both defined
+    here, registered, built from a model folder and stepped, with no change to the framework's files."""
+    from distie_b200.config import LayerCall, LayerSpec, ModelSpec, PartSpec, register_architecture, unregister_architecture
+    from distie_b200.engine.engine import Engine
+    from distie_b200.engine.trace_replay import TraceSession
+    from distie_b200.kernels.interface import RotaryTable
+    from distie_b200.parts import FEED_FORWARDS, POSITION_ENCODINGS, TensorSpec
+    from distie_b200.weights import ModelTensors, write_random_model
+
+    hidden, vocab, inter, heads, kv_heads, head_dim, experts = 64, 96, 48, 4, 2, 16, 3
+
+    class RoutedFeedForward:
+        """out[t] = expert_{argmax_e(router[e] . x[t])}(x[t]), each expert a SwiGLU; router logits in float32."""
+
+        graph_safe = False  # the routing below reads nothing on the host, but gathers rows with index ops
+
+        def __init__(self, router, gate_up, down, kernels):
+            self.router, self.gate_up, self.down, self.kernels = router, gate_up, down, kernels
+
+        @classmethod
+        def tensor_specs(cls, spec, hidden_size):
+            p = spec.prefix
+            specs = [TensorSpec(p + "router.weight", (experts, hidden_size))]
+            for e in range(experts):
+                specs += [TensorSpec(p + f"e{e}.gate_proj.weight", (inter, hidden_size)),
+                          TensorSpec(p + f"e{e}.up_proj.weight", (inter, hidden_size)),
+                          TensorSpec(p + f"e{e}.down_proj.weight", (hidden_size, inter))]
+            return specs
+
+        @classmethod
+        def build(cls, spec, ctx):
+            p, w = spec.prefix, ctx.weights
+            gate_up = [torch.cat([w.matrix(p + f"e{e}.gate_proj.weight"), w.matrix(p + f"e{e}.up_proj.weight")]) for e in range(experts)]
+            down = [w.matrix(p + f"e{e}.down_proj.weight") for e in range(experts)]
+            return cls(w.matrix(p + "router.weight"), gate_up, down, ctx.kernels)
+
+        def forward(self, x, run):
+            k = self.kernels
+            choice = k.linear(x, self.router, out_dtype=torch.float32).argmax(-1)
+            out = torch.zeros((x.shape[0], hidden), dtype=torch.float32, device=x.device)
+            for e in range(experts):
+                rows = (choice == e).nonzero().flatten()
+                if rows.numel():
+                    mid = k.linear_swiglu(x.index_select(0, rows).contiguous(), self.gate_up[e])
+                    out.index_copy_(0, rows, k.linear(mid, self.down[e], out_dtype=torch.float32))
+            return out
+
+    class SlowRotation:
+        """Rotate-half with frequencies of its own: inv_freq[j] = 0.5 / (j + 1)."""
+
+        def __init__(self, table):
+            self._table = table
+
+        @classmethod
+        def build(cls, spec, ctx):
+            d = int(spec.params["head_dim"])
+            return cls(RotaryTable((0.5 / torch.arange(1, d // 2 + 1, dtype=torch.float32)).to(ctx.device), d, False))
+
+        def rotary_table(self):
+            return self._table
+
+    class ToyConfig:
+        def __init__(self, raw):
+            self.raw, self.eos_token_id = raw, None
+
+        @classmethod
+        def from_dict(cls, raw):
+            return cls(dict(raw))
+
+    def recipe(cfg):
+        layers = tuple(
+            LayerSpec(
+                "pre_norm",
+                PartSpec("gqa_attention", {"num_heads": heads, "num_kv_heads": kv_heads, "head_dim": head_dim, "qkv_bias": True,
+                                           "out_bias": False, "window": None,
+                                           "position": PartSpec("test_slow_rotation", {"head_dim": head_dim})}, f"l{i}.attn."),
+                PartSpec("test_routed", {}, f"l{i}.ff."),
+                {"input": PartSpec("rmsnorm", {"eps": 1e-5}, f"l{i}.n1."), "post_mixer": PartSpec("rmsnorm", {"eps": 1e-5}, f"l{i}.n2.")},
+            )
+            for i in range(2)
+        )
+        return ModelSpec("ToyRouted", vocab, hidden, layers, (LayerCall(0, 0), LayerCall(1, 1)),
+                         PartSpec("rmsnorm", {"eps": 1e-5}, "norm."), "embed.weight", None)
+
+    def plain_logits(ids, w):
+        """The same model written out with the plain functions (rotation with the toy's own frequencies)."""
+        ids = torch.as_tensor(ids)
+        pos = torch.arange(len(ids))
+        angles = pos[:, None].float() * (0.5 / torch.arange(1, head_dim // 2 + 1, dtype=torch.float32))[None, :]
+        cos, sin = torch.cat([angles.cos()] * 2, -1), torch.cat([angles.sin()] * 2, -1)
+        h = plain.embedding(ids, w["embed.weight"])
+        for i in range(2):
+            x = plain.rms_norm(h, w[f"l{i}.n1.weight"], 1e-5)
+            p = f"l{i}.attn."
+            q = torch.nn.functional.linear(x, w[p + "q_proj.weight"], w[p + "q_proj.bias"]).view(-1, heads, head_dim)
+            k = torch.nn.functional.linear(x, w[p + "k_proj.weight"], w[p + "k_proj.bias"]).view(-1, kv_heads, head_dim)
+            v = torch.nn.functional.linear(x, w[p + "v_proj.weight"], w[p + "v_proj.bias"]).view(-1, kv_heads, head_dim)
+            mixed = plain.attention_mix(plain.apply_rope(q, cos, sin), plain.apply_rope(k, cos, sin), v, None)
+            h = h + torch.nn.functional.linear(mixed.reshape(len(ids), -1), w[p + "o_proj.weight"])
+            x = plain.rms_norm(h, w[f"l{i}.n2.weight"], 1e-5)
+            choice = torch.nn.functional.linear(x, w[f"l{i}.ff.router.weight"]).argmax(-1)
+            rows = [plain.swiglu_mlp(x[t : t + 1], w, f"l{i}.ff.e{int(choice[t])}.") for t in range(len(ids))]
+            h = h + torch.cat(rows)
+        return torch.nn.functional.linear(plain.rms_norm(h, w["norm.weight"], 1e-5), w["embed.weight"])
+
+    FEED_FORWARDS.register("test_routed", RoutedFeedForward)
+    POSITION_ENCODINGS.register("test_slow_rotation", SlowRotation)
+    register_architecture("ToyRouted", ToyConfig, recipe)
+    try:
+        folder = write_random_model(str(tmp_path / "routed"), {"architectures": ["ToyRouted"]}, seed=6, std=0.3, dtype="float32")
+        stored = ModelTensors(folder)
+        weights = {n: stored.tensor(n).float() for n in stored.keys()}
+        engine = Engine.load(folder, dtype="float32", num_blocks=16, page_size=8, max_seqs=3)
+        session = TraceSession(engine)
+        ids_a, ids_b = helpers.random_ids(vocab, 30, 3), helpers.random_ids(vocab, 11, 4)
+        first = session.run_step([{"id": "a", "tokens": ids_a[:13], "want": list(range(13))},
+                                  {"id": "b", "tokens": ids_b, "want": list(range(11))}], ["b"])
+        rest = [session.run_step([{"id": "a", "tokens": [t], "want": [0]}]) for t in ids_a[13:]]
+        session.run_step([], ["a"])
+        got_a = torch.cat([torch.as_tensor(first[:13])] + [torch.as_tensor(r) for r in rest])
+        got_b = torch.as_tensor(first[13:])
+        for got, ids in ((got_a, ids_a), (got_b, ids_b)):
+            want = plain_logits(ids, weights)
+            assert float((got - want).abs().max()) <= 1e-4 * float(want.abs().max())
+        used = {int(c) for i in range(2) for c in torch.nn.functional.linear(
+            plain.rms_norm(plain.embedding(torch.as_tensor(ids_a), weights["embed.weight"]), weights[f"l{i}.n2.weight"], 1e-5),
+            weights[f"l{i}.ff.router.weight"]).argmax(-1)}
+        assert len(used) > 1, "the test is meant to send tokens to more than one expert"
+        assert engine.cache.free_pages() == engine.cache.total_pages()
+    finally:
+        FEED_FORWARDS.unregister("test_routed")
+        POSITION_ENCODINGS.unregister("test_slow_rotation")
+        unregister_architecture("ToyRouted")
