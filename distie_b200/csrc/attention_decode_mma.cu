@@ -33,7 +33,6 @@
 namespace distie {
 
 constexpr int kMmaDecodeWarps = 4;
-constexpr int kMmaDecodeStages = 3;
 constexpr int kMmaDecodeClusterSplits = 8;  // splits that one cluster can hold (portable cluster size)
 constexpr int kMmaDecodePages = 1024;       // page ids of a split that are kept in shared memory
 
@@ -62,7 +61,9 @@ __device__ __forceinline__ uint32_t word_of(const uint4& v, int i) {
   return i == 0 ? v.x : (i == 1 ? v.y : (i == 2 ? v.z : v.w));
 }
 
-template <int D>
+// STAGES groups of 16 keys per warp are in flight or in use: 3 for few CTAs (deep prefetch), 2 for many
+// (three CTAs fit an SM then, and twelve warps hide more latency than eight).
+template <int D, int STAGES>
 __global__ void __launch_bounds__(kMmaDecodeWarps * 32)
 attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, __nv_bfloat16* __restrict__ out,
                             int out_row_stride, float* __restrict__ scratch_o, float* __restrict__ scratch_ml,
@@ -80,8 +81,10 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_row_strid
   // The ring of the main loop and the merge area of the tail share the dynamic shared memory.
   uint4* ring = reinterpret_cast<uint4*>(dyn);  // [warp][stage][load][lane]
   float(*sh_o)[16][D + 1] = reinterpret_cast<float(*)[16][D + 1]>(dyn);
+  // This split's result, read by the other CTAs of a cluster: behind the merge area.
+  float(*cl_o)[D] = reinterpret_cast<float(*)[D]>(dyn + kMmaDecodeWarps * 16 * (D + 1) * sizeof(float));
   __shared__ float sh_m[kMmaDecodeWarps][16], sh_l[kMmaDecodeWarps][16];
-  __shared__ float cl_o[16][D], cl_m[16], cl_l[16];  // this split's result, read by the other CTAs of a cluster
+  __shared__ float cl_m[16], cl_l[16];
   __shared__ int sh_pages[kMmaDecodePages];           // the split's part of the block table
 
   grid_dependency_release();
@@ -129,7 +132,7 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_row_strid
 
   const int lo16 = lo & ~15;
   const int groups = hi >= lo ? (hi - lo16) / 16 + 1 : 0;
-  uint4* my_ring = ring + (size_t)warp * kMmaDecodeStages * LOADS * 32;
+  uint4* my_ring = ring + (size_t)warp * STAGES * LOADS * 32;
   // Issues the copies of one group of 16 keys into a stage of this warp's ring: 2 key rows (columns g
   // and g + 8 of S) and 4 value rows (reduction slots 2c, 2c+1, 2c+8, 2c+9 of P V) per lane.
   auto issue = [&](int grp, int stage) {
@@ -181,12 +184,12 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_row_strid
   // position comes from the kernel before this one (every other row was written in an earlier step),
   // so groups of keys that end before it are requested before the wait; q comes after it.
   const bool early0 = lo16 + warp * 16 + 15 < pos;
-  const bool early1 = early0 && lo16 + (warp + kMmaDecodeWarps) * 16 + 15 < pos;
+  const bool early1 = STAGES > 2 && early0 && lo16 + (warp + kMmaDecodeWarps) * 16 + 15 < pos;
   if (early0) issue(warp, 0);
   if (early1) issue(warp + kMmaDecodeWarps, 1);
   grid_dependency_wait();
   if (!early0) issue(warp, 0);
-  if (!early1) issue(warp + kMmaDecodeWarps, 1);
+  if (STAGES > 2 && !early1) issue(warp + kMmaDecodeWarps, 1);
   // Query fragments: rows g and g + 8 of the head chunk, 8 consecutive dims per piece.
   uint4 qa[QC], qb[QC];
   const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
@@ -203,8 +206,9 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_row_strid
   int stage = 0;
   for (int grp = warp; grp < groups; grp += kMmaDecodeWarps) {
     const int base_key = lo16 + grp * 16;
-    issue(grp + 2 * kMmaDecodeWarps, (stage + 2) % kMmaDecodeStages);  // empty group past the end
-    asm volatile("cp.async.wait_group 2;" ::: "memory");
+    issue(grp + (STAGES - 1) * kMmaDecodeWarps, (stage + STAGES - 1) % STAGES);  // empty group past the end
+    if (STAGES > 2) asm volatile("cp.async.wait_group 2;" ::: "memory");
+    else asm volatile("cp.async.wait_group 1;" ::: "memory");
     __syncwarp();
     uint4 kr[2][QC], vr[4][VW];
     const uint4* src = my_ring + (size_t)stage * LOADS * 32 + lane;
@@ -216,7 +220,7 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_row_strid
     for (int s = 0; s < 4; ++s)
 #pragma unroll
       for (int w = 0; w < VW; ++w) vr[s][w] = src[(2 * QC + s * VW + w) * 32];
-    stage = (stage + 1) % kMmaDecodeStages;
+    stage = (stage + 1) % STAGES;
 
     // ---- S = Q K^T for keys base..base+7 (s1) and base+8..base+15 (s2) ---------------------------
     float s1[4] = {0.f, 0.f, 0.f, 0.f}, s2[4] = {0.f, 0.f, 0.f, 0.f};
@@ -365,6 +369,12 @@ attention_decode_mma_merge_kernel(const float* __restrict__ scratch_o, const flo
 
 using namespace distie;
 
+// Stages of the key/value ring (and with them the CTAs that fit an SM: 2 with three stages, 3 with two)
+// for `tokens` single tokens and `blocks_per_token` CTAs per token and split.
+extern "C" int distie_attention_decode_mma_stages(int tokens, int blocks_per_token, int sm_count) {
+  return (long long)tokens * blocks_per_token * 2 >= sm_count ? 2 : 3;
+}
+
 // Same arguments and scratch layout as distie_attention_decode (bfloat16 only).
 extern "C" int distie_attention_decode_mma(const void* q, int q_row_stride, void* out, int out_row_stride,
                                            float* scratch, const int* positions, const int* token_seq,
@@ -388,30 +398,48 @@ extern "C" int distie_attention_decode_mma(const void* q, int q_row_stride, void
     for (page_shift = 0; (1 << page_shift) < page_size; ++page_shift) {
     }
   cudaError_t err;
-  // Dynamic shared memory: the larger of the ring (warps x stages x loads x 512 bytes) and the merge area.
+  // Many CTAs: two stages, so that three CTAs fit an SM; few: three stages.
+  static int sm_count = 0;
+  if (sm_count == 0) {
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sm_count < 1)
+      sm_count = 148;
+  }
+  const int stages = distie_attention_decode_mma_stages(tokens, num_kv_heads * chunks, sm_count);
+  // Dynamic shared memory: the larger of the ring (warps x stages x loads x 512 bytes) and the merge areas.
   const size_t loads = 2 * (head_dim / 32) + 4 * (head_dim / 64);
-  const size_t ring_bytes = (size_t)kMmaDecodeWarps * kMmaDecodeStages * loads * 512;
-  const size_t merge_bytes = (size_t)kMmaDecodeWarps * 16 * (head_dim + 1) * sizeof(float);
+  const size_t ring_bytes = (size_t)kMmaDecodeWarps * stages * loads * 512;
+  const size_t merge_bytes = (size_t)kMmaDecodeWarps * 16 * (head_dim + 1) * sizeof(float) + 16 * head_dim * sizeof(float);
   const size_t shared = ring_bytes > merge_bytes ? ring_bytes : merge_bytes;
   static bool configured = false;
   if (!configured) {
-    err = cudaFuncSetAttribute(attention_decode_mma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+    err = cudaFuncSetAttribute(attention_decode_mma_kernel<64, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
     if (err == cudaSuccess)
-      err = cudaFuncSetAttribute(attention_decode_mma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+      err = cudaFuncSetAttribute(attention_decode_mma_kernel<64, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+    if (err == cudaSuccess)
+      err = cudaFuncSetAttribute(attention_decode_mma_kernel<128, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+    if (err == cudaSuccess)
+      err = cudaFuncSetAttribute(attention_decode_mma_kernel<128, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
     if (err != cudaSuccess) return (int)err;
     configured = true;
   }
   // Up to 8 splits (the portable cluster size) are merged inside the kernel, through the cluster's shared memory.
   const int cluster_merge = (num_splits > 1 && num_splits <= kMmaDecodeClusterSplits) ? 1 : 0;
   const dim3 cluster = cluster_merge ? dim3(1, 1, num_splits) : dim3(0, 0, 0);
-#define DISTIE_MMA_DECODE(DV)                                                                                      \
-  err = launch_dependent_cluster(8, cluster, attention_decode_mma_kernel<DV>, grid, dim3(kMmaDecodeWarps * 32), shared, \
+#define DISTIE_MMA_DECODE(DV, SV)                                                                                  \
+  err = launch_dependent_cluster(8, cluster, attention_decode_mma_kernel<DV, SV>, grid, dim3(kMmaDecodeWarps * 32), shared, \
                          stream, (const __nv_bfloat16*)q, q_row_stride, (__nv_bfloat16*)out, out_row_stride, scratch_o, \
                          scratch_ml, positions, token_seq, seq_seat, block_table, table_width,                     \
                          (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, num_heads, group, chunks,   \
                          num_kv_heads, page_size, page_shift, num_pages, window, scale_log2, cluster_merge, error)
-  if (head_dim == 64) DISTIE_MMA_DECODE(64);
-  else DISTIE_MMA_DECODE(128);
+  if (head_dim == 64) {
+    if (stages == 2) DISTIE_MMA_DECODE(64, 2);
+    else DISTIE_MMA_DECODE(64, 3);
+  } else {
+    if (stages == 2) DISTIE_MMA_DECODE(128, 2);
+    else DISTIE_MMA_DECODE(128, 3);
+  }
 #undef DISTIE_MMA_DECODE
   if (err != cudaSuccess) return (int)err;
   if (num_splits > 1 && !cluster_merge) {
