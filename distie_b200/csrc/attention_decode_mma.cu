@@ -8,26 +8,20 @@
 //
 //   grid   (token, kv head * chunks of up to 16 query heads, split)
 //   block  4 warps; a warp takes groups of 16 keys of the split in turn
-//   S      the query heads of the group are the 16 rows of mma.m16n8k16, 8 keys
-//          the columns, head_dim the reduction:  S[head, key] = q[head] . k[key]
-//   P V    the same heads are the rows, 16 keys the reduction, head_dim the columns
+//   S^T    the 16 keys of a group are the rows of mma.m16n8k16, the (up to 8, or 2 x 8) query heads
+//          that share the kv head are the columns, head_dim the reduction: S^T[key, head] = k[key] . q[head]
+//   O^T    16 dims are the rows, the heads the columns, the 16 keys the reduction: O^T += V^T P^T
 //
-// Operands come from global memory in 16-byte pieces that are already the lanes' mma
-// fragments, so nothing is rearranged on the way: the reduction index of an mma may be enumerated in any order as long as
-// both operands agree, and so may the columns of the output.  A lane therefore
-// loads 8 consecutive elements of a key row and uses them as its share of two
-// k-steps of S, and 2 * head_dim / 16 consecutive elements of 4 value rows, from
-// which it assembles its B fragments of P V with byte permutes; output column
-// (n-tile t, lane group g) stands for dimension g * head_dim / 8 + t.
+// With the heads as the narrow side, 16 keys cost head_dim / 16 MMAs for the scores and as many for
+// the output, whatever the number of heads up to 8; the accumulators are head_dim / 4 registers.
+// K and V rows travel by cp.async into a per-warp ring in shared memory whose 16-byte chunks are
+// swizzled (chunk ^ (row & 7)), so that ldmatrix reads the A operands -- K as it lies, V transposed --
+// without bank conflicts.  P^T becomes the B operand of the second product with two movmatrix
+// transposes.  Column maxima and sums (per head, over keys) are reduced over the lanes that hold
+// the same column.
 //
-// The pieces travel through a small ring in shared memory (cp.async, three groups of 16 keys per
-// warp): the copies of the next two groups are in flight while a group is computed, which is what
-// keeps enough bytes in the air with only eight warps per SM.  Each lane reads back exactly the
-// pieces it copied, so the ring needs no layout beyond [stage][load][lane].
-//
-// Softmax state (max, sum) is float32 per lane; the four warps and, with several
-// splits, the CTAs of a token are merged as in the other kernel (same scratch
-// layout, same merge kernel).  head_dim 64 or 128.
+// Softmax state (max, sum) is float32 per lane; the four warps and, with several splits, the CTAs of a
+// token are merged as in the other kernel (same scratch layout, same merge kernel).  head_dim 64 or 128.
 #include "common.cuh"
 
 namespace distie {
@@ -57,13 +51,28 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-__device__ __forceinline__ uint32_t word_of(const uint4& v, int i) {
-  return i == 0 ? v.x : (i == 1 ? v.y : (i == 2 ? v.z : v.w));
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+// An 8 x 8 matrix of 16-bit values held as an mma C-style fragment (lane = row * 4 + column pair), transposed.
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
+  uint32_t y;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(y) : "r"(x));
+  return y;
 }
 
 // STAGES groups of 16 keys per warp are in flight or in use: 3 for few CTAs (deep prefetch), 2 for many
 // (three CTAs fit an SM then, and twelve warps hide more latency than eight).
-template <int D, int STAGES>
+// NH: column tiles of 8 query heads (1 for up to 8 heads per kv head, 2 for up to 16).
+// PAGE16: the page size is a power of two >= 16, so a group of 16 keys lies in one page.
+// (The kernel runs for microseconds; its code is kept small -- one form of the copy loop per
+// instantiation, few inlined copies of it -- because fetching instructions is part of that time.)
+template <int D, int STAGES, int NH, bool PAGE16>
 __global__ void __launch_bounds__(kMmaDecodeWarps * 32)
 attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, __nv_bfloat16* __restrict__ out,
                             int out_row_stride, float* __restrict__ scratch_o, float* __restrict__ scratch_ml,
@@ -73,13 +82,14 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_row_strid
                             int num_heads, int group_size, int head_chunks, int num_kv_heads, int page_size,
                             int page_shift, int num_pages, int window, float scale_log2, int cluster_merge,
                             int* __restrict__ error) {
-  constexpr int QC = D / 32;      // 16-byte pieces of a key row per lane (and of a query row)
-  constexpr int NT = D / 8;       // output n-tiles
-  constexpr int VW = D / 64;      // 16-byte pieces of a value row per lane
-  constexpr int LOADS = 2 * QC + 4 * VW;  // 16-byte pieces per lane and group of 16 keys
-  extern __shared__ __align__(16) unsigned char dyn[];
-  // The ring of the main loop and the merge area of the tail share the dynamic shared memory.
-  uint4* ring = reinterpret_cast<uint4*>(dyn);  // [warp][stage][load][lane]
+  constexpr int CPR = D / 8;                 // 16-byte chunks per row of keys or values
+  constexpr int ROW_BYTES = D * 2;
+  constexpr int TILE_BYTES = 16 * ROW_BYTES;  // 16 keys (or values)
+  constexpr int COPIES = 16 * CPR / 32;       // chunks a lane copies per tile
+  constexpr int MT = D / 16;                  // 16-dim row tiles of O^T, and k-steps of S^T
+  extern __shared__ __align__(128) unsigned char dyn[];
+  // The ring of the main loop ([warp][stage][K tile | V tile]) and the merge area of the tail share the
+  // dynamic shared memory.
   float(*sh_o)[16][D + 1] = reinterpret_cast<float(*)[16][D + 1]>(dyn);
   // This split's result, read by the other CTAs of a cluster: behind the merge area.
   float(*cl_o)[D] = reinterpret_cast<float(*)[D]>(dyn + kMmaDecodeWarps * 16 * (D + 1) * sizeof(float));
@@ -123,59 +133,71 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_row_strid
     return (staged_ready && i < kMmaDecodePages) ? sh_pages[i] : table[column];
   };
 
-  float o[NT][4];
+  float o[NH][MT][4];  // O^T: [dim 16 mt + g (+8)][head 8 nh + 2c (+1)]
 #pragma unroll
-  for (int i = 0; i < NT; ++i)
+  for (int nh = 0; nh < NH; ++nh)
 #pragma unroll
-    for (int r = 0; r < 4; ++r) o[i][r] = 0.f;
-  float row_max[2] = {-INFINITY, -INFINITY}, row_sum[2] = {0.f, 0.f};
+    for (int i = 0; i < MT; ++i)
+#pragma unroll
+      for (int r = 0; r < 4; ++r) o[nh][i][r] = 0.f;
+  float col_max[NH][2], col_sum[NH][2];  // of heads 8 nh + 2c and + 1; the sums over this lane's keys only
+#pragma unroll
+  for (int nh = 0; nh < NH; ++nh) {
+    col_max[nh][0] = col_max[nh][1] = -INFINITY;
+    col_sum[nh][0] = col_sum[nh][1] = 0.f;
+  }
 
   const int lo16 = lo & ~15;
   const int groups = hi >= lo ? (hi - lo16) / 16 + 1 : 0;
-  uint4* my_ring = ring + (size_t)warp * STAGES * LOADS * 32;
-  // Issues the copies of one group of 16 keys into a stage of this warp's ring: 2 key rows (columns g
-  // and g + 8 of S) and 4 value rows (reduction slots 2c, 2c+1, 2c+8, 2c+9 of P V) per lane.
+  const uint32_t my_ring = (uint32_t)__cvta_generic_to_shared(dyn) + (uint32_t)warp * STAGES * 2 * TILE_BYTES;
+  // Issues the copies of one group of 16 keys into a stage of this warp's ring: chunk `id` of the tile
+  // (row id / CPR, chunk id % CPR) goes to row * ROW_BYTES + ((chunk ^ (row & 7)) * 16), K and V alike.
+  constexpr int RPI = 32 / CPR;  // rows of a tile that one copy instruction of the warp covers
+  const int row0 = lane / CPR, ch = lane % CPR;  // this lane's row within those, and its chunk of the row
   auto issue = [&](int grp, int stage) {
     const int base_key = lo16 + grp * 16;
-    uint4* dst = my_ring + (size_t)stage * LOADS * 32 + lane;
+    const uint32_t k_dst = my_ring + (uint32_t)stage * 2 * TILE_BYTES, v_dst = k_dst + TILE_BYTES;
+    const bool live = grp < groups;
+    if (PAGE16) {
+      // Pages of 16, 32, ... rows: the group lies in one page, whose id is looked up once; the rows
+      // are then a fixed distance apart.  Groups inside [lo, hi] need no test per row.
+      const int page = live ? page_of(base_key) : 0;
+      const bool page_ok = live && page >= 0 && page < num_pages;
+      if (live && !page_ok && error) atomicExch(error, 4);
+      const size_t at = (((size_t)(page_ok ? page : 0) * num_kv_heads + kv_head) * page_size +
+                         (base_key & (page_size - 1)) + row0) * D + ch * 8;
+      const __nv_bfloat16* k_src = k_cache + at;
+      const __nv_bfloat16* v_src = v_cache + at;
+      const bool whole = page_ok && base_key >= lo && base_key + 15 <= hi;
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const int key = base_key + g + 8 * h;
-      bool ok = grp < groups && key >= lo && key <= hi;
-      size_t at = 0;
-      if (ok) {
-        // page_shift >= 0: the page size is a power of two, so no division per row.
-        const int page = page_of(key);
-        const int within = page_shift >= 0 ? key & (page_size - 1) : key % page_size;
-        if (page < 0 || page >= num_pages) {
-          if (error) atomicExch(error, 4);
-          ok = false;
-        } else {
-          at = (((size_t)page * num_kv_heads + kv_head) * page_size + within) * D + 8 * c;
-        }
+      for (int i = 0; i < COPIES; ++i) {
+        const int row = i * RPI + row0;
+        const bool ok = whole || (page_ok && base_key + row >= lo && base_key + row <= hi);
+        const uint32_t offset = (uint32_t)(row * ROW_BYTES + ((ch ^ (row & 7)) << 4));
+        cp_async16(k_dst + offset, ok ? k_src + i * RPI * D : k_cache, ok ? 16 : 0);
+        cp_async16(v_dst + offset, ok ? v_src + i * RPI * D : v_cache, ok ? 16 : 0);
       }
+    } else {
 #pragma unroll
-      for (int j = 0; j < QC; ++j)
-        cp_async16((uint32_t)__cvta_generic_to_shared(dst + (h * QC + j) * 32), k_cache + at + 32 * j, ok ? 16 : 0);
-    }
-#pragma unroll
-    for (int s = 0; s < 4; ++s) {
-      const int key = base_key + 2 * c + (s & 1) + 8 * (s >> 1);
-      bool ok = grp < groups && key >= lo && key <= hi;
-      size_t at = 0;
-      if (ok) {
-        const int page = page_of(key);
-        const int within = page_shift >= 0 ? key & (page_size - 1) : key % page_size;
-        if (page < 0 || page >= num_pages) {
-          ok = false;
-        } else {
-          at = (((size_t)page * num_kv_heads + kv_head) * page_size + within) * D + g * (D / 8);
+      for (int i = 0; i < COPIES; ++i) {
+        const int row = i * RPI + row0;
+        const int key = base_key + row;
+        bool ok = live && key >= lo && key <= hi;
+        size_t at = 0;
+        if (ok) {
+          const int page = page_of(key);
+          const int within = page_shift >= 0 ? key & (page_size - 1) : key % page_size;
+          if (page < 0 || page >= num_pages) {
+            if (error) atomicExch(error, 4);
+            ok = false;
+          } else {
+            at = (((size_t)page * num_kv_heads + kv_head) * page_size + within) * D + ch * 8;
+          }
         }
+        const uint32_t offset = (uint32_t)(row * ROW_BYTES + ((ch ^ (row & 7)) << 4));
+        cp_async16(k_dst + offset, k_cache + at, ok ? 16 : 0);
+        cp_async16(v_dst + offset, v_cache + at, ok ? 16 : 0);
       }
-#pragma unroll
-      for (int w = 0; w < VW; ++w)
-        cp_async16((uint32_t)__cvta_generic_to_shared(dst + (2 * QC + s * VW + w) * 32), v_cache + at + 8 * w,
-                   ok ? 16 : 0);
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
@@ -183,26 +205,33 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_row_strid
   // Positions, seats and tables are inputs of the step.  Of the cache only the row of the newest
   // position comes from the kernel before this one (every other row was written in an earlier step),
   // so groups of keys that end before it are requested before the wait; q comes after it.
-  const bool early0 = lo16 + warp * 16 + 15 < pos;
-  const bool early1 = STAGES > 2 && early0 && lo16 + (warp + kMmaDecodeWarps) * 16 + 15 < pos;
-  if (early0) issue(warp, 0);
-  if (early1) issue(warp + kMmaDecodeWarps, 1);
+  int issued = 0;
+#pragma unroll 1
+  for (; issued < STAGES - 1; ++issued) {
+    if (lo16 + (warp + issued * kMmaDecodeWarps) * 16 + 15 >= pos) break;
+    issue(warp + issued * kMmaDecodeWarps, issued);
+  }
   grid_dependency_wait();
-  if (!early0) issue(warp, 0);
-  if (STAGES > 2 && !early1) issue(warp + kMmaDecodeWarps, 1);
-  // Query fragments: rows g and g + 8 of the head chunk, 8 consecutive dims per piece.
-  uint4 qa[QC], qb[QC];
-  const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll 1
+  for (; issued < STAGES - 1; ++issued) issue(warp + issued * kMmaDecodeWarps, issued);
+  // B fragments of S^T = K Q^T: for k-step ks, dims 16 ks + 2c, + 1 and 16 ks + 2c + 8, + 9 of head g.
+  uint32_t qb[NH][MT][2];
 #pragma unroll
-  for (int j = 0; j < QC; ++j) {
-    const __nv_bfloat16* base = q + (size_t)t * q_row_stride + 32 * j + 8 * c;
-    qa[j] = g < heads_here ? load16_cg(base + (size_t)(head0 + g) * D) : zero;
-    qb[j] = g + 8 < heads_here ? load16_cg(base + (size_t)(head0 + g + 8) * D) : zero;
+  for (int nh = 0; nh < NH; ++nh) {
+    const int hd = nh * 8 + g;
+    const __nv_bfloat16* row = q + (size_t)t * q_row_stride + (size_t)(head0 + hd) * D + 2 * c;
+#pragma unroll
+    for (int ks = 0; ks < MT; ++ks) {
+      qb[nh][ks][0] = hd < heads_here ? __ldcg(reinterpret_cast<const unsigned int*>(row + 16 * ks)) : 0u;
+      qb[nh][ks][1] = hd < heads_here ? __ldcg(reinterpret_cast<const unsigned int*>(row + 16 * ks + 8)) : 0u;
+    }
   }
 #pragma unroll
   for (int u = 0; u < kStagedPerThread; ++u) sh_pages[threadIdx.x + u * kMmaDecodeWarps * 32] = staged[u];
   __syncthreads();
   staged_ready = true;
+  // ldmatrix addressing: lane = 8 * matrix + row of the matrix.
+  const int lm_mat = lane >> 3, lm_row = lane & 7;
   int stage = 0;
   for (int grp = warp; grp < groups; grp += kMmaDecodeWarps) {
     const int base_key = lo16 + grp * 16;
@@ -210,67 +239,84 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_row_strid
     if (STAGES > 2) asm volatile("cp.async.wait_group 2;" ::: "memory");
     else asm volatile("cp.async.wait_group 1;" ::: "memory");
     __syncwarp();
-    uint4 kr[2][QC], vr[4][VW];
-    const uint4* src = my_ring + (size_t)stage * LOADS * 32 + lane;
-#pragma unroll
-    for (int h = 0; h < 2; ++h)
-#pragma unroll
-      for (int j = 0; j < QC; ++j) kr[h][j] = src[(h * QC + j) * 32];
-#pragma unroll
-    for (int s = 0; s < 4; ++s)
-#pragma unroll
-      for (int w = 0; w < VW; ++w) vr[s][w] = src[(2 * QC + s * VW + w) * 32];
+    const uint32_t k_tile = my_ring + (uint32_t)stage * 2 * TILE_BYTES, v_tile = k_tile + TILE_BYTES;
     stage = (stage + 1) % STAGES;
 
-    // ---- S = Q K^T for keys base..base+7 (s1) and base+8..base+15 (s2) ---------------------------
-    float s1[4] = {0.f, 0.f, 0.f, 0.f}, s2[4] = {0.f, 0.f, 0.f, 0.f};
+    // ---- S^T = K Q^T: rows = keys g and g + 8 of the group, columns = heads 2c and 2c + 1 -------------
+    float st[NH][4];
+    {
+      // Matrices of a k-step: (keys 0-7, chunk 2 ks), (keys 8-15, 2 ks), (keys 0-7, 2 ks + 1), (keys 8-15, 2 ks + 1).
+      // Even and odd k-steps accumulate apart, which halves the chain of dependent MMAs.
+      float half[NH][2][4];
 #pragma unroll
-    for (int j = 0; j < QC; ++j) {
-      mma_16816_bf16(s1, qa[j].x, qb[j].x, qa[j].y, qb[j].y, kr[0][j].x, kr[0][j].y);
-      mma_16816_bf16(s1, qa[j].z, qb[j].z, qa[j].w, qb[j].w, kr[0][j].z, kr[0][j].w);
-      mma_16816_bf16(s2, qa[j].x, qb[j].x, qa[j].y, qb[j].y, kr[1][j].x, kr[1][j].y);
-      mma_16816_bf16(s2, qa[j].z, qb[j].z, qa[j].w, qb[j].w, kr[1][j].z, kr[1][j].w);
-    }
-
-    // ---- mask and online softmax; rows: [0] head g, [1] head g + 8 ----------------------------------
-    float p1[4], p2[4], corr[2];
+      for (int nh = 0; nh < NH; ++nh)
 #pragma unroll
-    for (int r = 0; r < 4; ++r) {
-      const int key1 = base_key + 2 * c + (r & 1), key2 = key1 + 8;
-      p1[r] = (key1 >= lo && key1 <= hi) ? s1[r] * scale_log2 : -INFINITY;
-      p2[r] = (key2 >= lo && key2 <= hi) ? s2[r] * scale_log2 : -INFINITY;
-    }
+        for (int r = 0; r < 4; ++r) half[nh][0][r] = half[nh][1][r] = 0.f;
+      const int key = lm_row + 8 * (lm_mat & 1);
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      float m = fmaxf(fmaxf(p1[2 * h], p1[2 * h + 1]), fmaxf(p2[2 * h], p2[2 * h + 1]));
-      m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
-      m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
-      const float m_new = fmaxf(row_max[h], m);
-      corr[h] = m_new == -INFINITY ? 1.f : exp2f(row_max[h] - m_new);
-      row_max[h] = m_new;
-      const float shift = m_new == -INFINITY ? 0.f : m_new;
-      float sum = 0.f;
+      for (int ks = 0; ks < MT; ++ks) {
+        const int ch = 2 * ks + (lm_mat >> 1);
+        uint32_t a[4];
+        ldmatrix_x4(a, k_tile + (uint32_t)(key * ROW_BYTES + ((ch ^ (key & 7)) << 4)));
 #pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        p1[2 * h + e] = exp2f(p1[2 * h + e] - shift);
-        p2[2 * h + e] = exp2f(p2[2 * h + e] - shift);
-        sum += p1[2 * h + e] + p2[2 * h + e];
+        for (int nh = 0; nh < NH; ++nh)
+          mma_16816_bf16(half[nh][ks & 1], a[0], a[1], a[2], a[3], qb[nh][ks][0], qb[nh][ks][1]);
       }
-      row_sum[h] = row_sum[h] * corr[h] + sum;
-    }
-    const uint32_t a0 = pack2(p1[0], p1[1]), a1 = pack2(p1[2], p1[3]);
-    const uint32_t a2 = pack2(p2[0], p2[1]), a3 = pack2(p2[2], p2[3]);
-
-    // ---- O = O * corr + P V --------------------------------------------------------------------------
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
-      o[nt][0] *= corr[0]; o[nt][1] *= corr[0];
-      o[nt][2] *= corr[1]; o[nt][3] *= corr[1];
-      const int w = (nt >> 1) & 3, piece = nt >> 3;
-      const uint32_t sel = (nt & 1) ? 0x7632u : 0x5410u;
-      const uint32_t b0 = __byte_perm(word_of(vr[0][piece], w), word_of(vr[1][piece], w), sel);
-      const uint32_t b1 = __byte_perm(word_of(vr[2][piece], w), word_of(vr[3][piece], w), sel);
-      mma_16816_bf16(o[nt], a0, a1, a2, a3, b0, b1);
+      for (int nh = 0; nh < NH; ++nh)
+#pragma unroll
+        for (int r = 0; r < 4; ++r) st[nh][r] = half[nh][0][r] + half[nh][1][r];
+    }
+
+    // ---- mask (first and last group of a split), maxima and exponentials per head -------------------------
+    const bool edge = base_key < lo || base_key + 15 > hi;
+    const bool keep_lo = !edge || (base_key + g >= lo && base_key + g <= hi);
+    const bool keep_hi = !edge || (base_key + g + 8 >= lo && base_key + g + 8 <= hi);
+    uint32_t pb[NH][2];
+    float corr[NH][2];
+#pragma unroll
+    for (int nh = 0; nh < NH; ++nh) {
+      float x[4];
+      x[0] = keep_lo ? st[nh][0] * scale_log2 : -INFINITY;
+      x[1] = keep_lo ? st[nh][1] * scale_log2 : -INFINITY;
+      x[2] = keep_hi ? st[nh][2] * scale_log2 : -INFINITY;
+      x[3] = keep_hi ? st[nh][3] * scale_log2 : -INFINITY;
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {  // column e of the lane: head 8 nh + 2c + e
+        float m = fmaxf(x[e], x[e + 2]);
+        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 4));
+        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 8));
+        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 16));
+        const float m_new = fmaxf(col_max[nh][e], m);
+        corr[nh][e] = m_new == -INFINITY ? 1.f : exp2f(col_max[nh][e] - m_new);
+        col_max[nh][e] = m_new;
+        const float shift = m_new == -INFINITY ? 0.f : m_new;
+        x[e] = exp2f(x[e] - shift);
+        x[e + 2] = exp2f(x[e + 2] - shift);
+        col_sum[nh][e] = col_sum[nh][e] * corr[nh][e] + x[e] + x[e + 2];
+      }
+      // P^T as the B operand of the second product: keys become the reduction index.
+      pb[nh][0] = movmatrix_trans(pack2(x[0], x[1]));
+      pb[nh][1] = movmatrix_trans(pack2(x[2], x[3]));
+    }
+
+    // ---- O^T = O^T * corr + V^T P^T ------------------------------------------------------------------------
+    {
+      // Matrices of a row tile: (keys 0-7, chunk 2 mt), (keys 0-7, 2 mt + 1), (keys 8-15, 2 mt), (keys 8-15, 2 mt + 1),
+      // each transposed on the way in.
+      const int key = lm_row + 8 * (lm_mat >> 1);
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        const int ch = 2 * mt + (lm_mat & 1);
+        uint32_t a[4];
+        ldmatrix_x4_trans(a, v_tile + (uint32_t)(key * ROW_BYTES + ((ch ^ (key & 7)) << 4)));
+#pragma unroll
+        for (int nh = 0; nh < NH; ++nh) {
+          o[nh][mt][0] *= corr[nh][0]; o[nh][mt][1] *= corr[nh][1];
+          o[nh][mt][2] *= corr[nh][0]; o[nh][mt][3] *= corr[nh][1];
+          mma_16816_bf16(o[nh][mt], a[0], a[1], a[2], a[3], pb[nh][0], pb[nh][1]);
+        }
+      }
     }
   }
 
@@ -278,17 +324,22 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_row_strid
   asm volatile("cp.async.wait_group 0;" ::: "memory");
   __syncthreads();  // the ring is done with: its memory becomes the merge area
 #pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    float l = row_sum[h];
-    l += __shfl_xor_sync(0xffffffffu, l, 1);
-    l += __shfl_xor_sync(0xffffffffu, l, 2);
-    if (c == 0) { sh_m[warp][g + 8 * h] = row_max[h]; sh_l[warp][g + 8 * h] = l; }
+  for (int nh = 0; nh < NH; ++nh)
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
-      sh_o[warp][g + 8 * h][(2 * c) * (D / 8) + nt] = o[nt][2 * h];
-      sh_o[warp][g + 8 * h][(2 * c + 1) * (D / 8) + nt] = o[nt][2 * h + 1];
+    for (int e = 0; e < 2; ++e) {
+      float l = col_sum[nh][e];  // add up the lanes that hold other keys of the same head
+      l += __shfl_xor_sync(0xffffffffu, l, 4);
+      l += __shfl_xor_sync(0xffffffffu, l, 8);
+      l += __shfl_xor_sync(0xffffffffu, l, 16);
+      const int hd = nh * 8 + 2 * c + e;
+      if (g == 0) { sh_m[warp][hd] = col_max[nh][e]; sh_l[warp][hd] = l; }
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        sh_o[warp][hd][16 * mt + g] = o[nh][mt][e];
+        sh_o[warp][hd][16 * mt + g + 8] = o[nh][mt][e + 2];
+      }
     }
-  }
+  if (NH == 1 && lane < 8) { sh_m[warp][8 + lane] = -INFINITY; sh_l[warp][8 + lane] = 0.f; }
   __syncthreads();
   for (int idx = threadIdx.x; idx < heads_here * D; idx += kMmaDecodeWarps * 32) {
     const int hd = idx / D, e = idx % D;
@@ -408,38 +459,45 @@ extern "C" int distie_attention_decode_mma(const void* q, int q_row_stride, void
   }
   const int stages = distie_attention_decode_mma_stages(tokens, num_kv_heads * chunks, sm_count);
   // Dynamic shared memory: the larger of the ring (warps x stages x loads x 512 bytes) and the merge areas.
-  const size_t loads = 2 * (head_dim / 32) + 4 * (head_dim / 64);
-  const size_t ring_bytes = (size_t)kMmaDecodeWarps * stages * loads * 512;
+  const size_t ring_bytes = (size_t)kMmaDecodeWarps * stages * 2 * 16 * head_dim * 2;  // K and V tiles of 16 rows
   const size_t merge_bytes = (size_t)kMmaDecodeWarps * 16 * (head_dim + 1) * sizeof(float) + 16 * head_dim * sizeof(float);
   const size_t shared = ring_bytes > merge_bytes ? ring_bytes : merge_bytes;
+  const int column_tiles = group > 8 ? 2 : 1;  // (of a chunk of up to 16 heads)
   static bool configured = false;
   if (!configured) {
-    err = cudaFuncSetAttribute(attention_decode_mma_kernel<64, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
-    if (err == cudaSuccess)
-      err = cudaFuncSetAttribute(attention_decode_mma_kernel<64, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
-    if (err == cudaSuccess)
-      err = cudaFuncSetAttribute(attention_decode_mma_kernel<128, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
-    if (err == cudaSuccess)
-      err = cudaFuncSetAttribute(attention_decode_mma_kernel<128, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
-    if (err != cudaSuccess) return (int)err;
+#define DISTIE_MMA_DECODE_SMEM(DV, SV, NV)                                                                        \
+  if ((err = cudaFuncSetAttribute(attention_decode_mma_kernel<DV, SV, NV, true>,                                    \
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024)) != cudaSuccess ||       \
+      (err = cudaFuncSetAttribute(attention_decode_mma_kernel<DV, SV, NV, false>,                                   \
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024)) != cudaSuccess)         \
+    return (int)err
+    DISTIE_MMA_DECODE_SMEM(64, 2, 1); DISTIE_MMA_DECODE_SMEM(64, 3, 1); DISTIE_MMA_DECODE_SMEM(128, 2, 1); DISTIE_MMA_DECODE_SMEM(128, 3, 1);
+    DISTIE_MMA_DECODE_SMEM(64, 2, 2); DISTIE_MMA_DECODE_SMEM(64, 3, 2); DISTIE_MMA_DECODE_SMEM(128, 2, 2); DISTIE_MMA_DECODE_SMEM(128, 3, 2);
+#undef DISTIE_MMA_DECODE_SMEM
     configured = true;
   }
   // Up to 8 splits (the portable cluster size) are merged inside the kernel, through the cluster's shared memory.
   const int cluster_merge = (num_splits > 1 && num_splits <= kMmaDecodeClusterSplits) ? 1 : 0;
   const dim3 cluster = cluster_merge ? dim3(1, 1, num_splits) : dim3(0, 0, 0);
-#define DISTIE_MMA_DECODE(DV, SV)                                                                                  \
-  err = launch_dependent_cluster(8, cluster, attention_decode_mma_kernel<DV, SV>, grid, dim3(kMmaDecodeWarps * 32), shared, \
-                         stream, (const __nv_bfloat16*)q, q_row_stride, (__nv_bfloat16*)out, out_row_stride, scratch_o, \
-                         scratch_ml, positions, token_seq, seq_seat, block_table, table_width,                     \
+#define DISTIE_MMA_DECODE(DV, SV, NV)                                                                              \
+  if (page_shift >= 4) DISTIE_MMA_DECODE_PAGE(DV, SV, NV, true);                                                   \
+  else DISTIE_MMA_DECODE_PAGE(DV, SV, NV, false)
+#define DISTIE_MMA_DECODE_PAGE(DV, SV, NV, PV)                                                                     \
+  err = launch_dependent_cluster(8, cluster, attention_decode_mma_kernel<DV, SV, NV, PV>, grid, dim3(kMmaDecodeWarps * 32), \
+                         shared, stream, (const __nv_bfloat16*)q, q_row_stride, (__nv_bfloat16*)out, out_row_stride, \
+                         scratch_o, scratch_ml, positions, token_seq, seq_seat, block_table, table_width,          \
                          (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, num_heads, group, chunks,   \
                          num_kv_heads, page_size, page_shift, num_pages, window, scale_log2, cluster_merge, error)
+#define DISTIE_MMA_DECODE_BY_STAGES(DV, NV)   \
+  if (stages == 2) DISTIE_MMA_DECODE(DV, 2, NV); \
+  else DISTIE_MMA_DECODE(DV, 3, NV)
   if (head_dim == 64) {
-    if (stages == 2) DISTIE_MMA_DECODE(64, 2);
-    else DISTIE_MMA_DECODE(64, 3);
+    if (column_tiles == 1) { DISTIE_MMA_DECODE_BY_STAGES(64, 1); } else { DISTIE_MMA_DECODE_BY_STAGES(64, 2); }
   } else {
-    if (stages == 2) DISTIE_MMA_DECODE(128, 2);
-    else DISTIE_MMA_DECODE(128, 3);
+    if (column_tiles == 1) { DISTIE_MMA_DECODE_BY_STAGES(128, 1); } else { DISTIE_MMA_DECODE_BY_STAGES(128, 2); }
   }
+#undef DISTIE_MMA_DECODE_BY_STAGES
+#undef DISTIE_MMA_DECODE_PAGE
 #undef DISTIE_MMA_DECODE
   if (err != cudaSuccess) return (int)err;
   if (num_splits > 1 && !cluster_merge) {
