@@ -45,6 +45,7 @@ class _Bucket:
         self.ints = torch.zeros(5 * size, dtype=torch.int32, device=device)
         self.floats = torch.zeros(2 * size, dtype=torch.float32, device=device)  # temperatures | uniforms
         self.tokens = torch.zeros(size, dtype=torch.int32, device=device)
+        self.advance = torch.zeros(size, dtype=torch.int32, device=device)  # added to the positions after every replay
         self.logits: torch.Tensor | None = None
         self.graph: torch.cuda.CUDAGraph | None = None
         self.kernels_per_replay = 0  # own kernels inside the captured step
@@ -265,16 +266,19 @@ class ModelRunner:
             ints[size + row] = item.past_len
             ints[3 * size + row] = item.seq.seat
             advance[row] = 1
-        advance = advance.to(self.device)
         self.cache.upload_tables([item.seq.seat for item in items])
         bucket.upload()
         if bucket.graph is None:
             self._capture(bucket)  # runs the first step once more than asked: same tokens, same slots
+            bucket.upload()        # (and fed its tokens back: start again from the given ones)
         out = torch.empty((steps, size), dtype=torch.int32, device=self.device)
-        for k in range(steps):
-            bucket.graph.replay()
-            out[k].copy_(bucket.tokens)
-            bucket.ints[size : 2 * size].add_(advance)  # the token ids were fed back inside the graph
+        bucket.advance.copy_(advance, non_blocking=False)
+        try:
+            for k in range(steps):
+                bucket.graph.replay()  # feeds its tokens back as the next ids and moves the positions on
+                out[k].copy_(bucket.tokens)
+        finally:
+            bucket.advance.zero_()
         self.graph_replays += steps
         self.steps += steps
         return out[:, :rows]
@@ -288,6 +292,7 @@ class ModelRunner:
         self.sampler.pick(bucket.logits, bucket.floats[:size], bucket.floats[size:], bucket.tokens)
         # The sampled tokens are also the next step's token ids, should it be launched before they reach the host.
         bucket.ints[:size].copy_(bucket.tokens)
+        bucket.ints[size : 2 * size].add_(bucket.advance)  # zeros, except while a burst runs steps back to back
 
     def _capture(self, bucket: _Bucket) -> None:
         # Warm up on a side stream (library workspaces, lazy kernel loading), then capture.

@@ -424,7 +424,7 @@ def test_decode_kernel_equals_generic_kernel(kernel_sets, dtype):
     close(fast, slow, dtype, "decode vs generic")
 
 
-@pytest.mark.parametrize("vocab", [100, 384, 151936])
+@pytest.mark.parametrize("vocab", [100, 384, 32771, 151936])
 def test_sampling(kernel_sets, vocab):
     ks = kernel_sets[torch.float32]
     rows = 6
