@@ -385,7 +385,11 @@ __global__ void rope_kv_write_vec_kernel(const QT* in, int splits, size_t split_
   auto gather = [&](int first, int second, float4& a, float4& b) {
     a = make_float4(0.f, 0.f, 0.f, 0.f);
     b = a;
-    for (int sp0 = 0; sp0 < splits; sp0 += ROUND) {
+    if (splits == 1) {  // the product of a prompt portion: one slice, no rounds
+      a = load4_cg(row + first);
+      b = load4_cg(row + second);
+    }
+    for (int sp0 = 0; splits > 1 && sp0 < splits; sp0 += ROUND) {
       float4 da[ROUND], db[ROUND];
 #pragma unroll
       for (int u = 0; u < ROUND; ++u) {
