@@ -435,7 +435,7 @@ template <int BN, int STAGES>
 struct SkinnyShared {
   alignas(1024) unsigned char w[STAGES][kGemmBM * kGemmBK * 2];
   alignas(1024) unsigned char x[STAGES][BN * kGemmBK * 2];
-  float exchange[kGemmBM][BN + 1];  // SwiGLU: gate and up rows meet here
+  float exchange[kGemmBM][17];  // SwiGLU: gate and up rows meet here, 16 rows of x at a time
   uint64_t full[STAGES];
   uint64_t empty[STAGES];
   uint64_t accum;
@@ -540,44 +540,44 @@ gemm_tcgen05_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
     const int quadrant = warp & 3;
     const int local_row = quadrant * 32 + lane;
     const uint32_t lane_base = tmem + ((uint32_t)(quadrant * 32) << 16);
-    float acc[BN];
-    if (ready && !sm.failed && k_blocks > 0) {
-#pragma unroll
-      for (int c0 = 0; c0 < BN; c0 += 16) {
+    const bool valid = ready && !sm.failed && k_blocks > 0;
+    const int row = r0 + local_row;
+    const float b = (EPI == SKINNY_EPI_STORE && bias && row < N) ? bias[row] : 0.f;
+    // Sixteen rows of x at a time: the accumulator never occupies more than sixteen registers.
+    for (int c0 = 0; c0 < BN && c0 < M; c0 += 16) {
+      float acc[16];
+      if (valid) {
         uint32_t v[16];
         tmem_load_16(lane_base + c0, v);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-        for (int j = 0; j < 16; ++j) acc[c0 + j] = __uint_as_float(v[j]);
+        for (int j = 0; j < 16; ++j) acc[j] = __uint_as_float(v[j]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) acc[j] = 0.f;
       }
-    } else {
+      if (EPI == SKINNY_EPI_SWIGLU) {
 #pragma unroll
-      for (int j = 0; j < BN; ++j) acc[j] = 0.f;
-    }
-    if (EPI == SKINNY_EPI_SWIGLU) {
-#pragma unroll
-      for (int j = 0; j < BN; ++j) sm.exchange[local_row][j] = acc[j];
-      asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps only
-      if (local_row < 64) {
-        const int col = r0 + local_row;
+        for (int j = 0; j < 16; ++j) sm.exchange[local_row][j] = acc[j];
+        asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps only
+        // Output column r0 + (local_row % 64); the two halves of the threads share the sixteen rows of x.
+        const int pair = local_row & 63, j0 = (local_row >> 6) * 8;
+        const int col = r0 + pair;
         if (col < inter) {
 #pragma unroll
-          for (int j = 0; j < BN; ++j) {
-            if (j < M) {
-              const float g = sm.exchange[local_row][j], u = sm.exchange[64 + local_row][j];
-              out[(size_t)j * ldo + col] = from_float<OutT>(g / (1.f + __expf(-g)) * u);
+          for (int j = j0; j < j0 + 8; ++j) {
+            if (c0 + j < M) {
+              const float g = sm.exchange[pair][j], u = sm.exchange[64 + pair][j];
+              out[(size_t)(c0 + j) * ldo + col] = from_float<OutT>(__fdividef(g * u, 1.f + __expf(-g)));
             }
           }
         }
-      }
-    } else {
-      const int row = r0 + local_row;
-      if (row < N) {
+        asm volatile("bar.sync 1, 128;" ::: "memory");  // before the next sixteen overwrite the exchange
+      } else if (row < N) {
         OutT* dst = out + (EPI == SKINNY_EPI_SLICE ? (size_t)split * M * ldo : 0) + row;
-        const float b = (EPI == SKINNY_EPI_STORE && bias) ? bias[row] : 0.f;
 #pragma unroll
-        for (int j = 0; j < BN; ++j)
-          if (j < M) dst[(size_t)j * ldo] = from_float<OutT>(acc[j] + b);
+        for (int j = 0; j < 16; ++j)
+          if (c0 + j < M) dst[(size_t)(c0 + j) * ldo] = from_float<OutT>(acc[j] + b);
       }
     }
   }

@@ -26,7 +26,7 @@ from .library import KernelError, check, function
 _CODE = {torch.float32: 0, torch.bfloat16: 1}
 _DECODE_HEAD_DIMS = (16, 32, 64, 128, 256)
 _PREFILL_HEAD_DIMS = (64, 128)  # tensor-core attention for portions of prompts (bfloat16)
-_SKINNY_ROWS = 32               # weight-streaming products (tcgen05, weights as the 128-row operand) take up to 64 rows
+_SKINNY_ROWS = 64               # weight-streaming products (tcgen05, weights as the 128-row operand) take up to 64 rows
 _CLUSTER_SPLITS = 8             # splits of a decode attention that one cluster of CTAs merges itself
 _TENSOR_CORE_ROWS = 128         # from here on the tcgen05 kernel's 128-row tiles are full; in between: the library
 

@@ -200,7 +200,7 @@ def test_tensor_core_product(kernel_sets, m, k, n):
 
 @pytest.mark.parametrize(
     "m,k,n", [(1, 64, 128), (8, 1536, 2048), (16, 200, 1000), (17, 96, 40), (3, 8960, 1536), (40, 1536, 264),
-              (64, 72, 130), (33, 4096, 512), (5, 8, 6)]
+              (64, 72, 130), (33, 4096, 512), (5, 8, 6), (48, 264, 520)]
 )
 def test_weight_streaming_product(kernel_sets, m, k, n):
     """The tcgen05 kernel for few rows alone: slices, stored result with bias, and SwiGLU, ragged everywhere."""
@@ -210,7 +210,11 @@ def test_weight_streaming_product(kernel_sets, m, k, n):
     w = (torch.randn(n, k, device="cuda") * 0.1).to(torch.bfloat16)
     b = torch.randn(n, device="cuda")
     want = torch.nn.functional.linear(x.double(), w.double())
-    slices = ks.linear_split(x, w)
+    from distie_b200.kernels.library import function
+
+    splits = function("distie_gemm_tcgen05_skinny_splits")(n, k, ks.sm_count)
+    slices = torch.full((splits, m, n), float("nan"), dtype=torch.float32, device="cuda")
+    ks._stream_weights(x, w, None, slices, 0)
     ks.check_errors()
     assert slices.dim() == 3 and slices.dtype == torch.float32
     close(slices.sum(0), want, torch.float32, "weight streaming, slices")
