@@ -34,7 +34,7 @@ constexpr int GEMM_EPI_BF16 = 0;
 constexpr int GEMM_EPI_F32 = 1;
 constexpr int GEMM_EPI_SWIGLU = 2;
 
-template <int BN, int STAGES, bool STAGING>
+template <int BN, int STAGES>
 struct GemmShared {
   alignas(1024) unsigned char a[STAGES][kGemmBM * kGemmBK * 2];
   alignas(1024) unsigned char b[STAGES][BN * kGemmBK * 2];
@@ -44,28 +44,7 @@ struct GemmShared {
   uint64_t accum_empty[2];
   uint32_t tmem_base;
   uint32_t failed;
-  float stage[STAGING ? 8 : 1][32 * 33];  // a 32 x 32 block per epilogue warp (float32 results), see store_block
 };
-
-constexpr int kStagePitch = 33;  // floats per row of a warp's 32 x 32 staging block: conflict-free both ways
-
-// A 32 x 32 block of results, one row per lane in `v`, to out[row0 + r][col0 + c]: through the warp's
-// staging block in shared memory, so that a store instruction writes 32 consecutive elements of one row
-// (whole 128-byte lines) instead of 32 pieces in 32 rows.
-template <typename OutT>
-__device__ __forceinline__ void store_block(float* stage, const float (&v)[32], OutT* __restrict__ out, int ldo,
-                                            int row0, int rows_valid, int col0, int cols_valid, int lane) {
-#pragma unroll
-  for (int j = 0; j < 32; ++j) stage[lane * kStagePitch + j] = v[j];
-  __syncwarp();
-  if (lane < cols_valid) {
-    OutT* dst = out + (size_t)row0 * ldo + col0 + lane;
-    const int rows = rows_valid < 32 ? rows_valid : 32;
-#pragma unroll 8
-    for (int r = 0; r < rows; ++r) dst[(size_t)r * ldo] = from_float<OutT>(stage[r * kStagePitch + lane]);
-  }
-  __syncwarp();
-}
 
 // 32 consecutive bfloat16 results of one row: 64 bytes per thread, whole sectors, in pieces of 16 bytes
 // when the row allows it.
@@ -86,12 +65,23 @@ __device__ __forceinline__ void store_row_bf16(const float (&v)[32], __nv_bfloat
   }
 }
 
+// 32 consecutive float32 results of one row with 256-bit stores: every store writes a whole 32-byte
+// sector, so nothing is written in part (16-byte stores of a row fill each sector in two instructions
+// that other rows' stores come between).  dst must be 32-byte aligned.
+__device__ __forceinline__ void store_row_f32(const float (&v)[32], float* __restrict__ dst) {
+#pragma unroll
+  for (int j = 0; j < 32; j += 8)
+    asm volatile("st.global.v8.f32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(dst + j), "f"(v[j]), "f"(v[j + 1]),
+                 "f"(v[j + 2]), "f"(v[j + 3]), "f"(v[j + 4]), "f"(v[j + 5]), "f"(v[j + 6]), "f"(v[j + 7])
+                 : "memory");
+}
+
 // The epilogue of one warp: its 32 rows (from row `row0` of the output) of a 128 x BN accumulator
 // (tensor-memory address `lane_base`, first output column `n0`) to global memory as bfloat16, float32, or
 // silu(gate) * up with the gate in columns [0, BN / 2) and the up values in [BN / 2, BN).
 // Two warps share a quarter of the rows: `part` (0 or 1) selects this warp's half of the output columns.
 template <int BN, int EPI>
-__device__ __forceinline__ void store_accumulator(uint32_t lane_base, float* stage, int row0, int lane, int n0,
+__device__ __forceinline__ void store_accumulator(uint32_t lane_base, int row0, int lane, int n0,
                                                   void* __restrict__ out, int ldo, int M, int N, int inter, int part) {
   const int rows_valid = M - row0;
   if (EPI == GEMM_EPI_SWIGLU) {
@@ -121,8 +111,17 @@ __device__ __forceinline__ void store_accumulator(uint32_t lane_base, float* sta
       for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(acc[j]);
       const int col = n0 + c0;
       if (rows_valid > 0 && col < N) {
-        if (EPI == GEMM_EPI_F32)
-          store_block(stage, v, (float*)out, ldo, row0, rows_valid, col, N - col, lane);
+        if (EPI == GEMM_EPI_F32) {
+          // (uniform over the warp: whole rows of 32 columns, rows 32 bytes apart in alignment)
+          if (col + 32 <= N && ((ldo | col) & 7) == 0 && ((uintptr_t)out & 31) == 0) {
+            if (lane < rows_valid) store_row_f32(v, (float*)out + (size_t)(row0 + lane) * ldo + col);
+          } else if (lane < rows_valid) {
+            float* dst = (float*)out + (size_t)(row0 + lane) * ldo + col;
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col + j < N) dst[j] = v[j];
+          }
+        }
         else if (lane < rows_valid)
           store_row_bf16(v, (__nv_bfloat16*)out + (size_t)(row0 + lane) * ldo + col, N - col, ((ldo | col) & 7) == 0);
       }
@@ -139,7 +138,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     void* __restrict__ out, int ldo, int M, int N, int K, int inter, int m_tiles, int num_tiles,
                     int* __restrict__ error) {
   extern __shared__ unsigned char raw[];
-  auto& sm = *reinterpret_cast<GemmShared<BN, STAGES, EPI == GEMM_EPI_F32>*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
+  auto& sm = *reinterpret_cast<GemmShared<BN, STAGES>*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
   constexpr uint32_t TMEM_COLS = 512;   // two accumulators, the second at column 256
   constexpr uint32_t ACC_STRIDE = 256;
   constexpr uint32_t STAGE_BYTES = (kGemmBM + BN) * kGemmBK * 2;
@@ -236,7 +235,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       const int m0 = (tile % m_tiles) * kGemmBM;
       const int n0 = (tile / m_tiles) * PER_TILE;
       const uint32_t lane_base = tmem + buffer * ACC_STRIDE + ((uint32_t)(quadrant * 32) << 16);
-      store_accumulator<BN, EPI>(lane_base, sm.stage[EPI == GEMM_EPI_F32 ? warp - 2 : 0], m0 + quadrant * 32, lane, n0, out, ldo, M, N, inter, part);
+      store_accumulator<BN, EPI>(lane_base, m0 + quadrant * 32, lane, n0, out, ldo, M, N, inter, part);
       // This warp has read its part of the accumulator: hand the buffer back to the MMA issuer.
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
@@ -265,7 +264,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 //   accum_full[b]    in each CTA: tcgen05.commit after a tile's last MMA arrives on both
 //   accum_empty[b]   in the first CTA: the sixteen epilogue warps of the pair arrive on it
 // ---------------------------------------------------------------------------------------------------------------
-template <int BN, int STAGES, int KB, bool STAGING>
+template <int BN, int STAGES, int KB>
 struct PairShared {
   alignas(1024) unsigned char a[STAGES][KB][kGemmBM * kGemmBK * 2];  // KB boxes of 64 along K per stage
   alignas(1024) unsigned char b[STAGES][KB][(BN / 2) * kGemmBK * 2];
@@ -275,7 +274,6 @@ struct PairShared {
   uint64_t accum_empty[2];
   uint32_t tmem_base;
   uint32_t failed;
-  float stage[STAGING ? 8 : 1][32 * 33];  // a 32 x 32 block per epilogue warp (float32 results), see store_block
 };
 
 template <int BN, int STAGES, int KB, int EPI>
@@ -284,7 +282,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                          void* __restrict__ out, int ldo, int M, int N, int K, int inter, int m_tiles, int num_tiles,
                          int* __restrict__ error) {
   extern __shared__ unsigned char raw[];
-  auto& sm = *reinterpret_cast<PairShared<BN, STAGES, KB, EPI == GEMM_EPI_F32>*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
+  auto& sm = *reinterpret_cast<PairShared<BN, STAGES, KB>*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
   constexpr uint32_t TMEM_COLS = 512;   // two accumulators, the second at column 256
   constexpr uint32_t ACC_STRIDE = 256;
   constexpr uint32_t STAGE_BYTES_PAIR = 2 * KB * (kGemmBM + BN / 2) * kGemmBK * 2;
@@ -390,7 +388,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       const int m0 = (tile % m_tiles) * 2 * kGemmBM + (int)rank * kGemmBM;
       const int n0 = (tile / m_tiles) * PER_TILE;
       const uint32_t lane_base = tmem + buffer * ACC_STRIDE + ((uint32_t)(quadrant * 32) << 16);
-      store_accumulator<BN, EPI>(lane_base, sm.stage[EPI == GEMM_EPI_F32 ? warp - 2 : 0], m0 + quadrant * 32, lane, n0, out, ldo, M, N, inter, part);
+      store_accumulator<BN, EPI>(lane_base, m0 + quadrant * 32, lane, n0, out, ldo, M, N, inter, part);
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(cluster_address(&sm.accum_empty[buffer], 0));
@@ -594,7 +592,7 @@ gemm_tcgen05_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
 template <int BN, int STAGES, int EPI>
 static int launch_gemm(const CUtensorMap& map_a, const CUtensorMap& map_b, void* out, int ldo, int M, int N, int K,
                        int inter, int sm_count, int* error, cudaStream_t stream) {
-  const size_t shared = sizeof(GemmShared<BN, STAGES, EPI == GEMM_EPI_F32>) + 1024;
+  const size_t shared = sizeof(GemmShared<BN, STAGES>) + 1024;
   static bool configured = false;
   if (!configured) {
     const cudaError_t err =
@@ -616,7 +614,7 @@ static int launch_gemm(const CUtensorMap& map_a, const CUtensorMap& map_b, void*
 template <int BN, int STAGES, int KB, int EPI>
 static int launch_gemm_pair(const CUtensorMap& map_a, const CUtensorMap& map_b, void* out, int ldo, int M, int N, int K,
                             int inter, int sm_count, int* error, cudaStream_t stream) {
-  const size_t shared = sizeof(PairShared<BN, STAGES, KB, EPI == GEMM_EPI_F32>) + 1024;
+  const size_t shared = sizeof(PairShared<BN, STAGES, KB>) + 1024;
   static bool configured = false;
   static int resident_pairs = 0;  // pairs that can run at the same time (an SM left over in a GPC hosts none)
   if (!configured) {
@@ -696,7 +694,7 @@ extern "C" int distie_gemm_tcgen05(const void* x, int ldx, const void* w, void* 
     if ((status = make_map(&map_b, w, N, K, K, width / 2)) != 0) return status;
 #define DISTIE_GEMM_PAIR(BNV, STAGESV)                                                                                   \
   return epi == GEMM_EPI_F32                                                                                             \
-             ? launch_gemm_pair<BNV, STAGESV - 1, 1, GEMM_EPI_F32>(map_a, map_b, out, ldo, M, N, K, 0, sm_count, error, stream) \
+             ? launch_gemm_pair<BNV, STAGESV, 1, GEMM_EPI_F32>(map_a, map_b, out, ldo, M, N, K, 0, sm_count, error, stream) \
              : launch_gemm_pair<BNV, STAGESV, 1, GEMM_EPI_BF16>(map_a, map_b, out, ldo, M, N, K, 0, sm_count, error, stream)
     if (width == 256) { DISTIE_GEMM_PAIR(256, 6); }
     if (width == 192) { DISTIE_GEMM_PAIR(192, 7); }
@@ -712,10 +710,9 @@ extern "C" int distie_gemm_tcgen05(const void* x, int ldx, const void* w, void* 
   const int width = pick_tile_width(M, N, kGemmBM, sm_count);
   status = make_map(&map_b, w, N, K, K, width);
   if (status != 0) return status;
-  // (the float32 epilogue stages its stores in shared memory: one stage of operands fewer)
 #define DISTIE_GEMM(BNV, STAGESV)                                                                                       \
   return epi == GEMM_EPI_F32                                                                                            \
-             ? launch_gemm<BNV, STAGESV - 1, GEMM_EPI_F32>(map_a, map_b, out, ldo, M, N, K, 0, sm_count, error, stream) \
+             ? launch_gemm<BNV, STAGESV, GEMM_EPI_F32>(map_a, map_b, out, ldo, M, N, K, 0, sm_count, error, stream) \
              : launch_gemm<BNV, STAGESV, GEMM_EPI_BF16>(map_a, map_b, out, ldo, M, N, K, 0, sm_count, error, stream)
   if (width == 256) { DISTIE_GEMM(256, 4); }
   if (width == 192) { DISTIE_GEMM(192, 5); }
