@@ -393,26 +393,63 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_row_strid
 }
 
 // Combines the partial results of the splits of one (token, head): maxima are base-2 exponents.
-__global__ void __launch_bounds__(128)
+// A row of head_dim floats takes head_dim / 4 threads (four floats each); the block's 256 threads
+// hold 256 / (head_dim / 4) rows at a time, so that the loads of many splits are in flight together,
+// and the rows meet in shared memory.  The order of the additions is fixed by the split count alone.
+constexpr int kMergeThreads = 256;
+
+__global__ void __launch_bounds__(kMergeThreads)
 attention_decode_mma_merge_kernel(const float* __restrict__ scratch_o, const float* __restrict__ scratch_ml,
                                   __nv_bfloat16* __restrict__ out, int out_row_stride, int num_heads, int head_dim,
                                   int num_splits) {
+  __shared__ float sh_max[kMergeThreads / 32];
+  __shared__ float sh_l[kMergeThreads / 16];
+  __shared__ float4 sh_acc[kMergeThreads];
   grid_dependency_release();
   grid_dependency_wait();
   const int t = blockIdx.x, head = blockIdx.y;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const size_t row0 = ((size_t)t * num_heads + head) * num_splits;
+  const int per_row = head_dim / 4;             // threads of one split's row (16 or 32)
+  const int rows = kMergeThreads / per_row;     // splits in flight
+  const int mine = threadIdx.x / per_row, piece = threadIdx.x % per_row;
+
   float m_all = -INFINITY;
-  for (int s = 0; s < num_splits; ++s) m_all = fmaxf(m_all, __ldcg(scratch_ml + (row0 + s) * 2));
-  for (int e = threadIdx.x; e < head_dim; e += blockDim.x) {
-    float l_all = 0.f, acc = 0.f;
-    for (int s = 0; s < num_splits; ++s) {
-      const float ms = __ldcg(scratch_ml + (row0 + s) * 2);
-      const float weight = ms == -INFINITY ? 0.f : exp2f(ms - m_all);
-      l_all += __ldcg(scratch_ml + (row0 + s) * 2 + 1) * weight;
-      acc += __ldcg(scratch_o + (row0 + s) * head_dim + e) * weight;
+  for (int s = threadIdx.x; s < num_splits; s += kMergeThreads) m_all = fmaxf(m_all, __ldcg(scratch_ml + (row0 + s) * 2));
+#pragma unroll
+  for (int d = 16; d >= 1; d >>= 1) m_all = fmaxf(m_all, __shfl_xor_sync(0xffffffffu, m_all, d));
+  if (lane == 0) sh_max[warp] = m_all;
+  __syncthreads();
+#pragma unroll
+  for (int w = 0; w < kMergeThreads / 32; ++w) m_all = fmaxf(m_all, sh_max[w]);
+
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  float l = 0.f;
+#pragma unroll 4
+  for (int s = mine; s < num_splits; s += rows) {
+    const float2 ml = __ldcg(reinterpret_cast<const float2*>(scratch_ml + (row0 + s) * 2));
+    const float4 o = load4_cg(scratch_o + (row0 + s) * head_dim + piece * 4);
+    const float weight = ml.x == -INFINITY ? 0.f : exp2f(ml.x - m_all);
+    l += ml.y * weight;
+    acc.x += o.x * weight; acc.y += o.y * weight; acc.z += o.z * weight; acc.w += o.w * weight;
+  }
+  sh_acc[threadIdx.x] = acc;
+  if (piece == 0) sh_l[mine] = l;
+  __syncthreads();
+  if (threadIdx.x < per_row) {
+    float l_all = 0.f;
+    float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int r = 0; r < rows; ++r) {
+      const float4 part = sh_acc[r * per_row + piece];
+      sum.x += part.x; sum.y += part.y; sum.z += part.z; sum.w += part.w;
+      l_all += sh_l[r];
     }
-    out[(size_t)t * out_row_stride + (size_t)head * head_dim + e] =
-        __float2bfloat16_rn(l_all > 0.f ? acc / l_all : 0.f);
+    const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
+    __nv_bfloat162 lo = __floats2bfloat162_rn(sum.x * inv, sum.y * inv), hi = __floats2bfloat162_rn(sum.z * inv, sum.w * inv);
+    uint2 packed;
+    packed.x = *reinterpret_cast<uint32_t*>(&lo);
+    packed.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(out + (size_t)t * out_row_stride + (size_t)head * head_dim + piece * 4) = packed;
   }
 }
 
@@ -435,7 +472,8 @@ extern "C" int distie_attention_decode_mma(const void* q, int q_row_stride, void
                                            float scale, int num_splits, int* error, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (num_heads < 1 || num_kv_heads < 1 || num_heads % num_kv_heads != 0 || page_size < 1 || table_width < 1 ||
-      num_splits < 1 || num_splits > 65535 || (num_splits > kMmaDecodeClusterSplits && scratch == nullptr) || (q_row_stride & 7))
+      num_splits < 1 || num_splits > 65535 || (num_splits > kMmaDecodeClusterSplits && scratch == nullptr) || (q_row_stride & 7) ||
+      (out_row_stride & 3))
     return DISTIE_ERR_ARG;
   if (head_dim != 64 && head_dim != 128) return DISTIE_ERR_UNSUPPORTED;
   const int group = num_heads / num_kv_heads;
@@ -502,7 +540,7 @@ extern "C" int distie_attention_decode_mma(const void* q, int q_row_stride, void
   if (err != cudaSuccess) return (int)err;
   if (num_splits > 1 && !cluster_merge) {
     const dim3 merge_grid(tokens, num_heads);
-    err = launch_dependent_family(8, attention_decode_mma_merge_kernel, merge_grid, dim3(head_dim >= 128 ? 128 : 64), 0, stream,
+    err = launch_dependent_family(8, attention_decode_mma_merge_kernel, merge_grid, dim3(kMergeThreads), 0, stream,
                            (const float*)scratch_o, (const float*)scratch_ml, (__nv_bfloat16*)out, out_row_stride,
                            num_heads, head_dim, num_splits);
     if (err != cudaSuccess) return (int)err;
