@@ -7,17 +7,27 @@
 //                    Q and K are K-major tiles in shared memory (TMA, 128-byte swizzle); S lands in
 //                    tensor memory (two buffers of 128 columns, so the next S is computed while the
 //                    softmax of this one runs)
-//   P = softmax part eight warps, two threads per query row (64 keys each; the row maxima and, at the end,
-//                    the row sums of the two meet in shared memory): tcgen05.ld of the row, mask,
-//                    running maximum and sum in float32, exp2, P as bfloat16 into shared memory in the
-//                    K-major swizzled layout of an A operand
-//   O += P V         tcgen05.mma, N = head_dim, reduction over the 128 keys; V stays as the cache holds
-//                    it (a key per row, head_dim contiguous), which for this product is an MN-major
-//                    B operand; O accumulates in tensor memory
+//   P = softmax part eight warps in two groups of four: group 0 owns keys 0..63 of every block, group 1 keys
+//                    64..127, a thread per query row in each.  The groups are two softmax streams of
+//                    their own -- running maximum, sum and an O accumulator each -- and never wait
+//                    for one another inside the loop, so one group's exponentials (16 a clock and SM)
+//                    overlap the other's loads, maxima and waits.  P goes back into the first 32 of the
+//                    group's 64 columns of S as bfloat16, two keys to a column
+//   O_g += P_g V_g   tcgen05.mma with P as the A operand straight from tensor memory, N = head_dim,
+//                    reduction over the group's 64 keys; V stays as the cache holds it (a key per row,
+//                    head_dim contiguous), which for this product is an MN-major B operand
+//   end              the two partial results of a row are brought to a common maximum, added and
+//                    divided by the common sum
+//
+//   tensor memory    S0 | S1 | O of group 0 | O of group 1 (128 + 128 + head_dim + head_dim columns)
+//   MMA order        PV0(j), PV1(j), S(j + 2): the S that overwrites a block's P is issued behind the
+//                    products that read it (MMAs of one thread execute in the order of issue)
 //
 // Keys and values come straight from their pages: a page of the cache is page_size rows of head_dim, so
 // one TMA box of [page_size x 64] per page and half of the head fills its rows of the 128-key tile.
-// Pages past the last key the tile needs are not fetched.
+// Pages past the last key the tile needs are not fetched.  The page ids of a block are read from the
+// table one block ahead of their use, by two producer warps (K and V), so that neither the look-up nor
+// the other operand's stage stands between a stage becoming free and its copies being issued.
 //
 // The running maximum is only raised when a row's new maximum exceeds the one in use by more than 8
 // (in base-2 units): P then stays below 2^8, the sums stay exact in float32, and O needs to be read,
@@ -26,12 +36,13 @@
 // Rows of V that belong to no key of the request (the rest of its last page, pages that were not
 // fetched) are set to zero in shared memory before the product, since 0 * garbage need not be 0.
 //
-//   warp 0      producer: TMA loads of Q, then K and V blocks through two stages each (a lane per page)
+//   warp 0      producer: TMA loads of Q, then K blocks through two stages (a lane per page)
 //   warp 1      allocates tensor memory; one lane issues the MMAs and commits them to mbarriers
-//   warps 2..9  softmax, correction of O, final normalisation and store
+//   warps 2..9  softmax, correction of O, final merge and store
+//   warp 10     producer of the V blocks, three stages
 //
 // Every wait on an mbarrier is bounded; when one runs out the CTA sets the error word to 6, every role
-// stops at its next wait, the producer waits (bounded) for its copies in flight, and tensor memory is
+// stops at its next wait, the producers wait (bounded) for their copies in flight, and tensor memory is
 // released.  head_dim 64 or 128; page sizes 8, 16, ..., 128.
 #include "tcgen05.cuh"
 
@@ -39,26 +50,27 @@ namespace distie {
 
 constexpr int kAttnRows = 128;     // query rows of a tile = lanes of tensor memory
 constexpr int kAttnKeys = 128;     // keys per block
+constexpr int kAttnGroupKeys = kAttnKeys / 2;  // keys of a block that one softmax group owns
 constexpr int kAttnSoftmaxWarps = 8;
-constexpr int kAttnThreads = (2 + kAttnSoftmaxWarps) * 32;
-constexpr int kAttnStages = 2;
+constexpr int kAttnVProducerWarp = 2 + kAttnSoftmaxWarps;  // behind the softmax warps
+constexpr int kAttnThreads = (3 + kAttnSoftmaxWarps) * 32;
+constexpr int kAttnKStages = 2, kAttnVStages = 3;  // V of a block is needed a block time after its stage is freed, K two
 constexpr int kAttnHalf = kAttnRows * 128;  // bytes of one [128 rows x 64 elements] swizzled half tile
 constexpr float kAttnRaise = 8.f;  // the maximum in use is raised when a row exceeds it by this much (base 2)
 
 template <int D>
 struct AttnShared {
   alignas(1024) unsigned char q[kAttnRows * D * 2];
-  alignas(1024) unsigned char k[kAttnStages][kAttnKeys * D * 2];
-  alignas(1024) unsigned char v[kAttnStages][kAttnKeys * D * 2];
-  alignas(1024) unsigned char p[kAttnRows * kAttnKeys * 2];
+  alignas(1024) unsigned char k[kAttnKStages][kAttnKeys * D * 2];
+  alignas(1024) unsigned char v[kAttnVStages][kAttnKeys * D * 2];
   uint64_t q_full;
-  uint64_t k_full[kAttnStages], k_empty[kAttnStages];
-  uint64_t v_full[kAttnStages], v_empty[kAttnStages];
-  uint64_t s_full[2], s_empty[2];
-  uint64_t p_full, pv_done;
-  uint64_t max_ready[2], sum_ready;
-  float row_max[2][2][kAttnRows];  // [S buffer][side][row]: the maxima the two threads of a row exchange
-  float row_sum[2][kAttnRows];
+  uint64_t k_full[kAttnKStages], k_empty[kAttnKStages];
+  uint64_t v_full[kAttnVStages], v_empty[kAttnVStages];
+  uint64_t s_full[2];
+  uint64_t p_full[2][2];  // [group][S buffer]
+  uint64_t pv_done[2];    // [group]
+  uint64_t merge_ready;
+  float row_max[2][kAttnRows], row_sum[2][kAttnRows];  // [group][row]: what the groups exchange at the end
   uint32_t tmem_base;
   uint32_t failed;
 };
@@ -82,26 +94,29 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   auto& sm = *reinterpret_cast<AttnShared<D>*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
   constexpr int HALVES = D / 64;
   constexpr uint32_t TMEM_COLS = 512;
-  constexpr uint32_t O_COL = 256;
+  constexpr uint32_t O_COL = 256;  // S0 | S1 | O of group 0 | O of group 1
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   volatile uint32_t* failed = &sm.failed;
 
   if (threadIdx.x == 0) {
     mbar_init(&sm.q_full, 1);
-    for (int s = 0; s < kAttnStages; ++s) {
+    for (int s = 0; s < kAttnKStages; ++s) {
       mbar_init(&sm.k_full[s], 1);
       mbar_init(&sm.k_empty[s], 1);
+    }
+    for (int s = 0; s < kAttnVStages; ++s) {
       mbar_init(&sm.v_full[s], 1);
       mbar_init(&sm.v_empty[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&sm.s_full[b], 1);
-      mbar_init(&sm.s_empty[b], kAttnSoftmaxWarps);  // one arrival per softmax warp
-      mbar_init(&sm.max_ready[b], kAttnSoftmaxWarps);
+      // One barrier per group and S buffer: a group may be a block ahead of the MMA issuer, never two
+      // on one buffer (the S of block j + 2 is issued only after the P of block j has been seen).
+      mbar_init(&sm.p_full[0][b], kAttnSoftmaxWarps / 2);  // one arrival per warp of the group
+      mbar_init(&sm.p_full[1][b], kAttnSoftmaxWarps / 2);
+      mbar_init(&sm.pv_done[b], 1);
     }
-    mbar_init(&sm.sum_ready, kAttnSoftmaxWarps);
-    mbar_init(&sm.p_full, kAttnSoftmaxWarps);
-    mbar_init(&sm.pv_done, 1);
+    mbar_init(&sm.merge_ready, kAttnSoftmaxWarps);
     sm.failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -131,156 +146,149 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   const int blocks = last_pos / kAttnKeys - block_first + 1;
   const int page_size = 1 << page_shift;
 
-  if (warp == 0) {
-    // ---- producer: lane pg looks up page pg of a block and issues its copies -------------------------------
-    if (lane == 0) {
+  if (warp == 0 || warp == kAttnVProducerWarp) {
+    // ---- producers: warp 0 fetches Q and K, the last warp V; lane pg takes page pg of a block -----------------
+    const bool for_k = warp == 0;
+    if (for_k && lane == 0) {
       mbar_expect_tx(&sm.q_full, kAttnRows * D * 2);
       for (int h = 0; h < HALVES; ++h) tma_load_2d(sm.q + h * kAttnHalf, &map_q, &sm.q_full, head * D + h * 64, t0);
     }
     const int* table = block_table + (size_t)seat * table_width;
     const int pages_per_block = kAttnKeys >> page_shift;  // at most 16
-    int issued_k = 0, issued_v = 0;  // blocks whose K (V) copies have been issued
+    const int stages = for_k ? kAttnKStages : kAttnVStages;
+    const CUtensorMap* map = for_k ? &map_k : &map_v;
+    uint64_t* full = for_k ? sm.k_full : sm.v_full;
+    uint64_t* empty = for_k ? sm.k_empty : sm.v_empty;
+    auto pages_of = [&](int j) {  // pages of block j that hold keys the tile needs
+      return min(pages_per_block, ((last_pos - (block_first + j) * kAttnKeys) >> page_shift) + 1);
+    };
+    auto read_table = [&](int j) {  // this lane's page of block j, -1 beyond the block's pages
+      if (j >= blocks) return -1;
+      const int column = (((block_first + j) * kAttnKeys) >> page_shift) + lane;
+      return (lane < pages_of(j) && column < table_width) ? __ldg(table + column) : -1;
+    };
+    int issued = 0;
     bool ok = true;
-    // Pages of block j that hold keys the tile needs, this lane's page and its first row in the cache.
-    int count = 0, row = 0;
-    auto look_up = [&](int j) {
-      const int key0 = (block_first + j) * kAttnKeys;
-      count = min(pages_per_block, ((last_pos - key0) >> page_shift) + 1);
-      const int column = (key0 >> page_shift) + lane;
-      const int page = (lane < count && column < table_width) ? table[column] : -1;
-      row = (page * num_kv_heads + kv_head) * page_size;
+    int page_ahead = read_table(0);
+    for (int j = 0; j < blocks && ok; ++j) {
+      const int s = j % stages, use = j / stages;
+      const int page = page_ahead;
+      page_ahead = read_table(j + 1);
+      const int count = pages_of(j);
       if (__any_sync(0xffffffffu, lane < count && (page < 0 || page >= num_pages))) {
         if (lane == 0 && error) atomicExch(error, 4);
-        return false;
+        ok = false;
+        break;
       }
-      return true;
-    };
-    auto copy = [&](unsigned char* stage, const CUtensorMap* map, uint64_t* full, uint64_t* empty, int j, int& issued) {
-      if (!__all_sync(0xffffffffu, mbar_wait_unless(empty, ((j >> 1) & 1) ^ 1, failed))) return false;
-      if (lane == 0) mbar_expect_tx(full, (uint32_t)count * page_size * D * 2);
+      if (!__all_sync(0xffffffffu, mbar_wait_unless(&empty[s], (use & 1) ^ 1, failed))) { ok = false; break; }
+      if (lane == 0) mbar_expect_tx(&full[s], (uint32_t)count * page_size * D * 2);
       __syncwarp();
-      if (lane < count)
-        for (int h = 0; h < HALVES; ++h)
-          tma_load_2d(stage + h * kAttnHalf + lane * page_size * 128, map, full, h * 64, row);
-      issued = j + 1;
-      return true;
-    };
-    // K runs a block ahead of V: K of block j + 1 only waits for S of block j - 1, which is done early,
-    // while V of block j waits for the product of block j - 2.
-    ok = look_up(0) && copy(sm.k[0], &map_k, &sm.k_full[0], &sm.k_empty[0], 0, issued_k);
-    for (int j = 0; j < blocks && ok; ++j) {
-      const int s = j & 1;
-      const int count_now = count, row_now = row;
-      if (j + 1 < blocks) {
-        ok = look_up(j + 1) && copy(sm.k[s ^ 1], &map_k, &sm.k_full[s ^ 1], &sm.k_empty[s ^ 1], j + 1, issued_k);
-        if (!ok) break;
+      if (lane < count) {
+        unsigned char* stage = (for_k ? sm.k[s] : sm.v[s]) + lane * page_size * 128;
+        const int row = (page * num_kv_heads + kv_head) * page_size;
+        for (int h = 0; h < HALVES; ++h) tma_load_2d(stage + h * kAttnHalf, map, &full[s], h * 64, row);
       }
-      const int count_next = count, row_next = row;
-      count = count_now;
-      row = row_now;
-      ok = copy(sm.v[s], &map_v, &sm.v_full[s], &sm.v_empty[s], j, issued_v);
-      count = count_next;
-      row = row_next;
+      issued = j + 1;
     }
     if (!ok) atomicExch(&sm.failed, 1u);
     if (sm.failed && lane == 0) {
       // Copies already under way must land before the CTA may leave: wait (bounded) for the last few.
-      mbar_wait(&sm.q_full, 0);
-      for (int j = max(0, issued_k - 2); j < issued_k; ++j) mbar_wait(&sm.k_full[j & 1], (j >> 1) & 1);
-      for (int j = max(0, issued_v - 2); j < issued_v; ++j) mbar_wait(&sm.v_full[j & 1], (j >> 1) & 1);
+      if (for_k) mbar_wait(&sm.q_full, 0);
+      for (int j = max(0, issued - stages); j < issued; ++j) mbar_wait(&full[j % stages], (j / stages) & 1);
     }
   } else if (warp == 1) {
     // ---- MMA issuer ------------------------------------------------------------------------------------------
     if (lane == 0) {
       constexpr uint32_t idesc_s = instr_desc(kAttnKeys);
       constexpr uint32_t idesc_o = instr_desc(D, true);
-      const uint64_t q_desc = smem_desc(sm.q), p_desc = smem_desc(sm.p);
+      const uint64_t q_desc = smem_desc(sm.q);
       bool ok = mbar_wait_unless(&sm.q_full, 0, failed);
+      // S of block j into buffer j & 1.  Both groups have that buffer's last S in registers and their P
+      // consumed: the caller has seen both P of block j - 2 and issued the products that read them.
       auto issue_s = [&](int j) {
-        const int s = j & 1;
-        if (!mbar_wait_unless(&sm.k_full[s], (j >> 1) & 1, failed)) return false;
-        if (!mbar_wait_unless(&sm.s_empty[s], ((j >> 1) & 1) ^ 1, failed)) return false;
+        const int s = j & 1, ks = j % kAttnKStages;
+        if (!mbar_wait_unless(&sm.k_full[ks], (j / kAttnKStages) & 1, failed)) return false;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint64_t k_desc = smem_desc(sm.k[s]);
+        const uint64_t k_desc = smem_desc(sm.k[ks]);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint64_t step = (uint64_t)(((kk >> 2) * kAttnHalf + (kk & 3) * 32) >> 4);
           umma_bf16(tmem + s * kAttnKeys, q_desc + step, k_desc + step, idesc_s, kk > 0 ? 1u : 0u);
         }
-        umma_commit(&sm.k_empty[s]);
+        umma_commit(&sm.k_empty[ks]);
         umma_commit(&sm.s_full[s]);
         return true;
       };
       ok = ok && issue_s(0);
+      if (ok && blocks > 1) ok = issue_s(1);
       for (int j = 0; j < blocks && ok; ++j) {
-        const int s = j & 1;
-        if (j + 1 < blocks) ok = issue_s(j + 1);
-        if (!ok) break;
-        if (!mbar_wait_unless(&sm.p_full, j & 1, failed)) { ok = false; break; }
-        if (!mbar_wait_unless(&sm.v_full[s], (j >> 1) & 1, failed)) { ok = false; break; }
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint64_t v_desc = smem_desc_mn(sm.v[s], kAttnHalf, 1024);
+        const int s = j & 1, vs = j % kAttnVStages;
+        if (!mbar_wait_unless(&sm.v_full[vs], (j / kAttnVStages) & 1, failed)) { ok = false; break; }
+        const uint64_t v_desc = smem_desc_mn(sm.v[vs], kAttnHalf, 1024);
 #pragma unroll
-        for (int kk = 0; kk < kAttnKeys / 16; ++kk) {
-          const uint64_t p_step = (uint64_t)(((kk >> 2) * kAttnHalf + (kk & 3) * 32) >> 4);
-          const uint64_t v_step = (uint64_t)((kk * 16 * 128) >> 4);
-          umma_bf16(tmem + O_COL, p_desc + p_step, v_desc + v_step, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+        for (int g = 0; g < 2; ++g) {
+          if (!mbar_wait_unless(&sm.p_full[g][s], (j >> 1) & 1, failed)) { ok = false; break; }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+          for (int kk = 0; kk < kAttnGroupKeys / 16; ++kk) {
+            // P of the group: 32 columns at the start of its half of the S buffer, 16 keys are 8 columns;
+            // its keys are rows g * 64 ... of the V block.
+            const uint64_t v_step = (uint64_t)(((g * kAttnGroupKeys + kk * 16) * 128) >> 4);
+            umma_bf16_ts(tmem + O_COL + g * D, tmem + s * kAttnKeys + g * kAttnGroupKeys + kk * 8, v_desc + v_step,
+                         idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+          }
+          umma_commit(&sm.pv_done[g]);
         }
-        umma_commit(&sm.v_empty[s]);
-        umma_commit(&sm.pv_done);
+        if (!ok) break;
+        umma_commit(&sm.v_empty[vs]);
+        if (j + 2 < blocks) ok = issue_s(j + 2);
       }
       if (!ok) atomicExch(&sm.failed, 1u);
     }
-  } else {
-    // ---- softmax, correction, epilogue: two threads per query row, 64 keys (and half of O) each ---------------
+  } else if (warp < kAttnVProducerWarp) {
+    // ---- softmax, correction, epilogue: group g owns 64 keys of every block, thread = query row ---------------
     const int quadrant = warp & 3;
-    const int side = (warp - 2) >> 2;  // which half of the block's keys and of O's columns
+    const int g = (warp - 2) >> 2;
     const int r = quadrant * 32 + lane;
     const uint32_t lane_base = tmem + ((uint32_t)(quadrant * 32) << 16);
+    const uint32_t o_addr = lane_base + O_COL + g * D;
     const int limit = min(pos0 + r, last_pos);                      // newest key this row may see
     const int oldest = window > 0 ? pos0 + r - window + 1 : 0;      // oldest key inside its window
-    constexpr int SIDE_KEYS = kAttnKeys / 2, SIDE_DIMS = D / 2;
     float m_used = -INFINITY, l = 0.f;
     bool ok = true;
-    // The warp waits as one: the tensor-memory instructions below need all of its lanes.
+    // One lane polls the barrier; the warp continues as one (the tensor-memory instructions need all lanes).
     auto wait_all = [&](uint64_t* bar, uint32_t parity) {
-      return __all_sync(0xffffffffu, mbar_wait_unless(bar, parity, failed));
+      int done = 1;
+      if (lane == 0) done = mbar_wait_unless(bar, parity, failed) ? 1 : 0;
+      done = __shfl_sync(0xffffffffu, done, 0);
+      __syncwarp();
+      return done != 0;
     };
     for (int j = 0; j < blocks; ++j) {
-      const int s = j & 1;
-      const int key0 = (block_first + j) * kAttnKeys + side * SIDE_KEYS;  // first key of this thread's half
+      const int s = j & 1, vs = j % kAttnVStages;
+      const int block_key0 = (block_first + j) * kAttnKeys;
+      const int key0 = block_key0 + g * kAttnGroupKeys;  // first key of this group's part
+      const uint32_t s_addr = lane_base + s * kAttnKeys + g * kAttnGroupKeys;
       if (!wait_all(&sm.s_full[s], (j >> 1) & 1)) { ok = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       // No row of the tile needs a mask when every key of the block is old enough and inside every window.
-      const int block_key0 = (block_first + j) * kAttnKeys;
       const bool unmasked =
           block_key0 + kAttnKeys - 1 <= pos0 && (window <= 0 || block_key0 >= last_pos - window + 1);
-      const uint32_t s_addr = lane_base + s * kAttnKeys + side * SIDE_KEYS;
-      // Pass 1: the row's maximum over this half of the block (kept in registers for pass 2); the two
-      // halves meet in shared memory.  Four running maxima, so that the chain of dependent operations is short.
-      uint32_t sv[SIDE_KEYS];
+      uint32_t sv[kAttnGroupKeys];
       tmem_load_64(s_addr, sv);
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-      // This warp has its part of S in registers: the buffer may be overwritten.
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&sm.s_empty[s]);
       if (!unmasked) {
 #pragma unroll
-        for (int i = 0; i < SIDE_KEYS; ++i) {
+        for (int i = 0; i < kAttnGroupKeys; ++i) {
           const int key = key0 + i;
           if (!(key <= limit && key >= oldest)) sv[i] = 0xff800000u;  // -inf
         }
       }
+      // The row's maximum over the group's keys: four running maxima keep the chain of dependent operations short.
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int i = 0; i < SIDE_KEYS; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sv[i]));
-      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-      sm.row_max[s][side][r] = mx;
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&sm.max_ready[s]);  // release: the store above is ordered before it
-      if (!wait_all(&sm.max_ready[s], (j >> 1) & 1)) { ok = false; break; }
-      mx = fmaxf(mx, sm.row_max[s][side ^ 1][r]);
+      for (int i = 0; i < kAttnGroupKeys; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sv[i]));
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       const float m_new = fmaxf(m_used, mx * scale_log2);
       const bool raise = m_new > m_used + kAttnRaise || (m_used == -INFINITY && m_new > -INFINITY);
       float corr = 1.f;
@@ -289,84 +297,87 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         m_used = m_new;
       }
       l *= corr;
-      const bool any_raise = __any_sync(0xffffffffu, raise);
-      // P and O are in use by the product of the block before this one until it has completed.
-      if (j > 0) {
-        if (!wait_all(&sm.pv_done, (j - 1) & 1)) { ok = false; break; }
+      // The group's O is in use by its product of the block before this one until that has completed.
+      if (j > 0 && __any_sync(0xffffffffu, raise)) {
+        if (!wait_all(&sm.pv_done[g], (j - 1) & 1)) { ok = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (any_raise) {
 #pragma unroll
-          for (int c0 = 0; c0 < SIDE_DIMS; c0 += 32) {
-            uint32_t v[32];
-            tmem_load_32(lane_base + O_COL + side * SIDE_DIMS + c0, v);
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        for (int c0 = 0; c0 < D; c0 += 32) {
+          uint32_t v[32];
+          tmem_load_32(o_addr + c0, v);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * corr);
-            tmem_store_32(lane_base + O_COL + side * SIDE_DIMS + c0, v);
-          }
-          asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+          for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * corr);
+          tmem_store_32(o_addr + c0, v);
         }
       }
-      // Pass 2: P = exp2(S * scale - maximum in use), its sum, and P as bfloat16 into the A-operand tile
-      // (this thread's 64 keys are one swizzled half of it).  A masked S is -inf and gives 0.
+      // P = exp2(S * scale - maximum in use) and its sum; P as bfloat16, two keys to a column, into the
+      // first 32 of the group's 64 columns of this S buffer (the thread has its S in registers).  A
+      // masked S is -inf and gives 0.
       const float shift = m_used == -INFINITY ? 0.f : m_used;
       float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-      unsigned char* row_base = sm.p + side * kAttnHalf + r * 128;
+      uint32_t packed[kAttnGroupKeys / 2];
 #pragma unroll
-      for (int c0 = 0; c0 < SIDE_KEYS; c0 += 8) {
-        uint32_t packed[4];
-#pragma unroll
-        for (int i = 0; i < 8; i += 2) {
-          const float p0 = exp2_approx(fmaf(__uint_as_float(sv[c0 + i]), scale_log2, -shift));
-          const float p1 = exp2_approx(fmaf(__uint_as_float(sv[c0 + i + 1]), scale_log2, -shift));
-          sum4[(i >> 1) & 3] += p0 + p1;
-          const __nv_bfloat162 pair = __floats2bfloat162_rn(p0, p1);
-          packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&pair);
-        }
-        const int chunk = c0 >> 3;
-        *reinterpret_cast<uint4*>(row_base + ((chunk ^ (r & 7)) << 4)) =
-            make_uint4(packed[0], packed[1], packed[2], packed[3]);
+      for (int i = 0; i < kAttnGroupKeys; i += 2) {
+        const float p0 = exp2_approx(fmaf(__uint_as_float(sv[i]), scale_log2, -shift));
+        const float p1 = exp2_approx(fmaf(__uint_as_float(sv[i + 1]), scale_log2, -shift));
+        sum4[(i >> 1) & 3] += p0 + p1;
+        const __nv_bfloat162 pair = __floats2bfloat162_rn(p0, p1);
+        packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&pair);
       }
+      tmem_store_32(s_addr, packed);
       l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-      // Rows of V past the last key the tile needs: zero, so that P = 0 gives 0 (side 0 does it).
-      if (block_key0 + kAttnKeys - 1 > last_pos && side == 0) {
-        if (!wait_all(&sm.v_full[s], (j >> 1) & 1)) { ok = false; break; }
-        if (block_key0 + r > last_pos) {
+      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+      // Rows of V past the last key the tile needs: zero, so that P = 0 gives 0.  Each group clears the
+      // rows of its own keys.
+      if (block_key0 + kAttnKeys - 1 > last_pos) {
+        if (!wait_all(&sm.v_full[vs], (j / kAttnVStages) & 1)) { ok = false; break; }
+        const int row = g * kAttnGroupKeys + (r & (kAttnGroupKeys - 1));
+        if (r < kAttnGroupKeys && block_key0 + row > last_pos) {
 #pragma unroll
           for (int h = 0; h < HALVES; ++h) {
-            uint4* dst = reinterpret_cast<uint4*>(sm.v[s] + h * kAttnHalf + r * 128);
+            uint4* dst = reinterpret_cast<uint4*>(sm.v[vs] + h * kAttnHalf + row * 128);
 #pragma unroll
             for (int i = 0; i < 8; ++i) dst[i] = make_uint4(0u, 0u, 0u, 0u);
           }
         }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       }
-      // P (and the zeroed rows) written by this thread become visible to the tensor core's reads.
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
-      if (lane == 0) mbar_arrive(&sm.p_full);
+      if (lane == 0) mbar_arrive(&sm.p_full[g][s]);
     }
     if (!ok) atomicExch(&sm.failed, 1u);
-    // ---- epilogue: O / l; the two sides of a row add their sums -----------------------------------------------
-    sm.row_sum[side][r] = l;
+    // ---- epilogue: the two groups' parts of a row at a common maximum, added, divided by the common sum -------
+    sm.row_max[g][r] = m_used;
+    sm.row_sum[g][r] = l;
     __syncwarp();
-    if (lane == 0) mbar_arrive(&sm.sum_ready);
-    if (ok && wait_all(&sm.sum_ready, 0) && wait_all(&sm.pv_done, (blocks - 1) & 1)) {
+    if (lane == 0) mbar_arrive(&sm.merge_ready);  // release: the stores above are ordered before it
+    if (ok && wait_all(&sm.merge_ready, 0) && wait_all(&sm.pv_done[0], (blocks - 1) & 1) &&
+        wait_all(&sm.pv_done[1], (blocks - 1) & 1)) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      l += sm.row_sum[side ^ 1][r];
-      const float inv = l > 0.f ? 1.f / l : 0.f;
-      __nv_bfloat16* dst = out + (size_t)(t0 + r) * out_row_stride + (size_t)head * D + side * SIDE_DIMS;
+      const float m0 = sm.row_max[0][r], m1 = sm.row_max[1][r];
+      const float m_all = fmaxf(m0, m1);
+      const float w0 = m0 == -INFINITY ? 0.f : exp2_approx(m0 - m_all);
+      const float w1 = m1 == -INFINITY ? 0.f : exp2_approx(m1 - m_all);
+      const float l_all = sm.row_sum[0][r] * w0 + sm.row_sum[1][r] * w1;
+      const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
+      const float f0 = w0 * inv, f1 = w1 * inv;
+      // Group g writes columns g * D / 2 ... of the row, from both accumulators.
+      constexpr int SIDE_DIMS = D / 2;
+      __nv_bfloat16* dst = out + (size_t)(t0 + r) * out_row_stride + (size_t)head * D + g * SIDE_DIMS;
 #pragma unroll
       for (int c0 = 0; c0 < SIDE_DIMS; c0 += 32) {
-        uint32_t v[32];
-        tmem_load_32(lane_base + O_COL + side * SIDE_DIMS + c0, v);
+        uint32_t a[32], b[32];
+        tmem_load_32(lane_base + O_COL + g * SIDE_DIMS + c0, a);
+        tmem_load_32(lane_base + O_COL + D + g * SIDE_DIMS + c0, b);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         if (r < rows) {
 #pragma unroll
           for (int i = 0; i < 32; i += 8) {
             float y[8];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) y[e] = __uint_as_float(v[i + e]) * inv;
+            for (int e = 0; e < 8; ++e) y[e] = __uint_as_float(a[i + e]) * f0 + __uint_as_float(b[i + e]) * f1;
             store8(dst + c0 + i, y);
           }
         }

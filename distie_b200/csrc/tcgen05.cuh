@@ -149,6 +149,18 @@ __device__ __forceinline__ void tmem_store_32(uint32_t taddr, const uint32_t (&r
       : "memory");
 }
 
+// D[tmem] (+)= A[tmem] x B[shared memory]: A is M x 16 of 16-bit values, K-major, two to a 32-bit column
+// (row = lane, 8 columns per MMA).
+__device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t b_desc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 // ---- pairs of CTAs (cta_group::2): one MMA over the shared memory and tensor memory of both CTAs of a cluster ----
 __device__ __forceinline__ uint32_t cluster_cta_rank() {
   uint32_t rank;
