@@ -136,7 +136,7 @@ class ClockSampler:
         return {"sm_mhz": int(statistics.median(busy)) if busy else None, "sm_max_mhz": peak or None, "reasons": sorted(reasons), "samples": len(clocks)}
 
 
-def build_engine(shape: dict, layers: int, max_seqs: int, num_blocks: int):
+def build_engine(shape: dict, layers: int, max_seqs: int, num_blocks: int, max_model_len: int = CONTEXT):
     import torch
 
     from distie_b200.config import EngineConfig, get_architecture
@@ -151,7 +151,7 @@ def build_engine(shape: dict, layers: int, max_seqs: int, num_blocks: int):
     kernels = make_kernels(torch.bfloat16, "cuda:0")
     source = RandomSource(model_tensor_specs(arch.recipe(typed)), seed=0, std=0.02, dtype=torch.bfloat16, device="cuda:0")
     config = EngineConfig(
-        num_blocks=num_blocks, page_size=PAGE, max_seqs=max_seqs, token_budget=2048, max_model_len=CONTEXT,
+        num_blocks=num_blocks, page_size=PAGE, max_seqs=max_seqs, token_budget=2048, max_model_len=max_model_len,
         dtype="bfloat16", decode_graphs=True, device="cuda:0",
     )
     return Engine.assemble(arch, typed, source, kernels, config)
@@ -249,28 +249,32 @@ def time_e2e(engine, batch: int, steps: int, warmup: int) -> dict:
     }
 
 
-def time_prefill(engine, repeats: int = 5) -> dict:
+def time_prefill(engine, repeats: int = 5, past: int = 0) -> dict:
+    """One 2,048-token portion through the step function, behind `past` tokens that are already in the cache."""
     import torch
 
     from distie_b200.engine.batch import BatchEntry
 
     vocab = engine.model.vocab_size
-    prompt = random_prompt(vocab, PREFILL_TOKENS, 7)
+    prompt = random_prompt(vocab, past + PREFILL_TOKENS, 7)
     times = []
     for _ in range(repeats + 2):
         seat = engine.cache.open_seat()
-        assert engine.cache.grow(seat, PREFILL_TOKENS)
+        assert engine.cache.grow(seat, past + PREFILL_TOKENS)
+        for start in range(0, past, PREFILL_TOKENS):  # the earlier portions, untimed
+            engine.runner.step([BatchEntry(seat, prompt[start : min(past, start + PREFILL_TOKENS)], start, ())])
+            engine.runner.finish_step()
         torch.cuda.synchronize()
         begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         begin.record()
-        engine.runner.step([BatchEntry(seat, prompt, 0, (PREFILL_TOKENS - 1,))])
+        engine.runner.step([BatchEntry(seat, prompt[past:], past, (PREFILL_TOKENS - 1,))])
         end.record()
         torch.cuda.synchronize()
         times.append(begin.elapsed_time(end))
         engine.runner.finish_step()
         engine.cache.close_seat(seat)
     ms = statistics.median(times[2:])
-    return {"ms": ms, "tokens": PREFILL_TOKENS, "value": PREFILL_TOKENS / (ms / 1e3)}
+    return {"ms": ms, "tokens": PREFILL_TOKENS, "past": past, "value": PREFILL_TOKENS / (ms / 1e3)}
 
 
 def prefill_flops(shape: dict, layers: int, tokens: int) -> float:
@@ -292,6 +296,8 @@ def main() -> int:
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--only", default=None, choices=["decode", "prefill"],
                         help="run one part and print a short line (for profiling captures; not a bench value)")
+    parser.add_argument("--past", type=int, default=0,
+                        help="with --only prefill: tokens already in the cache ahead of the timed 2,048-token portion")
     args = parser.parse_args()
     if args.impl == "reference":
         print(json.dumps({
@@ -311,7 +317,11 @@ def main() -> int:
     peaks, peaks_kind = measured_peaks()
     new_tokens = args.warmup + args.steps + 8
     pages = 64 * -(-(PROMPT_LEN + new_tokens + 1) // PAGE) + 2 * (PREFILL_TOKENS // PAGE)
-    engine = build_engine(shape, layers, 64, pages)
+    if args.only == "prefill" and args.past > 0:
+        pages = 2 * -(-(args.past + PREFILL_TOKENS) // PAGE)
+        engine = build_engine(shape, layers, 8, pages, max(CONTEXT, args.past + PREFILL_TOKENS))
+    else:
+        engine = build_engine(shape, layers, 64, pages)
     weight_bytes = engine.model.weight_bytes()
     kv_bytes_per_token = engine.cache.bytes_per_token()
 
@@ -319,7 +329,7 @@ def main() -> int:
         print(json.dumps({"only": "decode", "batch": args.batch, "layers": layers, **time_decode(engine, args.batch, args.steps, args.warmup)}))
         return 0
     if args.only == "prefill":
-        print(json.dumps({"only": "prefill", "layers": layers, **time_prefill(engine, repeats=max(1, args.steps))}))
+        print(json.dumps({"only": "prefill", "layers": layers, **time_prefill(engine, repeats=max(1, args.steps), past=args.past)}))
         return 0
 
     with ClockSampler() as sampler:
@@ -335,6 +345,7 @@ def main() -> int:
     step_bytes = weight_bytes + args.batch * head["mean_context"] * kv_bytes_per_token
     achieved = step_bytes / (head["ms_per_step"] / 1e3) / 1e9
     flops = prefill_flops(shape, layers, PREFILL_TOKENS)
+    prefill.pop("past", None)
     prefill["frac"] = round(flops / (prefill["ms"] / 1e3) / (peaks["bf16_tflops"] * 1e12), 4)
     prefill["value"] = round(prefill["value"], 1)
     prefill["ms"] = round(prefill["ms"], 3)
