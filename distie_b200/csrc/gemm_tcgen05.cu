@@ -482,36 +482,46 @@ gemm_tcgen05_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
 
   if (warp == 0) {
     // ---- producer ----------------------------------------------------------------------------------------
-    if (lane == 0) {
-      auto load_w = [&](int kb, int s) {
-        const int k = (kb_begin + kb) * kGemmBK;
-        if (EPI == SKINNY_EPI_SWIGLU) {
-          tma_load_2d(sm.w[s], &map_w, &sm.full[s], k, r0);
-          tma_load_2d(sm.w[s] + 64 * kGemmBK * 2, &map_w, &sm.full[s], k, inter + r0);
-        } else {
-          tma_load_2d(sm.w[s], &map_w, &sm.full[s], k, r0);
-        }
-      };
-      // The weights are written by no kernel: the first ring of stages starts before the wait.
-      const int early = min(k_blocks, STAGES);
-      for (int kb = 0; kb < early; ++kb) {
-        mbar_expect_tx(&sm.full[kb], W_BYTES + X_BYTES);
-        load_w(kb, kb);
+    // The copies of a stage are issued by as many lanes in one instruction (lane 0: the weights, or with
+    // SwiGLU the gate rows; lane 1: the up rows; the next lane: x): one thread issuing them one after
+    // the other takes several hundred clocks a stage, which is as long as the stage's bytes take at
+    // this SM's share of the memory bandwidth.
+    constexpr int X_LANE = EPI == SKINNY_EPI_SWIGLU ? 2 : 1;
+    auto load_w = [&](int kb, int s) {
+      const int k = (kb_begin + kb) * kGemmBK;
+      if (EPI == SKINNY_EPI_SWIGLU) {
+        if (lane == 0) tma_load_2d(sm.w[s], &map_w, &sm.full[s], k, r0);
+        if (lane == 1) tma_load_2d(sm.w[s] + 64 * kGemmBK * 2, &map_w, &sm.full[s], k, inter + r0);
+      } else {
+        if (lane == 0) tma_load_2d(sm.w[s], &map_w, &sm.full[s], k, r0);
       }
-      grid_dependency_wait();
+    };
+    // The weights are written by no kernel: the first ring of stages starts before the wait.
+    const int early = min(k_blocks, STAGES);
+    for (int kb = 0; kb < early; ++kb) {
+      if (lane == 0) mbar_expect_tx(&sm.full[kb], W_BYTES + X_BYTES);
+      __syncwarp();
+      load_w(kb, kb);
+    }
+    grid_dependency_wait();
+    if (lane == X_LANE)
       for (int kb = 0; kb < early; ++kb) tma_load_2d(sm.x[kb], &map_x, &sm.full[kb], (kb_begin + kb) * kGemmBK, 0);
-      int issued = early;
-      for (int kb = early; kb < k_blocks; ++kb) {
-        const int s = kb % STAGES;
-        if (!mbar_wait(&sm.empty[s], ((kb / STAGES) & 1) ^ 1)) { atomicExch(&sm.failed, 1u); break; }
-        mbar_expect_tx(&sm.full[s], W_BYTES + X_BYTES);
-        load_w(kb, s);
-        tma_load_2d(sm.x[s], &map_x, &sm.full[s], (kb_begin + kb) * kGemmBK, 0);
-        issued = kb + 1;
+    int issued = early;
+    for (int kb = early; kb < k_blocks; ++kb) {
+      const int s = kb % STAGES;
+      int ready = 1;
+      if (lane == 0) {
+        ready = mbar_wait(&sm.empty[s], ((kb / STAGES) & 1) ^ 1) ? 1 : 0;
+        if (ready) mbar_expect_tx(&sm.full[s], W_BYTES + X_BYTES);
       }
-      if (sm.failed) {
-        for (int kb = max(0, issued - STAGES); kb < issued; ++kb) mbar_wait(&sm.full[kb % STAGES], (kb / STAGES) & 1);
-      }
+      if (!__shfl_sync(0xffffffffu, ready, 0)) { atomicExch(&sm.failed, 1u); break; }
+      load_w(kb, s);
+      if (lane == X_LANE) tma_load_2d(sm.x[s], &map_x, &sm.full[s], (kb_begin + kb) * kGemmBK, 0);
+      issued = kb + 1;
+    }
+    __syncwarp();
+    if (sm.failed && lane == 0) {
+      for (int kb = max(0, issued - STAGES); kb < issued; ++kb) mbar_wait(&sm.full[kb % STAGES], (kb / STAGES) & 1);
     }
   } else if (warp == 1) {
     // ---- MMA issuer ----------------------------------------------------------------------------------------
