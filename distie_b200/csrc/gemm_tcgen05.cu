@@ -736,8 +736,8 @@ namespace distie {
 static int skinny_splits(int tiles, int K, int sm_count) {
   const int k_blocks = (K + kGemmBK - 1) / kGemmBK;
   int splits = sm_count / tiles;                 // one CTA per SM at most: a second wave would wait for the first
-  splits = min(splits, max(1, k_blocks / 2));    // at least two K blocks per CTA
-  return max(1, min(splits, 8));                 // the consumers sum up to eight slices in one round of loads
+  splits = min(splits, max(1, k_blocks / 4));    // at least four K blocks per CTA: below that a CTA's start and end outweigh its copies
+  return max(1, min(splits, 10));                // every slice is written once and read once more by the consumer
 }
 
 template <int BN, int STAGES, int EPI, typename OutT>

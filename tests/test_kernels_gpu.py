@@ -267,19 +267,21 @@ def test_rope_kv_write(kernel_sets, dtype, heads, kv_heads, head_dim, rotary_dim
     close(kv.k, kv_ref.k, dtype, "cached keys")
     assert torch.equal(kv.v, kv_ref.v), "values are copied bit for bit"
     assert float(kv.k.float().abs().sum()) > 0
-    # The same from float32 slices of the projection plus a bias, q into its own buffer.
-    slices = torch.randn(3, step.num_tokens, qkv.shape[1], device="cuda")
-    bias = torch.randn(qkv.shape[1], device="cuda")
-    kv_a = make_cache(dtype, 64, kv_heads, page, head_dim, 4, width, fill=False)
-    kv_b = make_cache(dtype, 64, kv_heads, page, head_dim, 4, width, fill=False)
-    q_a = torch.zeros(step.num_tokens, heads * head_dim, dtype=dtype, device="cuda")
-    q_b = torch.zeros_like(q_a)
-    ks.rope_kv_write(slices, step, kv_a, rotary, heads, kv_heads, head_dim, bias=bias, q_out=q_a)
-    ref.rope_kv_write(slices, step, kv_b, rotary, heads, kv_heads, head_dim, bias=bias, q_out=q_b)
-    ks.check_errors()
-    close(q_a, q_b, dtype, "rotated q from slices")
-    close(kv_a.k, kv_b.k, dtype, "cached keys from slices")
-    close(kv_a.v, kv_b.v, dtype, "cached values from slices")
+    # The same from float32 slices of the projection plus a bias, q into its own buffer: a few slices,
+    # and more than the kernel sums in one round of loads.
+    for count in (3, 10):
+        slices = torch.randn(count, step.num_tokens, qkv.shape[1], device="cuda")
+        bias = torch.randn(qkv.shape[1], device="cuda")
+        kv_a = make_cache(dtype, 64, kv_heads, page, head_dim, 4, width, fill=False)
+        kv_b = make_cache(dtype, 64, kv_heads, page, head_dim, 4, width, fill=False)
+        q_a = torch.zeros(step.num_tokens, heads * head_dim, dtype=dtype, device="cuda")
+        q_b = torch.zeros_like(q_a)
+        ks.rope_kv_write(slices, step, kv_a, rotary, heads, kv_heads, head_dim, bias=bias, q_out=q_a)
+        ref.rope_kv_write(slices, step, kv_b, rotary, heads, kv_heads, head_dim, bias=bias, q_out=q_b)
+        ks.check_errors()
+        close(q_a, q_b, dtype, f"rotated q from {count} slices")
+        close(kv_a.k, kv_b.k, dtype, f"cached keys from {count} slices")
+        close(kv_a.v, kv_b.v, dtype, f"cached values from {count} slices")
     # Nothing is written when the call only reads the cache; no rotation without a table.
     kv_none = make_cache(dtype, 64, kv_heads, page, head_dim, 4, width, fill=False)
     again = qkv.clone()
