@@ -762,20 +762,20 @@ static int dispatch_skinny_tc(const CUtensorMap& map_w, const void* x, int ldx, 
                               int M, int N, int K, int inter, int tiles, int splits, int* error, cudaStream_t stream) {
   CUtensorMap map_x;
   int status;
-  // A CTA whose share of K is a few blocks long asks for a ring no longer than that: the shared
+  // A CTA whose share of K is four blocks long or less asks for a ring of four stages: the shared
   // memory it leaves free lets the CTAs of the kernel after it (launched early) move in beside it.
   const int k_blocks = (K + kGemmBK - 1) / kGemmBK;
-  const bool brief = EPI == SKINNY_EPI_SLICE && (k_blocks + splits - 1) / splits <= 3;
+  const bool brief = EPI == SKINNY_EPI_SLICE && (k_blocks + splits - 1) / splits <= 4;
   if (M <= 16) {
     if ((status = make_map(&map_x, x, M, K, ldx, 16)) != 0) return status;
     if (brief)
-      return launch_skinny_tc<16, 3, EPI, OutT>(map_w, map_x, bias, out, ldo, M, N, K, inter, tiles, splits, error, stream);
+      return launch_skinny_tc<16, 4, EPI, OutT>(map_w, map_x, bias, out, ldo, M, N, K, inter, tiles, splits, error, stream);
     return launch_skinny_tc<16, 10, EPI, OutT>(map_w, map_x, bias, out, ldo, M, N, K, inter, tiles, splits, error, stream);
   }
   if (M <= 32) {
     if ((status = make_map(&map_x, x, M, K, ldx, 32)) != 0) return status;
     if (brief)
-      return launch_skinny_tc<32, 3, EPI, OutT>(map_w, map_x, bias, out, ldo, M, N, K, inter, tiles, splits, error, stream);
+      return launch_skinny_tc<32, 4, EPI, OutT>(map_w, map_x, bias, out, ldo, M, N, K, inter, tiles, splits, error, stream);
     return launch_skinny_tc<32, 9, EPI, OutT>(map_w, map_x, bias, out, ldo, M, N, K, inter, tiles, splits, error, stream);
   }
   if ((status = make_map(&map_x, x, M, K, ldx, 64)) != 0) return status;
