@@ -770,6 +770,10 @@ static int dispatch_skinny_tc(const CUtensorMap& map_w, const void* x, int ldx, 
     if ((status = make_map(&map_x, x, M, K, ldx, 16)) != 0) return status;
     if (brief)
       return launch_skinny_tc<16, 4, EPI, OutT>(map_w, map_x, bias, out, ldo, M, N, K, inter, tiles, splits, error, stream);
+    // The product that hands slices to a consumer runs on eight stages, the others on ten (measured:
+    // a decode step is 1.3 % shorter than with ten for all, and longer again with seven).
+    if (EPI == SKINNY_EPI_SLICE)
+      return launch_skinny_tc<16, 8, EPI, OutT>(map_w, map_x, bias, out, ldo, M, N, K, inter, tiles, splits, error, stream);
     return launch_skinny_tc<16, 10, EPI, OutT>(map_w, map_x, bias, out, ldo, M, N, K, inter, tiles, splits, error, stream);
   }
   if (M <= 32) {
