@@ -458,9 +458,13 @@ attention_decode_mma_merge_kernel(const float* __restrict__ scratch_o, const flo
 using namespace distie;
 
 // Stages of the key/value ring (and with them the CTAs that fit an SM: 2 with three stages, 3 with two)
-// for `tokens` single tokens and `blocks_per_token` CTAs per token and split.
-extern "C" int distie_attention_decode_mma_stages(int tokens, int blocks_per_token, int sm_count) {
-  return (long long)tokens * blocks_per_token * 2 >= sm_count ? 2 : 3;
+// for `tokens` single tokens, `blocks_per_token` CTAs per token and split, and `num_splits` splits.
+// Three stages when the kernel amounts to about one CTA per SM, which then has to cover the latency of
+// its copies alone; two otherwise (measured at batch 1 to 64 with 1,024-token contexts: a step at
+// batch 16 or 24 is 11 % shorter with two, at batch 8 it is 2 % shorter with three).
+extern "C" int distie_attention_decode_mma_stages(int tokens, int blocks_per_token, int num_splits, int sm_count) {
+  const long long ctas = (long long)tokens * blocks_per_token * num_splits;
+  return (2 * ctas > sm_count && ctas <= sm_count) ? 3 : 2;
 }
 
 // Same arguments and scratch layout as distie_attention_decode (bfloat16 only).
@@ -487,7 +491,7 @@ extern "C" int distie_attention_decode_mma(const void* q, int q_row_stride, void
     for (page_shift = 0; (1 << page_shift) < page_size; ++page_shift) {
     }
   cudaError_t err;
-  // Many CTAs: two stages, so that three CTAs fit an SM; few: three stages.
+  // Two or three ring stages (see distie_attention_decode_mma_stages).
   static int sm_count = 0;
   if (sm_count == 0) {
     int device = 0;
@@ -495,7 +499,7 @@ extern "C" int distie_attention_decode_mma(const void* q, int q_row_stride, void
         cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sm_count < 1)
       sm_count = 148;
   }
-  const int stages = distie_attention_decode_mma_stages(tokens, num_kv_heads * chunks, sm_count);
+  const int stages = distie_attention_decode_mma_stages(tokens, num_kv_heads * chunks, num_splits, sm_count);
   // Dynamic shared memory: the larger of the ring (warps x stages x loads x 512 bytes) and the merge areas.
   const size_t ring_bytes = (size_t)kMmaDecodeWarps * stages * 2 * 16 * head_dim * 2;  // K and V tiles of 16 rows
   const size_t merge_bytes = (size_t)kMmaDecodeWarps * 16 * (head_dim + 1) * sizeof(float) + 16 * head_dim * sizeof(float);
