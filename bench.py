@@ -286,6 +286,24 @@ def prefill_flops(shape: dict, layers: int, tokens: int) -> float:
     return layers * (per_layer + attention) + head
 
 
+def reference_arm(args) -> int:
+    """The unmodified reference on the same workload; none of this repository's engine is imported."""
+    from baseline import reference_arm as arm
+
+    shape = shape_from_baseline()
+    layers = args.layers or shape["num_hidden_layers"]
+    peaks, peaks_kind = measured_peaks()
+    constants = {"prompt_len": PROMPT_LEN, "context": CONTEXT, "prefill_tokens": PREFILL_TOKENS}
+    try:
+        line = arm.run(args, shape, layers, peaks, peaks_kind, constants, ClockSampler, prefill_flops)
+    except arm.Unavailable as exc:
+        line = {"impl": "reference", "unavailable": str(exc)}
+    except Exception as exc:  # noqa: BLE001  (the contract: a reference that cannot run prints why and exits 0)
+        line = {"impl": "reference", "unavailable": f"the reference raised {type(exc).__name__}: {exc}"[:400]}
+    print(json.dumps(line))
+    return 0
+
+
 def main() -> int:
     parser = argparse.ArgumentParser(description=__doc__.split("\n")[0])
     parser.add_argument("--gpus", type=int, default=1)
@@ -298,18 +316,17 @@ def main() -> int:
                         help="run one part and print a short line (for profiling captures; not a bench value)")
     parser.add_argument("--past", type=int, default=0,
                         help="with --only prefill: tokens already in the cache ahead of the timed 2,048-token portion")
+    parser.add_argument("--ref-attn", default=None, choices=["auto", "flash", "torch"],
+                        help="with --impl reference: its attention backend (default: DISTIE_ATTN, else auto)")
+    parser.add_argument("--ref-device", default=None, help=argparse.SUPPRESS)  # "cpu": a dry run of the reference arm
     args = parser.parse_args()
-    if args.impl == "reference":
-        print(json.dumps({
-            "impl": "reference",
-            "unavailable": "the reference is not installable offline: pip reports neither setup.py nor pyproject.toml in it",
-        }))
-        return 0
     if args.gpus != 1:
         print(json.dumps({"unsupported": f"--gpus {args.gpus}: this engine runs on one GPU; run with --gpus 1", "n_gpus": args.gpus}))
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.impl == "reference":
+        return reference_arm(args)
 
     shape = shape_from_baseline()
     layers_full = shape["num_hidden_layers"]

@@ -49,6 +49,15 @@ def pages_needed(tokens: int, page_size: int) -> int:
     return 0 if tokens <= 0 else (tokens + page_size - 1) // page_size
 
 
+def pages_that_fit(cache_needs, page_size: int, element_size: int, budget_bytes: int) -> int:
+    """How many pages per group ``budget_bytes`` of device memory hold (the spare page of every slab included
+    in the budget, not in the count): every cache slot keeps keys and values of its own for each page id."""
+    per_page = sum(2 * need.num_kv_heads * need.head_dim * element_size * page_size for need in cache_needs.values())
+    if per_page <= 0:
+        raise ValueError("the model declares no cache to size")
+    return int(budget_bytes // per_page) - 1
+
+
 @dataclass
 class _SeatPages:
     first: int = 0   # logical index of the first page still held

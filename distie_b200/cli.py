@@ -53,6 +53,8 @@ def _engine_options(parser: argparse.ArgumentParser) -> None:
     parser.add_argument("--device", default=os.getenv("WORKER_DEVICE", "cuda"), choices=["cuda"], help="the engine runs on CUDA only")
     parser.add_argument("--dtype", default="bf16", choices=["auto", "bf16", "fp32", "bfloat16", "float32"])
     parser.add_argument("--num-blocks", type=int, default=None, help="KV pages (default WORKER_NUM_BLOCKS or 1024)")
+    parser.add_argument("--gpu-mem-fraction", type=float, default=None,
+                        help="size the cache from this fraction of the free device memory instead of --num-blocks")
     parser.add_argument("--page-size", type=int, default=None, help="tokens per page (default 16)")
     parser.add_argument("--max-seqs", type=int, default=None, help="requests running at once (default WORKER_MAX_SEQS or 32)")
     parser.add_argument("--token-budget", type=int, default=None, help="tokens per scheduler step (default WORKER_TOKEN_BUDGET or 2048)")
@@ -70,6 +72,7 @@ def _load(args):
     knobs = dict(
         num_blocks=args.num_blocks, page_size=args.page_size, max_seqs=args.max_seqs, token_budget=args.token_budget,
         prefill_chunk=args.prefill_chunk, max_model_len=args.max_model_len, step_stats=args.step_stats,
+        gpu_mem_fraction=args.gpu_mem_fraction,
     )
     if args.no_decode_graphs:
         knobs["decode_graphs"] = False

@@ -5,6 +5,11 @@ The reference reads ``WORKER_NUM_BLOCKS`` (1024), ``WORKER_MAX_SEQS`` (32),
 ``WORKER_STEP_STATS`` (0) from the environment (README.md:105-119,
 worker/src/worker/config.py:22-57, worker/src/inference/torch_engine.py:212-225,
 462-493).  The same names give this engine's defaults; explicit arguments win.
+
+The cache is sized by a page count (``num_blocks``, the reference's only way,
+torch_engine.py:416-446) or, with ``gpu_mem_fraction``, from the device memory that
+is free once the weights are loaded: that fraction of it becomes pages
+(``WORKER_GPU_MEM_FRACTION``; an explicit ``num_blocks`` argument wins over it).
 """
 
 from __future__ import annotations
@@ -48,6 +53,8 @@ class EngineConfig:
     decode_ahead: bool = True  # launch a decode step before the tokens of the one ahead of it reached the host
     step_stats: int = 0
     device: str = "cuda:0"
+    float32_weights: str = "auto"  # matrices stored in 32-bit under a 16-bit engine: "auto" | "keep" | "cast"
+    gpu_mem_fraction: float | None = None  # size the cache from free device memory instead of num_blocks
 
     def __post_init__(self) -> None:
         for key in ("num_blocks", "page_size", "max_seqs", "token_budget"):
@@ -57,6 +64,10 @@ class EngineConfig:
             raise ValueError("prefill_chunk must be >= 1")
         if self.step_stats < 0:
             raise ValueError("step_stats must be >= 0")
+        if self.gpu_mem_fraction is not None and not 0.0 < float(self.gpu_mem_fraction) <= 1.0:
+            raise ValueError("gpu_mem_fraction must lie in (0, 1]")
+        if self.float32_weights not in ("auto", "keep", "cast"):
+            raise ValueError("float32_weights must be one of 'auto', 'keep', 'cast'")
         object.__setattr__(self, "dtype", resolve_dtype_name(self.dtype))
 
     @classmethod
@@ -68,9 +79,16 @@ class EngineConfig:
             decode_graphs=_env_bool("WORKER_DECODE_GRAPHS", True),
             decode_ahead=_env_bool("WORKER_DECODE_AHEAD", True),
             step_stats=_env_int("WORKER_STEP_STATS", 0, minimum=0),
+            gpu_mem_fraction=_env_float("WORKER_GPU_MEM_FRACTION"),
         )
         given = {k: v for k, v in overrides.items() if v is not None}
+        if "num_blocks" in given and "gpu_mem_fraction" not in given:
+            given["gpu_mem_fraction"] = None  # an explicit page count wins over a fraction from the environment
         return replace(base, **given)
+
+    def sized(self, num_blocks: int) -> "EngineConfig":
+        """This configuration with the page count that ``gpu_mem_fraction`` came to."""
+        return replace(self, num_blocks=int(num_blocks), gpu_mem_fraction=None)
 
 
 def _env_int(key: str, default: int, minimum: int = 1) -> int:
@@ -84,6 +102,16 @@ def _env_int(key: str, default: int, minimum: int = 1) -> int:
     if value < minimum:
         raise ValueError(f"{key} must be >= {minimum}")
     return value
+
+
+def _env_float(key: str) -> float | None:
+    raw = os.getenv(key)
+    if raw is None or raw.strip() == "":
+        return None
+    try:
+        return float(raw)
+    except ValueError as exc:
+        raise ValueError(f"{key} must be a number") from exc
 
 
 def _env_bool(key: str, default: bool) -> bool:

@@ -98,7 +98,11 @@ attention_decode_kernel(const T* __restrict__ q, int q_row_stride, T* __restrict
     for (int u = 0; u < kDecodeUnroll; ++u) {
       const int key = base_key + u;
       live[u] = key <= hi;
-      int page = live[u] ? table[key / page_size] : 0;
+      int page = 0;
+      if (live[u]) {  // a position past the end of the table is reported like a page that is missing
+        const int column = key / page_size;
+        page = column < table_width ? table[column] : -1;
+      }
       if (page < 0 || page >= num_pages) {
         if (error) atomicExch(error, 4);
         live[u] = false;

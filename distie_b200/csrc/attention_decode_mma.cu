@@ -130,7 +130,8 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_row_strid
   auto page_of = [&](int key) {
     const int column = page_shift >= 0 ? key >> page_shift : key / page_size;
     const int i = column - split_page;
-    return (staged_ready && i < kMmaDecodePages) ? sh_pages[i] : table[column];
+    if (staged_ready && i < kMmaDecodePages) return sh_pages[i];
+    return column < table_width ? table[column] : -1;  // past the end of the table: reported as a missing page
   };
 
   float o[NH][MT][4];  // O^T: [dim 16 mt + g (+8)][head 8 nh + 2c (+1)]

@@ -47,7 +47,8 @@ attention_generic_kernel(const T* __restrict__ q, int q_row_stride, T* __restric
   }
   float m = -INFINITY, l = 0.f;
   for (int key = first + warp; key <= pos; key += kGenericWarps) {
-    const int page = table[key / page_size];
+    const int column = key / page_size;
+    const int page = column < table_width ? table[column] : -1;
     if (page < 0 || page >= num_pages) {  // a table that does not cover the keys: report, skip
       if (lane == 0 && error) atomicExch(error, 3);
       continue;

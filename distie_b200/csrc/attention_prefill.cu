@@ -116,7 +116,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, 
         // page_shift >= 0: the page size is a power of two, so no division per row.
         const int column = page_shift >= 0 ? key >> page_shift : key / page_size;
         const int within = page_shift >= 0 ? key & (page_size - 1) : key % page_size;
-        const int page = table[column];
+        const int page = column < table_width ? table[column] : -1;
         if (page < 0 || page >= num_pages) {
           if (error) atomicExch(error, 5);
           ok = false;

@@ -22,6 +22,12 @@
 //    distie_no_alloc_error(code) gives the words for a code.
 //  * The first call on each device looks up the array's device address (once, with
 //    that device current).  Make that first call outside any stream capture.
+//  * The array that is used is the CURRENT device's (cudaGetDevice at the time of the
+//    call).  `stream` and every pointer must belong to that device: make the device
+//    that owns the stream current before calling.  The entry point does not check it.
+//  * `positions` must lie inside the block table (position / page_size < table_width);
+//    a position beyond it reads no memory: its keys count as missing pages and the
+//    error word is set to 4.
 //  * It calls no cudaMalloc, cudaFree or any other allocating routine, of CUDA or of
 //    a tensor library; inputs and outputs are the caller's.
 //  * All calls share the one array and it keeps what the last call left there.  No

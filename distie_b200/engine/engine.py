@@ -24,7 +24,7 @@ from typing import Callable, Sequence
 
 import torch
 
-from ..cache.manager import CacheExhausted, CacheManager
+from ..cache.manager import CacheExhausted, CacheManager, pages_that_fit
 from ..config.engine_config import EngineConfig
 from ..config.registry import read_config
 from ..kernels import make_kernels
@@ -95,9 +95,9 @@ class Engine:
     def load(cls, model: str, device: str = "cuda", dtype: str = "auto", **knobs) -> "Engine":
         """Build an engine for the model folder ``model`` (``config.json`` + safetensors).
 
-        ``knobs``: ``num_blocks``, ``page_size``, ``max_seqs``, ``token_budget``,
-        ``prefill_chunk``, ``max_model_len``, ``decode_graphs``, ``decode_ahead``, ``step_stats``; the
-        reference's ``WORKER_*`` environment variables give the defaults.
+        ``knobs``: ``num_blocks`` or ``gpu_mem_fraction``, ``page_size``, ``max_seqs``, ``token_budget``,
+        ``prefill_chunk``, ``max_model_len``, ``decode_graphs``, ``decode_ahead``, ``step_stats``,
+        ``float32_weights``; the reference's ``WORKER_*`` environment variables give the defaults.
         """
         if device == "cuda":
             device = "cuda:0"
@@ -112,8 +112,11 @@ class Engine:
         (a model folder or a dict of tensors by checkpoint name) and a kernel set."""
         spec = arch.recipe(model_config)
         started = time.perf_counter()
-        weights = open_weights(source, model_tensor_specs(spec), spec.tolerated, kernels.dtype, kernels.device)
+        weights = open_weights(source, model_tensor_specs(spec), spec.tolerated, kernels.dtype, kernels.device,
+                               config.float32_weights)
         decoder = DecoderModel(spec, kernels, weights)
+        if config.gpu_mem_fraction is not None:
+            config = config.sized(pages_from_free_memory(spec, config, kernels.dtype, kernels.device))
         cache = build_cache(spec, config, kernels.dtype, kernels.device)
         _log.info(
             "model ready architecture=%s dtype=%s pages=%s page_size=%s seats=%s load_s=%.1f",
@@ -157,12 +160,14 @@ class Engine:
         results: dict[str, GenerationResult] = {}
         seqs: dict[str, Seq] = {}
         for req in requests:
+            if req.request_id in results:
+                raise ValueError(f"duplicate request_id {req.request_id}")
             result = GenerationResult(req.request_id, prompt_tokens=len(req.prompt_ids))
             results[req.request_id] = result
             if not req.prompt_ids:  # the reference answers an empty prompt with one finished, empty event
                 result.finish_reason = "length"
                 continue
-            seq = Seq(
+            seqs[req.request_id] = Seq(
                 request_id=req.request_id,
                 prompt_ids=list(req.prompt_ids),
                 max_new_tokens=clamp_max_tokens(req.max_tokens),
@@ -170,8 +175,10 @@ class Engine:
                 eos_id=eos_id,
                 seed=req.seed,
             )
+        for seq in seqs.values():  # every request is checked before any is taken: a refusal leaves nothing behind
+            self.scheduler.validate(seq)
+        for seq in seqs.values():
             self.scheduler.submit(seq)
-            seqs[req.request_id] = seq
         try:
             while self.has_work():
                 for emission in self.step():
@@ -198,72 +205,108 @@ class Engine:
         tokens waited for, so the host's share of a step and the launch of the graph overlap the
         GPU's work on the step before.  A call still returns the emissions of exactly one step.
         """
-        if self._in_flight is not None or (self.config.decode_ahead and self.stats is None):
+        if self._in_flight is not None or self.config.decode_ahead:
             ahead = self._step_ahead()
             if ahead is not None:
                 return ahead
-        t0 = time.perf_counter()
+        clock = time.perf_counter
+        t0 = clock()
         plan, self._planned = self._planned or self.scheduler.schedule(), None
         if not plan.items:
-            if self.scheduler.has_work():
-                raise CacheExhausted("no request can run: waiting requests do not fit the free pages and nothing is running")
-            return []
-        t1 = time.perf_counter()
-        kernel_ms = None
-        if self.stats is not None:
-            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            begin.record()
-            tokens = self.runner.run_plan(plan)
-            end.record()
-            end.synchronize()
-            kernel_ms = begin.elapsed_time(end)
-        else:
-            tokens = self.runner.run_plan(plan)
-        t2 = time.perf_counter()
+            return self._nothing_to_run()
+        t1 = clock()
+        events = self._bracket()
+        tokens = self.runner.run_plan(plan)
+        kernel_ms = self._elapsed(events)
+        t2 = clock()
         emissions = self.scheduler.complete(plan, tokens)
-        t3 = time.perf_counter()
         self.steps += 1
         if self.stats is not None:
-            self.stats.record(
-                plan.kind, len(plan.items), plan.num_tokens, kernel_ms,
-                sched=(t1 - t0) * 1e3, gpu=(t2 - t1) * 1e3, emit=(t3 - t2) * 1e3,
-            )
+            self.stats.record(plan.kind, len(plan.items), plan.num_tokens, kernel_ms,
+                              sched=(t1 - t0) * 1e3, gpu=(t2 - t1) * 1e3, emit=(clock() - t2) * 1e3)
         return emissions
+
+    def _nothing_to_run(self) -> list[Emission]:
+        if self.scheduler.has_work():
+            raise CacheExhausted("no request can run: waiting requests do not fit the free pages and nothing is running")
+        return []
+
+    def _bracket(self):
+        """With step statistics on: a CUDA event recorded now, to be paired with one after the launches."""
+        if self.stats is None or self.runner.device.type != "cuda":
+            return None
+        begin = torch.cuda.Event(enable_timing=True)
+        begin.record()
+        return [begin, None]
+
+    @staticmethod
+    def _elapsed(events) -> float | None:
+        if events is None:
+            return None
+        if events[1] is None:
+            events[1] = torch.cuda.Event(enable_timing=True)
+            events[1].record()
+        events[1].synchronize()
+        return events[0].elapsed_time(events[1])
+
+    def _launch(self, plan, ids_on_device: bool = False):
+        """Launch a decode step; ``(plan, handle, events, host milliseconds)`` or None when no graph could be made."""
+        started = time.perf_counter()
+        events = self._bracket()
+        handle = self.runner.launch_decode(plan.items, ids_on_device=ids_on_device)
+        if handle is None:
+            return None
+        if events is not None:
+            events[1] = torch.cuda.Event(enable_timing=True)
+            events[1].record()
+        return plan, handle, events, (time.perf_counter() - started) * 1e3
 
     def _step_ahead(self) -> list[Emission] | None:
         """The pipelined form of ``step`` for decode steps; None when this step has to run the plain way."""
-        runner, scheduler = self.runner, self.scheduler
+        runner, scheduler, clock = self.runner, self.scheduler, time.perf_counter
+        sched_ms = 0.0
         if self._in_flight is None:
+            t0 = clock()
             plan = scheduler.schedule()
+            sched_ms += (clock() - t0) * 1e3
             if not plan.items:
-                if scheduler.has_work():
-                    raise CacheExhausted("no request can run: waiting requests do not fit the free pages and nothing is running")
-                return []
-            if not runner.can_launch_decode(plan.items):
-                self._planned = plan  # a step with prompt portions: the plain path runs this very plan
+                return self._nothing_to_run()
+            launched = self._launch(plan) if runner.can_launch_decode(plan.items) else None
+            if launched is None:
+                self._planned = plan  # prompt portions, or no graph could be made: the plain path runs this very plan
                 return None
-            self._in_flight = (plan, runner.launch_decode(plan.items))
-        plan, handle = self._in_flight
+            self._in_flight = launched
+        plan, handle, events, gpu_ms = self._in_flight
         self._in_flight = None
-        if scheduler.can_look_ahead(plan):
+        look_ahead = scheduler.can_look_ahead(plan)
+        if look_ahead:
+            t0 = clock()
             scheduler.assume(plan)
             following = scheduler.schedule()
+            sched_ms += (clock() - t0) * 1e3
             same_rows = len(following.items) == len(plan.items) and all(
                 a.seq is b.seq and len(b.token_ids) == 1 for a, b in zip(plan.items, following.items)
             )
             if same_rows and runner.can_launch_decode(following.items):
-                self._in_flight = (following, runner.launch_decode(following.items, ids_on_device=True))
+                self._in_flight = self._launch(following, ids_on_device=True)
             # otherwise the step after this one is planned again once these tokens are known
-            emissions = scheduler.resolve(plan, runner.fetch_decode(handle))
-        else:
-            emissions = scheduler.complete(plan, runner.fetch_decode(handle))
+        t1 = clock()
+        tokens = runner.fetch_decode(handle)
+        kernel_ms = self._elapsed(events)
+        t2 = clock()
+        emissions = scheduler.resolve(plan, tokens) if look_ahead else scheduler.complete(plan, tokens)
         self.steps += 1
+        if self.stats is not None:
+            # gpu: launching this step plus waiting for its tokens; the launch of the next step, done in between,
+            # is booked on the next step.
+            self.stats.record(plan.kind, len(plan.items), plan.num_tokens, kernel_ms,
+                              sched=sched_ms, gpu=gpu_ms + (t2 - t1) * 1e3, emit=(clock() - t2) * 1e3)
         return emissions
 
     def drain(self) -> None:
         """Waits for a launched step, if any, and drops its tokens (after requests were aborted)."""
         if self._in_flight is not None:
-            _, handle = self._in_flight
+            handle = self._in_flight[1]
             self._in_flight = None
             self.runner.fetch_decode(handle)
         self._planned = None
@@ -325,6 +368,24 @@ class Engine:
         finally:
             self.cache.close_seat(seat)
         return Trace(token_ids=picks, logits=torch.stack(rows))
+
+
+def pages_from_free_memory(spec, config: EngineConfig, torch_dtype, device) -> int:
+    """Pages that ``config.gpu_mem_fraction`` of the device memory free right now (the weights are loaded)
+    holds, keys and values of every cache slot counted.  What is left over serves activations, the captured
+    decode steps and the library's workspaces."""
+    cache_needs, _ = slot_needs(spec)
+    device = torch.device(device)
+    if device.type != "cuda":
+        raise ValueError("gpu_mem_fraction sizes the cache from a CUDA device's free memory; give num_blocks on other devices")
+    torch.cuda.empty_cache()
+    free, _total = torch.cuda.mem_get_info(device)
+    element = torch.empty((), dtype=torch_dtype).element_size()
+    pages = pages_that_fit(cache_needs, config.page_size, element, int(free * float(config.gpu_mem_fraction)))
+    if pages < 1:
+        raise CacheExhausted(f"{config.gpu_mem_fraction} of the {free >> 20} MiB that are free hold not one page of cache")
+    _log.info("cache sized from free memory free_mib=%s fraction=%s pages=%s", free >> 20, config.gpu_mem_fraction, pages)
+    return pages
 
 
 def build_cache(spec, config: EngineConfig, torch_dtype, device) -> CacheManager:

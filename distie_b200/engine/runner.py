@@ -101,6 +101,10 @@ class ModelRunner:
     # -- the step function ----------------------------------------------------
     @torch.inference_mode()
     def step(self, entries: Sequence[BatchEntry]) -> torch.Tensor | None:
+        if self.use_graphs and len(entries) <= self._sizes[-1] and all(len(e.tokens) == 1 for e in entries):
+            logits = self._graph_logits(entries)
+            if logits is not NotImplemented:
+                return logits
         layout = lay_out(entries, self.model.vocab_size)
         if layout.num_tokens > self.max_step_tokens or layout.num_seqs > self.max_seqs:
             raise ValueError(
@@ -111,6 +115,27 @@ class ModelRunner:
         step, rows = self.staging.upload(layout)
         self.steps += 1
         return self.model.forward(step, layout.seqs, self.cache, rows if layout.num_rows else None)
+
+    def _graph_logits(self, entries: Sequence[BatchEntry]):
+        """A step of single tokens through the captured decode step of its bucket: the logits of the
+        wanted entries, or ``NotImplemented`` when no graph could be made (every step is eager from then on)."""
+        vocab = self.model.vocab_size
+        for entry in entries:
+            if not 0 <= entry.tokens[0] < vocab or entry.past_len < 0:
+                raise ValueError(f"token id outside [0, {vocab}) or past_len < 0")
+            if any(place != 0 for place in entry.want):
+                raise ValueError("want outside the one token of its entry")
+        rows = [(entry.tokens[0], entry.past_len, entry.seat, 0.0, 0.0) for entry in entries]
+        bucket = self._replay(rows, ids_on_device=False)
+        if bucket is None:
+            return NotImplemented
+        self.steps += 1
+        wanted = [row for row, entry in enumerate(entries) for _ in entry.want]
+        if not wanted:
+            return None
+        if wanted == list(range(len(wanted))):
+            return bucket.logits[: len(wanted)].clone()
+        return bucket.logits.index_select(0, torch.tensor(wanted, dtype=torch.long, device=self.device))
 
     def finish_step(self) -> None:
         """After the step's results reached the host: surface device-side checks."""
@@ -123,12 +148,10 @@ class ModelRunner:
         if not items:
             raise ValueError("empty step plan")
         sampling = [item for item in items if item.samples]
-        if self.use_graphs and len(items) <= self._sizes[-1] and all(len(i.token_ids) == 1 for i in items):
-            try:
-                return self._graph_step(items)
-            except Exception:  # the eager step rewrites the same slots, so running it instead is safe
-                _log.exception("decode graph failed; every step stays eager from now on")
-                self.use_graphs = False
+        if self.can_launch_decode(items):
+            handle = self.launch_decode(items)
+            if handle is not None:
+                return self.fetch_decode(handle)  # a device-side check that fails here is the request's, not the graph's
         entries = [
             BatchEntry(i.seq.seat, i.token_ids, i.past_len, (len(i.token_ids) - 1,) if i.samples else ())
             for i in items
@@ -161,9 +184,6 @@ class ModelRunner:
             raise ValueError(f"decode batch of {rows} rows outside 1..{self._sizes[-1]}")
         return self._sizes[bisect.bisect_left(self._sizes, rows)]
 
-    def _graph_step(self, items) -> list[int]:
-        return self.fetch_decode(self.launch_decode(items))
-
     def can_launch_decode(self, items) -> bool:
         """Whether ``launch_decode`` takes these items: graphs on, one token each, a bucket large enough."""
         return bool(
@@ -173,13 +193,43 @@ class ModelRunner:
     @torch.inference_mode()
     def launch_decode(self, items, ids_on_device: bool = False):
         """Starts a decode step (graph replay) and returns a handle for ``fetch_decode``; does not wait.
+        Returns None when the bucket's graph could not be captured: graphs are off from then on and the
+        caller runs the step eagerly (which rewrites the same slots).
 
         With ``ids_on_device`` the rows' token ids are the tokens that the previous replay of
         the same bucket sampled for the same rows (they never left the device); everything
         else -- positions, seats, block tables, sampling numbers -- comes from the host as usual.
         """
-        rows = len(items)
-        size = self.bucket_for(rows)
+        rows = [
+            (
+                max(0, item.token_ids[0]), item.past_len, item.seq.seat,
+                float(item.seq.temperature) if item.seq.temperature > 0 else 0.0,
+                uniform(item.seq.seed, len(item.seq.output_ids)) if item.seq.temperature > 0 else 0.0,
+            )
+            for item in items
+        ]
+        bucket = self._replay(rows, ids_on_device)
+        if bucket is None:
+            return None
+        size = bucket.size
+        self.steps += 1
+        turn = bucket.turn
+        bucket.turn ^= 1
+        host = bucket.result_host[turn]
+        host[:size].copy_(bucket.tokens, non_blocking=True)
+        flag = getattr(self.kernels, "error_flag", None)
+        if flag is not None:
+            host[size:].copy_(flag, non_blocking=True)
+        else:
+            host[size:] = 0
+        if bucket.result_ready[turn] is not None:
+            bucket.result_ready[turn].record()
+        return bucket, turn, [item.samples for item in items]
+
+    def _replay(self, rows, ids_on_device: bool):
+        """Stage ``rows`` of (token, past_len, seat, temperature, uniform) into their bucket and replay its
+        captured step (capturing it first when new).  None: capture or replay failed, graphs are now off."""
+        size = self.bucket_for(len(rows))
         bucket = self._buckets.get(size)
         if bucket is None:
             bucket = _Bucket(size, self.device)
@@ -195,35 +245,28 @@ class ModelRunner:
         token_seq[:] = np.arange(size, dtype=np.int32)
         logit_rows[:] = np.arange(size, dtype=np.int32)
         floats[:] = 0.0
-        for row, item in enumerate(items):
-            ids[row] = max(0, item.token_ids[0])
-            positions[row] = item.past_len
-            seats[row] = item.seq.seat
-            if item.seq.temperature > 0:
-                floats[row] = float(item.seq.temperature)
-                floats[size + row] = uniform(item.seq.seed, len(item.seq.output_ids))
-        self.cache.upload_tables([item.seq.seat for item in items])
+        for row, (token, past_len, seat, temperature, draw) in enumerate(rows):
+            ids[row] = token
+            positions[row] = past_len
+            seats[row] = seat
+            floats[row] = temperature
+            floats[size + row] = draw
+        self.cache.upload_tables([row[2] for row in rows])
         bucket.upload(ids_on_device and bucket.graph is not None)
-        if bucket.graph is None:
-            if ids_on_device:
-                raise RuntimeError("token ids on the device need a replay of the same bucket before")
-            self._capture(bucket)
-        else:
-            bucket.graph.replay()
-            self.graph_replays += 1
-        self.steps += 1
-        turn = bucket.turn
-        bucket.turn ^= 1
-        host = bucket.result_host[turn]
-        host[:size].copy_(bucket.tokens, non_blocking=True)
-        flag = getattr(self.kernels, "error_flag", None)
-        if flag is not None:
-            host[size:].copy_(flag, non_blocking=True)
-        else:
-            host[size:] = 0
-        if bucket.result_ready[turn] is not None:
-            bucket.result_ready[turn].record()
-        return bucket, turn, [item.samples for item in items]
+        if bucket.graph is None and ids_on_device:
+            raise RuntimeError("token ids on the device need a replay of the same bucket before")
+        try:
+            if bucket.graph is None:
+                self._capture(bucket)
+            else:
+                bucket.graph.replay()
+                self.graph_replays += 1
+        except Exception:  # noqa: BLE001  (capture and replay only; device-side checks surface in fetch_decode)
+            _log.exception("decode graph failed; every step stays eager from now on")
+            self.use_graphs = False
+            self._buckets.pop(size, None)
+            return None
+        return bucket
 
     def fetch_decode(self, handle) -> list[int]:
         """The sampled tokens of a launched decode step (waits for them), after the device-side checks."""

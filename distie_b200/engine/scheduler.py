@@ -1,28 +1,29 @@
 """Continuous-batching scheduler: which tokens of which requests the next step runs.
 
-Bookkeeping only (no tensors), one owner, not thread-safe -- like the reference's
-scheduler (worker/src/inference/scheduler.py:1-17), whose order of work each step
-is kept:
+Bookkeeping only (no tensors), one owner, not thread-safe.  The policy is the
+reference's (worker/src/inference/scheduler.py:141-236), in its order of work:
 
-1. requests that were aborted are dropped and their pages returned
-   (scheduler.py:168-180);
-2. running requests get the pages their known tokens need; when the pool is short
-   the NEWEST running request is preempted: its pages are returned, it forgets what
-   it cached and goes to the FRONT of the waiting queue, to be recomputed later as
+1. requests that were aborted leave and give their pages back (scheduler.py:168-180);
+2. every running request gets the pages its known tokens need; when the pool is
+   short the NEWEST running request is sent back: it gives up its pages, forgets
+   what it cached and goes to the FRONT of the line, to be recomputed later as
    prompt + tokens generated so far (scheduler.py:182-194, 213-225);
-3. waiting requests are admitted first-in-first-out -- never skipping the head --
-   while a seat, budget and pages for all their known tokens are available
-   (scheduler.py:196-211);
+3. the line is admitted head first, never skipping, while a seat, budget and the
+   pages for all known tokens are there (scheduler.py:196-211);
 4. the plan: one token for every request that is decoding, then the rest of the
-   token budget is dealt, in admission order, to requests that still have prompt
-   tokens to cache, as portions.
+   token budget dealt, in admission order, to requests with prompt tokens still to
+   cache, as portions.
 
-Step 4 is where this scheduler goes beyond the reference, which always runs an
-admitted prompt whole (scheduler.py:145-147): here a prompt may be cut anywhere,
-down to one token, by the budget or by ``prefill_chunk``.  A request whose portion
-does not reach its last known token gets no sampled token in that step.
-``complete`` appends sampled tokens; tokens are appended nowhere else, so a
-preempted request never emits a token twice (scheduler.py:15-16).
+Step 4 goes beyond the reference, which always runs an admitted prompt whole
+(scheduler.py:145-147): here a prompt may be cut anywhere, down to one token, by
+the budget or by ``prefill_chunk``; a request whose portion does not reach its last
+known token samples nothing in that step.  Tokens are appended in one place only
+(``_take_token``), so a request that was sent back never emits a token twice
+(scheduler.py:15-16).
+
+How a request moves: ``submit`` puts it in the line (WAITING); ``_admit`` gives it a
+seat (RUNNING); ``_leave_running`` is the one way out of RUNNING, either back to the
+line (preemption) or for good (finished, aborted).
 """
 
 from __future__ import annotations
@@ -30,8 +31,7 @@ from __future__ import annotations
 import enum
 import logging
 from collections import deque
-from dataclasses import dataclass, field
-from typing import Sequence as SequenceT
+from typing import Iterable, NamedTuple, Sequence as SequenceT
 
 from ..cache.manager import CacheExhausted
 
@@ -44,20 +44,27 @@ class SeqState(enum.Enum):
     FINISHED = "finished"
 
 
-@dataclass(eq=False)
 class Sequence:
-    request_id: str
-    prompt_ids: list[int]
-    max_new_tokens: int
-    temperature: float = 0.0
-    eos_id: int | None = None
-    seed: int = 0
-    output_ids: list[int] = field(default_factory=list)
-    seat: int | None = None
-    num_cached: int = 0  # tokens whose keys and values are in the cache
-    state: SeqState = SeqState.WAITING
-    preemptions: int = 0
-    finish_reason: str | None = None
+    """One request as the scheduler sees it: what is known of it and how much of that is cached."""
+
+    def __init__(self, request_id: str, prompt_ids, max_new_tokens: int, temperature: float = 0.0,
+                 eos_id: int | None = None, seed: int = 0) -> None:
+        self.request_id = request_id
+        self.prompt_ids = list(prompt_ids)
+        self.max_new_tokens = max_new_tokens
+        self.temperature = temperature
+        self.eos_id = eos_id
+        self.seed = seed
+        self.output_ids: list[int] = []
+        self.seat: int | None = None
+        self.num_cached = 0  # tokens whose keys and values are in the cache
+        self.state = SeqState.WAITING
+        self.preemptions = 0
+        self.finish_reason: str | None = None  # "eos" | "length" | "aborted"
+
+    def __repr__(self) -> str:
+        return (f"Sequence({self.request_id!r}, prompt={len(self.prompt_ids)}, outputs={len(self.output_ids)}, "
+                f"cached={self.num_cached}, {self.state.value})")
 
     @property
     def num_tokens(self) -> int:
@@ -67,44 +74,52 @@ class Sequence:
     def num_pending(self) -> int:
         return self.num_tokens - self.num_cached
 
+    @property
+    def is_running(self) -> bool:
+        return self.state is SeqState.RUNNING
+
     def tokens(self, start: int, stop: int) -> list[int]:
-        n = len(self.prompt_ids)
-        if stop <= n:
-            return self.prompt_ids[start:stop]
-        if start >= n:
-            return self.output_ids[start - n : stop - n]
-        return self.prompt_ids[start:] + self.output_ids[: stop - n]
+        """Known tokens ``[start, stop)``, prompt and outputs read as one sequence."""
+        split = len(self.prompt_ids)
+        head = self.prompt_ids[start:min(stop, split)] if start < split else []
+        tail = self.output_ids[max(start, split) - split : stop - split] if stop > split else []
+        return head + tail
 
 
-@dataclass(frozen=True)
-class ScheduledSeq:
+class ScheduledSeq(NamedTuple):
     seq: Sequence
     token_ids: list[int]
     past_len: int
     samples: bool  # the portion reaches the request's last known token
 
 
-@dataclass(frozen=True)
+class Emission(NamedTuple):
+    seq: Sequence
+    token_id: int
+    finished: bool
+
+
 class StepPlan:
-    items: tuple[ScheduledSeq, ...]
+    def __init__(self, items: Iterable[ScheduledSeq]) -> None:
+        self.items = tuple(items)
 
     @property
     def num_tokens(self) -> int:
         return sum(len(item.token_ids) for item in self.items)
 
     @property
+    def num_samples(self) -> int:
+        return sum(1 for item in self.items if item.samples)
+
+    @property
     def kind(self) -> str:
+        """``decode`` when every request brings one token, else ``prefill`` (the step statistics' groups)."""
         return "decode" if all(len(item.token_ids) == 1 for item in self.items) else "prefill"
 
 
-@dataclass(frozen=True)
-class Emission:
-    seq: Sequence
-    token_id: int
-    finished: bool
-
-
 class Scheduler:
+    PLACEHOLDER = -1  # stands for a token that was sampled on the device and has not reached the host
+
     def __init__(self, cache, max_seqs: int = 32, token_budget: int = 2048, prefill_chunk: int | None = None) -> None:
         if max_seqs < 1 or token_budget < 1:
             raise ValueError("max_seqs and token_budget must be >= 1")
@@ -114,242 +129,233 @@ class Scheduler:
         self._max_seqs = max_seqs
         self._budget = token_budget
         self._chunk = prefill_chunk
-        self._waiting: deque[Sequence] = deque()
-        self._running: list[Sequence] = []
-        self._aborted: set[str] = set()
-        self._ids: dict[str, Sequence] = {}
+        self._book: dict[str, Sequence] = {}   # every request that has not left for good
+        self._line: deque[Sequence] = deque()  # WAITING, head first
+        self._live: list[Sequence] = []        # RUNNING, in admission order (the last one is the newest)
+        self._cancelled: set[str] = set()
 
     # -- queries ------------------------------------------------------------
     @property
     def num_waiting(self) -> int:
-        return len(self._waiting)
+        return len(self._line)
 
     @property
     def num_running(self) -> int:
-        return len(self._running)
+        return len(self._live)
+
+    def running(self) -> tuple[Sequence, ...]:
+        """Running requests, oldest first."""
+        return tuple(self._live)
+
+    def waiting(self) -> tuple[Sequence, ...]:
+        """The line, head first."""
+        return tuple(self._line)
 
     def has_work(self) -> bool:
-        return bool(self._waiting or self._running or self._aborted)
+        return bool(self._line or self._live or self._cancelled)
 
     # -- requests in and out ------------------------------------------------
-    def submit(self, seq: Sequence) -> None:
+    def validate(self, seq: Sequence) -> None:
+        """Raises what ``submit`` would raise, without taking the request."""
         if not seq.prompt_ids:
             raise ValueError("prompt_ids must be non-empty")
         if seq.max_new_tokens < 1:
             raise ValueError("max_new_tokens must be >= 1")
-        if seq.request_id in self._ids:
+        if seq.request_id in self._book:
             raise ValueError(f"duplicate request_id {seq.request_id}")
-        # Worst case the request holds every page it will ever need at once (scheduler.py:125-131).
-        total = len(seq.prompt_ids) + seq.max_new_tokens
-        if not self._cache.fits_ever(total):
+        # At worst the request holds every page it will ever need at the same time (scheduler.py:125-131).
+        most = len(seq.prompt_ids) + seq.max_new_tokens
+        if not self._cache.fits_ever(most):
             raise CacheExhausted(
-                f"out of KV blocks: request of {total} tokens can never fit "
+                f"out of KV blocks: request of {most} tokens can never fit "
                 f"(pool has {self._cache.total_pages()} pages per group)"
             )
+
+    def submit(self, seq: Sequence) -> None:
+        self.validate(seq)
         seq.state = SeqState.WAITING
-        self._waiting.append(seq)
-        self._ids[seq.request_id] = seq
+        self._book[seq.request_id] = seq
+        self._line.append(seq)
 
     def abort(self, request_id: str) -> None:
-        """Takes effect at the next ``schedule()``; results in flight for it are discarded."""
-        if request_id in self._ids:
-            self._aborted.add(request_id)
+        """Takes effect at the next ``schedule()``; results in flight for the request are dropped."""
+        if request_id in self._book:
+            self._cancelled.add(request_id)
 
     def force_preempt(self, request_id: str) -> bool:
-        """Preempt a running request now (for tests and experiments)."""
-        seq = self._ids.get(request_id)
-        if seq is None or seq.state is not SeqState.RUNNING:
+        """Send a running request back to the line now (for tests and experiments)."""
+        seq = self._book.get(request_id)
+        if seq is None or not seq.is_running:
             return False
-        self._preempt(seq)
+        self._leave_running(seq, requeue=True)
         return True
 
     # -- the step -----------------------------------------------------------
     def schedule(self) -> StepPlan:
-        self._reap_aborted()
-        self._grow_running()
+        self._drop_cancelled()
+        self._make_room()
         self._admit()
-        return StepPlan(items=tuple(self._deal()))
+        return StepPlan(self._deal())
 
     def complete(self, plan: StepPlan, sampled: SequenceT[int]) -> list[Emission]:
         """``sampled`` holds one token for every item of the plan with ``samples``, in order."""
-        wanted = sum(1 for item in plan.items if item.samples)
-        if len(sampled) != wanted:
-            raise ValueError(f"the plan samples {wanted} tokens, got {len(sampled)}")
-        out: list[Emission] = []
-        tokens = iter(sampled)
+        if len(sampled) != plan.num_samples:
+            raise ValueError(f"the plan samples {plan.num_samples} tokens, got {len(sampled)}")
+        feed = iter(sampled)
+        emissions = []
         for item in plan.items:
-            token = int(next(tokens)) if item.samples else None
+            token = int(next(feed)) if item.samples else None
             seq = item.seq
-            if seq.request_id in self._aborted or seq.state is not SeqState.RUNNING:
-                continue  # aborted, preempted or finished while the step was in flight
-            seq.num_cached = item.past_len + len(item.token_ids)
-            self._cache.trim(seq.seat, seq.num_cached)
-            if token is None:
-                continue
-            seq.output_ids.append(token)
-            if seq.eos_id is not None and token == seq.eos_id:
-                seq.finish_reason = "eos"
-            elif len(seq.output_ids) >= seq.max_new_tokens:
-                seq.finish_reason = "length"
-            finished = seq.finish_reason is not None
-            if finished:
-                self._finish(seq)
-            out.append(Emission(seq=seq, token_id=token, finished=finished))
-        return out
+            if seq.request_id in self._cancelled or not seq.is_running:
+                continue  # aborted, sent back or finished while the step was in flight
+            self._mark_cached(seq, item)
+            if token is not None:
+                seq.output_ids.append(token)
+                emissions.append(self._take_token(seq, len(seq.output_ids) - 1))
+        return emissions
 
     # -- a step ahead ---------------------------------------------------------
     # A decode step may be launched before the tokens of the step ahead of it have reached the host: the
-    # device feeds them to it directly.  The scheduler then books the earlier step provisionally
-    # (``assume``: one more cached token, a placeholder for the token nobody has seen yet), plans the next
-    # step as usual, and fills the tokens in when they arrive (``resolve``).  A request that turns out to
-    # have ended with that token is finished then; its row in the step already launched is ignored.
-    PLACEHOLDER = -1
-
+    # device feeds them to it directly.  The earlier step is then booked provisionally (``assume``: one more
+    # cached token and a placeholder where the unseen token will stand), the next step is planned as usual,
+    # and the tokens are filled in when they arrive (``resolve``).  A request that turns out to have ended
+    # with that token ends then; its row in the step launched meanwhile is ignored.
     def can_look_ahead(self, plan: StepPlan) -> bool:
         """True when the step after ``plan`` can be planned without ``plan``'s tokens: decoding only,
         nobody waiting or aborted, and no request that this step ends by length."""
-        if self._waiting or self._aborted or not plan.items:
+        if self._line or self._cancelled or len(plan.items) != len(self._live) or not plan.items:
             return False
-        for item in plan.items:
-            seq = item.seq
-            if len(item.token_ids) != 1 or not item.samples or seq.state is not SeqState.RUNNING:
-                return False
-            if len(seq.output_ids) + 1 >= seq.max_new_tokens:
-                return False
-        return len(plan.items) == len(self._running)
+        return all(
+            len(item.token_ids) == 1 and item.samples and item.seq.is_running
+            and len(item.seq.output_ids) + 1 < item.seq.max_new_tokens
+            for item in plan.items
+        )
 
     def assume(self, plan: StepPlan) -> None:
         for item in plan.items:
-            seq = item.seq
-            seq.num_cached = item.past_len + len(item.token_ids)
-            self._cache.trim(seq.seat, seq.num_cached)
-            seq.output_ids.append(self.PLACEHOLDER)
+            self._mark_cached(item.seq, item)
+            item.seq.output_ids.append(self.PLACEHOLDER)
 
     def resolve(self, plan: StepPlan, sampled: SequenceT[int]) -> list[Emission]:
-        """The tokens of a step booked with ``assume``: replaces the placeholders, finishes what ended."""
+        """The tokens of a step booked with ``assume``: replaces the placeholders, ends what ended."""
         if len(sampled) != len(plan.items):
             raise ValueError(f"the plan samples {len(plan.items)} tokens, got {len(sampled)}")
-        out: list[Emission] = []
+        emissions = []
         for item, token in zip(plan.items, sampled):
             seq = item.seq
-            index = item.past_len + 1 - len(seq.prompt_ids)  # where this step's token sits among the outputs
-            if seq.state is SeqState.FINISHED or index >= len(seq.output_ids) or seq.output_ids[index] != self.PLACEHOLDER:
+            index = item.past_len + 1 - len(seq.prompt_ids)  # where this step's token stands among the outputs
+            stale = seq.state is SeqState.FINISHED or index >= len(seq.output_ids) or seq.output_ids[index] != self.PLACEHOLDER
+            if stale:
                 continue
-            token = int(token)
-            seq.output_ids[index] = token
-            if seq.request_id in self._aborted:
-                continue
-            if seq.eos_id is not None and token == seq.eos_id:
-                seq.finish_reason = "eos"
-            elif index + 1 >= seq.max_new_tokens:
-                seq.finish_reason = "length"
-            finished = seq.finish_reason is not None
-            if finished:
-                del seq.output_ids[index + 1 :]  # a placeholder of the step launched meanwhile
-                if seq.state is SeqState.RUNNING:
-                    self._finish(seq)
-                else:  # preempted meanwhile: it waits, holding nothing
-                    self._waiting.remove(seq)
-                    seq.state = SeqState.FINISHED
-                    self._ids.pop(seq.request_id, None)
-            out.append(Emission(seq=seq, token_id=token, finished=finished))
-        return out
+            seq.output_ids[index] = int(token)
+            if seq.request_id not in self._cancelled:
+                emissions.append(self._take_token(seq, index))
+        return emissions
 
     # -- internals ------------------------------------------------------------
-    def _reap_aborted(self) -> None:
-        for request_id in list(self._aborted):
-            seq = self._ids.pop(request_id, None)
-            if seq is None:
-                continue
-            if seq.state is SeqState.WAITING:
-                self._waiting.remove(seq)
-            elif seq.state is SeqState.RUNNING:
-                self._running.remove(seq)
-                self._release(seq)
-            seq.state = SeqState.FINISHED
-            seq.finish_reason = "aborted"
-            _log.info("sequence aborted request_id=%s", request_id)
-        self._aborted.clear()
+    def _mark_cached(self, seq: Sequence, item: ScheduledSeq) -> None:
+        seq.num_cached = item.past_len + len(item.token_ids)
+        self._cache.trim(seq.seat, seq.num_cached)
 
-    def _grow_running(self) -> None:
-        index = 0
-        while index < len(self._running):
-            seq = self._running[index]
-            while seq.state is SeqState.RUNNING and not self._cache.grow(seq.seat, seq.num_tokens):
-                self._preempt(self._running[-1])  # the newest; may be seq itself
-            if seq.state is SeqState.RUNNING:
-                index += 1
+    def _take_token(self, seq: Sequence, index: int) -> Emission:
+        """Output ``index`` of ``seq`` is now known: decide whether the request ends with it."""
+        token = seq.output_ids[index]
+        if seq.eos_id is not None and token == seq.eos_id:
+            seq.finish_reason = "eos"
+        elif index + 1 >= seq.max_new_tokens:
+            seq.finish_reason = "length"
+        if seq.finish_reason is None:
+            return Emission(seq, token, False)
+        del seq.output_ids[index + 1 :]  # a placeholder of a step launched meanwhile
+        if seq.is_running:
+            self._leave_running(seq, requeue=False)
+        else:  # sent back meanwhile: it waits in the line, holding nothing
+            self._line.remove(seq)
+            self._forget(seq)
+        return Emission(seq, token, True)
 
-    def _planned_tokens(self) -> int:
-        """Tokens the running requests will take of this step's budget."""
-        left = self._budget
-        for seq in self._running:
-            if seq.num_pending == 1:
-                left -= 1
-        for seq in self._running:
-            if seq.num_pending > 1 and left > 0:
-                left -= min(seq.num_pending, left, self._chunk or left)
-        return self._budget - left
+    def _forget(self, seq: Sequence) -> None:
+        seq.state = SeqState.FINISHED
+        self._book.pop(seq.request_id, None)
 
-    def _admit(self) -> None:
-        tokens = self._planned_tokens()
-        while self._waiting and len(self._running) < self._max_seqs and self._cache.free_seats > 0:
-            seq = self._waiting[0]
-            if tokens >= self._budget and self._running:
-                break  # no budget left for even one of its tokens; a lone request is always admitted
-            if not self._cache.can_grow(None, seq.num_tokens):
-                break
-            self._waiting.popleft()
-            seq.seat = self._cache.open_seat()
-            if not self._cache.grow(seq.seat, seq.num_tokens):  # cannot happen after can_grow; stay safe
-                self._cache.close_seat(seq.seat)
-                seq.seat = None
-                self._waiting.appendleft(seq)
-                break
-            seq.num_cached = 0
-            seq.state = SeqState.RUNNING
-            self._running.append(seq)
-            room = max(0, self._budget - tokens)
-            tokens += min(seq.num_pending, room, self._chunk or room) if room else 0
-
-    def _deal(self) -> list[ScheduledSeq]:
-        items: list[ScheduledSeq] = []
-        left = self._budget
-        for seq in self._running:  # decoding requests first: one token each, whatever the budget
-            if seq.num_pending == 1:
-                items.append(ScheduledSeq(seq, seq.tokens(seq.num_cached, seq.num_tokens), seq.num_cached, True))
-                left -= 1
-        for seq in self._running:  # then portions of prompts, in admission order
-            pending = seq.num_pending
-            if pending <= 1:
-                continue
-            room = max(left, 0)
-            count = min(pending, room, self._chunk or room)
-            if count <= 0:
-                continue
-            stop = seq.num_cached + count
-            items.append(ScheduledSeq(seq, seq.tokens(seq.num_cached, stop), seq.num_cached, stop == seq.num_tokens))
-            left -= count
-        return items
-
-    def _preempt(self, seq: Sequence) -> None:
-        self._running.remove(seq)
-        self._release(seq)
+    def _leave_running(self, seq: Sequence, requeue: bool) -> None:
+        """The one way out of RUNNING: the seat and every page go back to the cache manager."""
+        self._live.remove(seq)
+        if seq.seat is not None:
+            self._cache.close_seat(seq.seat)
+            seq.seat = None
+        if not requeue:
+            self._forget(seq)
+            return
         seq.num_cached = 0
-        seq.state = SeqState.WAITING
         seq.preemptions += 1
-        self._waiting.appendleft(seq)
+        seq.state = SeqState.WAITING
+        self._line.appendleft(seq)
         _log.info(
             "sequence preempted request_id=%s tokens=%s preemptions=%s", seq.request_id, seq.num_tokens, seq.preemptions
         )
 
-    def _finish(self, seq: Sequence) -> None:
-        self._running.remove(seq)
-        self._release(seq)
-        seq.state = SeqState.FINISHED
-        self._ids.pop(seq.request_id, None)
+    def _drop_cancelled(self) -> None:
+        for request_id in self._cancelled:
+            seq = self._book.get(request_id)
+            if seq is None:
+                continue
+            seq.finish_reason = "aborted"
+            if seq.is_running:
+                self._leave_running(seq, requeue=False)
+            else:
+                self._line.remove(seq)
+                self._forget(seq)
+            _log.info("sequence aborted request_id=%s", request_id)
+        self._cancelled.clear()
 
-    def _release(self, seq: Sequence) -> None:
-        if seq.seat is not None:
-            self._cache.close_seat(seq.seat)
-            seq.seat = None
+    def _make_room(self) -> None:
+        """Pages for every running request's known tokens, oldest first; the newest pays when the pool is short."""
+        position = 0
+        while position < len(self._live):
+            seq = self._live[position]
+            while seq.is_running and not self._cache.grow(seq.seat, seq.num_tokens):
+                self._leave_running(self._live[-1], requeue=True)  # may be seq itself
+            position += seq.is_running
+
+    def _share(self, pending: int, left: int) -> int:
+        """How many of a request's ``pending`` prompt tokens fit into ``left`` tokens of budget."""
+        room = max(left, 0)
+        return min(pending, room, self._chunk or room)
+
+    def _spoken_for(self) -> int:
+        """Tokens of this step's budget that the running requests will take."""
+        left = self._budget - sum(1 for seq in self._live if seq.num_pending == 1)
+        for seq in self._live:
+            if seq.num_pending > 1:
+                left -= self._share(seq.num_pending, left)
+        return self._budget - left
+
+    def _admit(self) -> None:
+        used = self._spoken_for()
+        while self._line and len(self._live) < self._max_seqs and self._cache.free_seats > 0:
+            seq = self._line[0]
+            if used >= self._budget and self._live:
+                break  # not one token of budget left for it; a request alone is always admitted
+            if not self._cache.can_grow(None, seq.num_tokens):
+                break
+            seat = self._cache.open_seat()
+            if not self._cache.grow(seat, seq.num_tokens):  # cannot happen after can_grow; stay safe
+                self._cache.close_seat(seat)
+                break
+            self._line.popleft()
+            seq.seat, seq.num_cached, seq.state = seat, 0, SeqState.RUNNING
+            self._live.append(seq)
+            used += self._share(seq.num_pending, self._budget - used)
+
+    def _deal(self) -> list[ScheduledSeq]:
+        decoding = [seq for seq in self._live if seq.num_pending == 1]
+        items = [ScheduledSeq(seq, seq.tokens(seq.num_cached, seq.num_tokens), seq.num_cached, True) for seq in decoding]
+        left = self._budget - len(decoding)  # decoding requests get their token whatever the budget
+        for seq in self._live:  # portions of prompts, in admission order
+            count = self._share(seq.num_pending, left) if seq.num_pending > 1 else 0
+            if count:
+                stop = seq.num_cached + count
+                items.append(ScheduledSeq(seq, seq.tokens(seq.num_cached, stop), seq.num_cached, stop == seq.num_tokens))
+                left -= count
+        return items

@@ -1,36 +1,41 @@
 """Where each scheduler step spends its time, logged every N steps.
 
-The split follows the reference's (worker/src/inference/step_stats.py:1-19):
+The parts of a step are the reference's (worker/src/inference/step_stats.py:1-19):
 ``sched`` (planning the step), ``gpu`` (the forward and sampling, ending with the
-copy of the token ids to the host), ``emit`` (appending tokens, finishing
-requests, callbacks); ``gpu`` is further split into ``kernel`` (between two CUDA
-events around the launches) and ``host = gpu - kernel``.  Steps are grouped by
-kind: ``decode`` (every request decodes one token) and ``prefill`` (any other).
-There is no ``wait`` part: this engine has no event loop between the parts.
+copy of the token ids to the host) and ``emit`` (appending tokens, ending requests,
+callbacks); ``gpu`` divides into ``kernel`` (between two CUDA events around the
+launches) and ``host = gpu - kernel``.  Steps are grouped by kind: ``decode`` (every
+request brings one token) and ``prefill`` (any other).  The reference's fourth part,
+``wait``, is the time its event loop takes to resume; this engine has no event loop.
+
+A window keeps one record per step; ``summary`` reduces the window to plain numbers
+per kind (which measuring code reads) and ``format`` renders them as the log line,
+laid out like the reference's (step_stats.py:82-100).
 """
 
 from __future__ import annotations
 
 import logging
-from dataclasses import dataclass, field
+from typing import NamedTuple
 
 _log = logging.getLogger(__name__)
 
 PARTS = ("sched", "gpu", "emit")
 
 
-@dataclass
-class _Group:
-    steps: int = 0
-    rows: int = 0
-    tokens: int = 0
-    ms: dict = field(default_factory=lambda: dict.fromkeys(PARTS, 0.0))
-    kernel_ms: float = 0.0
-    kernel_steps: int = 0
-    kernel_gpu_ms: float = 0.0
+class StepRecord(NamedTuple):
+    kind: str
+    rows: int
+    tokens: int
+    sched: float
+    gpu: float
+    emit: float
+    kernel: float | None  # None: the step was not bracketed by events
 
-    def total_ms(self) -> float:
-        return sum(self.ms.values())
+
+def _mean(values) -> float:
+    values = list(values)
+    return sum(values) / len(values) if values else 0.0
 
 
 class StepStats:
@@ -38,53 +43,59 @@ class StepStats:
         if every < 1:
             raise ValueError("step stats interval must be >= 1")
         self.every = every
-        self._groups: dict[str, _Group] = {}
-        self._steps = 0
-        self.lines: list[str] = []
+        self._window: list[StepRecord] = []
+        self.lines: list[str] = []          # every line logged so far
+        self.summaries: list[dict] = []     # and the numbers behind it
 
-    def record(self, kind: str, rows: int, tokens: int, kernel: float | None = None, **parts_ms: float) -> None:
-        missing = set(PARTS) - set(parts_ms)
-        if missing:
-            raise ValueError(f"missing step parts: {sorted(missing)}")
-        group = self._groups.setdefault(kind, _Group())
-        group.steps += 1
-        group.rows += rows
-        group.tokens += tokens
-        for name in PARTS:
-            group.ms[name] += parts_ms[name]
-        if kernel is not None:
-            group.kernel_ms += kernel
-            group.kernel_steps += 1
-            group.kernel_gpu_ms += parts_ms["gpu"]
-        self._steps += 1
-        if self._steps >= self.every:
+    def record(self, kind: str, rows: int, tokens: int, kernel: float | None = None, *, sched: float, gpu: float, emit: float) -> None:
+        self._window.append(StepRecord(kind, rows, tokens, sched, gpu, emit, kernel))
+        if len(self._window) >= self.every:
             self.flush()
 
+    def summary(self) -> dict:
+        """Per kind: steps, mean rows and tokens, mean milliseconds of each part, kernel/host where timed,
+        and the kind's share of the window's wall time; under ``"wall"`` each part's share of it."""
+        wall = sum(r.sched + r.gpu + r.emit for r in self._window) or 1.0
+        out: dict = {"steps": len(self._window), "kinds": {}, "wall": {}}
+        for kind in sorted({r.kind for r in self._window}):
+            steps = [r for r in self._window if r.kind == kind]
+            entry = {
+                "n": len(steps),
+                "rows": _mean(r.rows for r in steps),
+                "tok": _mean(r.tokens for r in steps),
+                **{part: _mean(getattr(r, part) for r in steps) for part in PARTS},
+                "share": sum(r.sched + r.gpu + r.emit for r in steps) / wall,
+            }
+            timed = [r for r in steps if r.kernel is not None]
+            if timed:
+                entry["kernel"] = _mean(r.kernel for r in timed)
+                entry["host"] = _mean(r.gpu - r.kernel for r in timed)
+            out["kinds"][kind] = entry
+        for part in PARTS:
+            out["wall"][part] = sum(getattr(r, part) for r in self._window) / wall
+        return out
+
+    def format(self, summary: dict | None = None) -> str:
+        summary = summary or self.summary()
+        fields = [f"step stats steps={summary['steps']}"]
+        for kind, e in summary["kinds"].items():
+            parts = " ".join(f"{part}={e[part]:.2f}" for part in PARTS)
+            if "kernel" in e:
+                parts += f" (kernel={e['kernel']:.2f} host={e['host']:.2f})"
+            fields.append(
+                f"{kind} n={e['n']} rows={e['rows']:.1f} tok={e['tok']:.0f} ms/step[{parts}] share={100 * e['share']:.0f}%"
+            )
+        fields.append("wall " + " ".join(f"{part}={100 * summary['wall'][part]:.0f}%" for part in PARTS))
+        return " | ".join(fields)
+
     def flush(self) -> str | None:
-        if self._steps == 0:
+        """Log the window and start a new one; None when the window is empty."""
+        if not self._window:
             return None
-        line = self.format()
+        summary = self.summary()
+        line = self.format(summary)
         _log.info("%s", line)
         self.lines.append(line)
-        self._groups.clear()
-        self._steps = 0
+        self.summaries.append(summary)
+        self._window.clear()
         return line
-
-    def format(self) -> str:
-        wall = sum(g.total_ms() for g in self._groups.values()) or 1.0
-        pieces = [f"step stats steps={self._steps}"]
-        for kind in sorted(self._groups):
-            g = self._groups[kind]
-            n = g.steps
-            avg = " ".join(f"{name}={g.ms[name] / n:.2f}" for name in PARTS)
-            if g.kernel_steps:
-                kernel = g.kernel_ms / g.kernel_steps
-                host = (g.kernel_gpu_ms - g.kernel_ms) / g.kernel_steps
-                avg += f" (kernel={kernel:.2f} host={host:.2f})"
-            pieces.append(
-                f"{kind} n={n} rows={g.rows / n:.1f} tok={g.tokens / n:.0f} "
-                f"ms/step[{avg}] share={100 * g.total_ms() / wall:.0f}%"
-            )
-        totals = {name: sum(g.ms[name] for g in self._groups.values()) for name in PARTS}
-        pieces.append("wall " + " ".join(f"{name}={100 * totals[name] / wall:.0f}%" for name in PARTS))
-        return " | ".join(pieces)

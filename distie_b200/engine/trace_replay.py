@@ -42,9 +42,12 @@ class TraceSession:
         self.live: dict[str, list[int]] = {}  # id -> [seat, cached tokens]
 
     @classmethod
-    def open(cls, model: str, dtype: str, max_tokens: int, page_size: int = 16, device: str = "cuda") -> "TraceSession":
+    def open(cls, model: str, dtype: str, max_tokens: int, page_size: int = 16, device: str = "cuda",
+             decode_graphs: bool = True) -> "TraceSession":
         """``max_tokens``: the most tokens live requests hold at any time, each request's count
-        rounded up to a multiple of 64; the pool is made for exactly this many, so pages are reused."""
+        rounded up to a multiple of 64; the pool is made for exactly this many, so pages are reused.
+        With ``decode_graphs`` a step in which every request brings one token replays the captured
+        decode step of its batch bucket, as generation does."""
         rounded = -(-int(max_tokens) // 64) * 64
         engine = Engine.load(
             model,
@@ -55,7 +58,7 @@ class TraceSession:
             max_seqs=LIVE_REQUESTS,
             token_budget=rounded,
             max_model_len=rounded,
-            decode_graphs=False,
+            decode_graphs=decode_graphs,
         )
         return cls(engine)
 
@@ -127,9 +130,12 @@ def main(argv=None) -> int:
     parser.add_argument("--out", required=True, help="folder for <step>.f32 files")
     parser.add_argument("--max-tokens", type=int, required=True, help="most tokens live requests hold at any time")
     parser.add_argument("--page-size", type=int, default=16, help="tokens per cache page (default 16)")
+    parser.add_argument("--no-decode-graphs", action="store_true",
+                        help="run steps of single tokens eagerly instead of replaying captured decode steps")
     args = parser.parse_args(argv)
     print(f"[distie_b200] loading {args.model} as {args.dtype}", file=sys.stderr, flush=True)
-    session = TraceSession.open(args.model, args.dtype, args.max_tokens, args.page_size)
+    session = TraceSession.open(args.model, args.dtype, args.max_tokens, args.page_size,
+                                decode_graphs=not args.no_decode_graphs)
     print("[distie_b200] ready", file=sys.stderr, flush=True)
     replay(session, sys.stdin, args.out)
     return 0

@@ -63,11 +63,16 @@ class DeviceKernels(KernelSet):
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.error_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.launches = 0  # own kernels launched (library products are not counted)
+        self.kernel_counts: dict[str, int] = {}  # the same, by launcher
 
     # -- helpers ------------------------------------------------------------
     @staticmethod
     def _stream() -> int:
         return torch.cuda.current_stream().cuda_stream
+
+    def _ran(self, name: str, kernels: int = 1) -> None:
+        self.launches += kernels
+        self.kernel_counts[name] = self.kernel_counts.get(name, 0) + 1
 
     def check_errors(self) -> None:
         code = int(self.error_flag.item())
@@ -85,7 +90,7 @@ class DeviceKernels(KernelSet):
             ),
             "embed",
         )
-        self.launches += 1
+        self._ran("embed")
 
     def add_rmsnorm(self, delta, residual, weight, eps, out, rows_index=None) -> None:
         rows = out.shape[0]
@@ -96,7 +101,7 @@ class DeviceKernels(KernelSet):
                 out.data_ptr(), rows_ptr, rows, residual.shape[1], float(eps), self.code, self._stream(),
             )
             if code == 0:
-                self.launches += 1
+                self._ran("add_rmsnorm_split")
                 return
             if code != -2:
                 check(code, "add_rmsnorm_split")
@@ -115,7 +120,7 @@ class DeviceKernels(KernelSet):
             ),
             "add_rmsnorm",
         )
-        self.launches += 1
+        self._ran("add_rmsnorm")
 
     def linear_split(self, x, weight):
         if self._skinny(x, weight):
@@ -164,7 +169,7 @@ class DeviceKernels(KernelSet):
             ),
             "gemm_tcgen05",
         )
-        self.launches += 1
+        self._ran("gemm_tcgen05")
 
     def _skinny(self, x, weight) -> bool:
         return (
@@ -183,7 +188,7 @@ class DeviceKernels(KernelSet):
             ),
             "gemm_tcgen05_skinny",
         )
-        self.launches += 1
+        self._ran("gemm_tcgen05_skinny")
 
     def linear_swiglu(self, x, weight):
         if self._skinny(x, weight) and weight.shape[0] % 2 == 0:
@@ -205,7 +210,7 @@ class DeviceKernels(KernelSet):
             ),
             "bias_cast",
         )
-        self.launches += 1
+        self._ran("bias_cast")
         return out
 
     def swiglu(self, gate_up, out) -> None:
@@ -215,7 +220,7 @@ class DeviceKernels(KernelSet):
             ),
             "swiglu",
         )
-        self.launches += 1
+        self._ran("swiglu")
 
     def rope_kv_write(self, qkv, step, kv, rotary, num_heads, num_kv_heads, head_dim, bias=None, q_out=None) -> None:
         write = kv is not None
@@ -242,7 +247,7 @@ class DeviceKernels(KernelSet):
                 *tail, step.num_tokens, *sizes,
             )
             if code == 0:
-                self.launches += 1
+                self._ran("rope_kv_write_split")
                 return
             if code != -2:
                 check(code, "rope_kv_write_split")
@@ -258,7 +263,7 @@ class DeviceKernels(KernelSet):
             function("distie_rope_kv_write")(qkv.data_ptr(), *tail, step.num_tokens, qkv.stride(0), *sizes),
             "rope_kv_write",
         )
-        self.launches += 1
+        self._ran("rope_kv_write")
         if q_out is not None:
             q_out.copy_(qkv[:, : num_heads * head_dim])
 
@@ -301,7 +306,7 @@ class DeviceKernels(KernelSet):
                     function("distie_attention_decode")(*head, self.code, self.error_flag.data_ptr(), self._stream()),
                     "attention_decode",
                 )
-            self.launches += 1 if in_kernel_merge else 2
+            self._ran("attention_decode_mma" if tensor_cores else "attention_decode", 1 if in_kernel_merge else 2)
         rest = step.num_tokens - n_dec
         tiled = rest > 0 and self.dtype == torch.bfloat16 and head_dim in _PREFILL_HEAD_DIMS and step.num_q_tiles and n_dec == step.num_decode_tokens
         if tiled and self._attention_tcgen05(qkv, out, step, kv, num_heads, num_kv_heads, head_dim, window, scale):
@@ -317,7 +322,7 @@ class DeviceKernels(KernelSet):
                 ),
                 "attention_prefill",
             )
-            self.launches += 1
+            self._ran("attention_prefill")
         elif rest > 0:
             check(
                 function("distie_attention_generic")(
@@ -330,7 +335,7 @@ class DeviceKernels(KernelSet):
                 ),
                 "attention_generic",
             )
-            self.launches += 1
+            self._ran("attention_generic")
 
     def _attention_tcgen05(self, qkv, out, step, kv, num_heads, num_kv_heads, head_dim, window, scale) -> bool:
         """Prompt portions on the tcgen05 kernel; False when it refuses the page size or an alignment."""
@@ -346,7 +351,7 @@ class DeviceKernels(KernelSet):
         if code == -2:
             return False
         check(code, "attention_prefill_tcgen05")
-        self.launches += 1
+        self._ran("attention_prefill_tcgen05")
         return True
 
     def sample(self, logits, temperatures, uniforms, out_tokens) -> None:
@@ -358,4 +363,4 @@ class DeviceKernels(KernelSet):
             ),
             "sample",
         )
-        self.launches += 1
+        self._ran("sample")

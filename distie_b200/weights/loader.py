@@ -9,21 +9,32 @@ unexpected or of the wrong shape.
 
 Conversion on the way to the device:
 
-* ``matrix`` / ``table``: the engine's dtype.  bfloat16 engine: bfloat16 and
-  float16 tensors become bfloat16, a tensor stored in float32 stays float32 (its
-  products then run in float32).  float32 engine: everything becomes float32.
-* ``bias`` / ``norm``: float32 (exact for bfloat16 inputs).
+* ``matrix`` / ``table``: the engine's dtype, as the reference loads with the dtype
+  it serves in (worker/src/inference/torch_engine.py:135-141).  float32 engine:
+  everything becomes float32.  bfloat16 engine: bfloat16 and float16 tensors become
+  bfloat16; what happens to a tensor stored in 32-bit is the ``float32_weights``
+  policy.  ``"auto"`` (the default): a checkpoint that stores EVERY matrix in 32-bit
+  is a float32 checkpoint and is cast; in a checkpoint that stores matrices in
+  16-bit, one stored in 32-bit was kept wide on purpose and stays so (its products
+  then run in float32).  ``"keep"``: 32-bit tensors always stay; ``"cast"``: never.
+* ``bias`` / ``norm``: float32 (exact for bfloat16 inputs): stored in 32-bit they stay so.
 * integer tensors: int32.
 """
 
 from __future__ import annotations
 
+import logging
 from typing import Iterable, Mapping
 
 import torch
 
 from ..parts.base import TensorSpec
 from .safetensors_io import ModelTensors
+
+
+_log = logging.getLogger(__name__)
+FLOAT32_POLICIES = ("auto", "keep", "cast")
+_WIDE = (torch.float32, torch.float64)
 
 
 class WeightsError(ValueError):
@@ -80,12 +91,24 @@ def check_checkpoint(
 class WeightStore:
     """Hands converted device tensors to the parts, each name once (tied uses share the tensor)."""
 
-    def __init__(self, source, specs: Iterable[TensorSpec], dtype: torch.dtype, device) -> None:
+    def __init__(self, source, specs: Iterable[TensorSpec], dtype: torch.dtype, device, float32_weights: str = "auto") -> None:
+        if float32_weights not in FLOAT32_POLICIES:
+            raise ValueError(f"float32_weights must be one of {FLOAT32_POLICIES}, got {float32_weights!r}")
         self._source = source  # anything with .tensor(name) -> CPU tensor
         self._roles = {s.name: s.role for s in specs}
         self.dtype = dtype
         self.device = torch.device(device) if device is not None else None
         self._cache: dict[str, torch.Tensor] = {}
+        self.keep_wide = False  # whether a matrix stored in 32-bit stays 32-bit in a 16-bit engine
+        if dtype != torch.float32 and float32_weights != "cast":
+            stored = [source.dtype(n) for n, role in self._roles.items() if role in ("matrix", "table") and n in set(source.keys())]
+            wide = [d for d in stored if d in _WIDE]
+            self.keep_wide = bool(wide) and (float32_weights == "keep" or len(wide) < len(stored))
+            if self.keep_wide:
+                _log.warning(
+                    "%s of %s matrices are stored in 32-bit and stay so: their products run in float32, "
+                    "not on the %s kernels (float32_weights='cast' converts them)", len(wide), len(stored), dtype,
+                )
 
     def _convert(self, name: str, role: str) -> torch.Tensor:
         key = f"{role}:{name}"
@@ -96,7 +119,7 @@ class WeightStore:
             target = torch.int32
         elif role in ("bias", "norm"):
             target = torch.float32
-        elif self.dtype == torch.float32 or raw.dtype in (torch.float32, torch.float64):
+        elif self.dtype == torch.float32 or (self.keep_wide and raw.dtype in _WIDE):
             target = torch.float32
         else:
             target = self.dtype
@@ -142,7 +165,7 @@ class DictSource:
         return self._tensors[name]
 
 
-def open_weights(folder_or_dict, specs, tolerated, dtype: torch.dtype, device) -> WeightStore:
+def open_weights(folder_or_dict, specs, tolerated, dtype: torch.dtype, device, float32_weights: str = "auto") -> WeightStore:
     """Open a model folder (or a dict of tensors), check it against ``specs``, return the store."""
     if isinstance(folder_or_dict, Mapping):
         source = DictSource(folder_or_dict)
@@ -158,4 +181,4 @@ def open_weights(folder_or_dict, specs, tolerated, dtype: torch.dtype, device) -
         tolerated,
         {name: source.dtype(name) for name in names},
     )
-    return WeightStore(source, specs, dtype, device)
+    return WeightStore(source, specs, dtype, device, float32_weights)

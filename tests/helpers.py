@@ -36,7 +36,41 @@ TINY_B = {
     "tie_word_embeddings": False,
     "max_position_embeddings": 1024,
 }
-TINY = {"A": (TINY_A, 16, 0, 0.0), "B": (TINY_B, 8, 1, 0.02)}  # config, page size, seed, norm noise
+# Two more with the head sizes of real models (64 and 128): in bfloat16 these run on the tensor-core
+# attention kernels and, from 128 rows on, the tensor-core products, which the first two never reach.
+TINY_C = {
+    "architectures": ["Qwen2ForCausalLM"],
+    "vocab_size": 1000,
+    "hidden_size": 256,
+    "intermediate_size": 416,
+    "num_hidden_layers": 2,
+    "num_attention_heads": 4,
+    "num_key_value_heads": 2,
+    "head_dim": 64,
+    "rms_norm_eps": 1e-6,
+    "rope_theta": 10000.0,
+    "tie_word_embeddings": True,
+    "max_position_embeddings": 2048,
+}
+TINY_D = {
+    "architectures": ["Qwen2ForCausalLM"],
+    "vocab_size": 2003,
+    "hidden_size": 512,
+    "intermediate_size": 1384,
+    "num_hidden_layers": 3,
+    "num_attention_heads": 4,
+    "num_key_value_heads": 1,
+    "head_dim": 128,
+    "rms_norm_eps": 1e-5,
+    "rope_theta": 1000000.0,
+    "tie_word_embeddings": False,
+    "max_position_embeddings": 4096,
+}
+# config, page size, seed, norm noise
+TINY = {"A": (TINY_A, 16, 0, 0.0), "B": (TINY_B, 8, 1, 0.02), "C": (TINY_C, 16, 2, 0.0), "D": (TINY_D, 32, 3, 0.02)}
+# Standard deviation of the test weights per configuration: wide layers need smaller weights for logits
+# of a scale at which a wrong key shows without saturating the softmax.
+STD = {"A": 0.2, "B": 0.2, "C": 0.1, "D": 0.07}
 
 # Weights far larger than N(0, 0.02): logits then have a scale at which a wrong key shows.
 TEST_STD = 0.2
@@ -52,7 +86,7 @@ BF16_TOP1_MARGIN = 0.02  # pooled top-1 agreement may fall this far below theirs
 
 def tiny(name: str):
     cfg, page, seed, noise = TINY[name]
-    return dict(cfg), page, plain.random_weights(cfg, seed, std=TEST_STD, norm_noise=noise)
+    return dict(cfg), page, plain.random_weights(cfg, seed, std=STD[name], norm_noise=noise)
 
 
 def bf16_rounded(weights: dict) -> dict:
@@ -113,11 +147,16 @@ def schedule_portions(requests: dict) -> list[dict]:
     return steps
 
 
-def schedule_mixed(requests: dict, seed: int = 0, live_max: int = 4) -> list[dict]:
-    """Up to four live requests; portions of some beside single tokens of others; some sit a step out."""
+def schedule_mixed(requests: dict, seed: int = 0, live_max: int = 4, refeed: int = 0) -> list[dict]:
+    """Up to four live requests; portions of some beside single tokens of others; some sit a step out.
+
+    With ``refeed`` that many requests are ended early, once each, somewhere past their middle (what a
+    preemption does: their pages go back) and fed again from position 0 later, under the same id.
+    """
     rng = random.Random(seed)
     waiting = list(requests.items())
     live: dict[str, int] = {}
+    sent_back: set[str] = set()
     steps, n = [], 0
     while waiting or live:
         while waiting and len(live) < live_max and (not live or rng.random() < 0.7):
@@ -128,6 +167,12 @@ def schedule_mixed(requests: dict, seed: int = 0, live_max: int = 4) -> list[dic
             ids, at = requests[rid], live[rid]
             if len(live) > 1 and rng.random() < 0.2:
                 continue  # left out of this step, goes on later
+            if len(sent_back) < refeed and rid not in sent_back and at >= len(ids) // 2 and steps:
+                sent_back.add(rid)  # given up after the step before; comes back from position 0
+                steps[-1]["end"].append(rid)
+                del live[rid]
+                waiting.insert(min(1, len(waiting)), (rid, ids))
+                continue
             left = len(ids) - at
             if at > 0 and rng.random() < 0.5:
                 size = 1
@@ -161,9 +206,15 @@ def peak_tokens(steps: list[dict], granule: int = 64) -> int:
 
 
 def collect(steps: list[dict], outputs: dict) -> dict:
-    """Per request, the logits of every position, gathered from per-step outputs {step: array [wanted, vocab]}."""
+    """Per request, the logits of every position, gathered from per-step outputs {step: array [wanted, vocab]}.
+
+    A request that was ended early and fed again appears twice: the pass that was given up under
+    ``"<id>#<n>"`` (its first positions only), the complete one under its id; see `expected_for`.
+    """
     rows: dict[str, dict[int, torch.Tensor]] = {}
     cursor: dict[str, int] = {}
+    passes: dict[str, int] = {}
+    done: dict[str, torch.Tensor] = {}
     for step in steps:
         out = outputs.get(step["step"])
         at = 0
@@ -173,7 +224,28 @@ def collect(steps: list[dict], outputs: dict) -> dict:
                 rows.setdefault(entry["id"], {})[base + place] = torch.as_tensor(out[at])
                 at += 1
             cursor[entry["id"]] = base + len(entry["tokens"])
-    return {rid: torch.stack([r[i] for i in sorted(r)]) for rid, r in rows.items()}
+        for rid in step["end"]:
+            held = rows.pop(rid, None)
+            cursor.pop(rid, None)
+            if held is None:
+                continue
+            if rid in done:  # an earlier pass was given up: keep it under a name of its own
+                passes[rid] = passes.get(rid, 0) + 1
+                done[f"{rid}#{passes[rid]}"] = done[rid]
+            done[rid] = torch.stack([held[i] for i in sorted(held)])
+    for rid, held in rows.items():  # schedules that never end their requests
+        done[rid] = torch.stack([held[i] for i in sorted(held)])
+    return done
+
+
+def expected_for(got: dict, expected: dict) -> dict:
+    """`expected` with an entry for every pass `collect` found: a pass that was given up is compared
+    with the first positions of its request."""
+    out = dict(expected)
+    for key, value in got.items():
+        if "#" in key:
+            out[key] = expected[key.split("#")[0]][: value.shape[0]]
+    return out
 
 
 def run_schedule(session, steps: list[dict]) -> dict:
@@ -270,3 +342,53 @@ def toy_arrangement_spec(cfg: dict):
         layers[index] = replace(layers[index], mixer=PartSpec(mixer.kind, {**mixer.params, "window": TOY_WINDOW}, mixer.prefix))
     order = (LayerCall(0, 0, True), LayerCall(1, 1, True), LayerCall(0, 2, True), LayerCall(2, 1, False))
     return replace(spec, layers=tuple(layers), order=order)
+
+
+# -- temperature sampling against an oracle -------------------------------------------------------------
+def check_sampled_tokens(prompt, outputs, weights, cfg, temperature: float, seed: int, slack: float = 2e-4) -> None:
+    """Every sampled token must be the inverse-CDF pick of the plain implementation's distribution.
+
+    Output ``i`` of a request is drawn at ``u = uniform(seed, i)`` from
+    ``plain.temperature_probabilities(logits after prompt + outputs[:i])``: the first token whose cumulative
+    probability exceeds ``u``.  The engine's logits differ from the plain ones by rounding, so a token
+    next to the oracle's is accepted when ``u`` lies within ``slack`` of the boundary between the two.
+    """
+    from distie_b200.sampling.sampler import uniform
+
+    ids = list(prompt) + list(outputs)
+    logits = plain.forward_logits(ids[:-1], weights, cfg)[len(prompt) - 1 :]
+    assert logits.shape[0] == len(outputs)
+    for index, token in enumerate(outputs):
+        cdf = torch.cumsum(plain.temperature_probabilities(logits[index], temperature).double(), dim=0)
+        u = uniform(seed, index) * float(cdf[-1])
+        low = float(cdf[token - 1]) if token > 0 else 0.0
+        high = float(cdf[token])
+        assert low - slack <= u < high + slack, (
+            f"output {index}: token {token} covers [{low:.6f}, {high:.6f}) of the cumulative distribution, u = {u:.6f}"
+        )
+
+
+TINY_B_PROMPTS = (1, 5, 17, 40, 63)  # the workload of the second tiny configuration: prompts of these lengths,
+TINY_B_CHUNK, TINY_B_STEPS, TINY_B_TEMPERATURE, TINY_B_SEED = 11, 24, 0.8, 1  # portions of 11, 24 tokens each at T = 0.8
+
+
+def run_tiny_b_workload(engine, cfg):
+    """Five requests, prompts cut into portions of 11 beside decoding ones, temperature 0.8 from seed 1, 24
+    tokens each, and one preemption forced on the request that was admitted last once it has decoded a few
+    tokens.  Returns (prompts, results)."""
+    from distie_b200.engine.engine import GenerateRequest
+
+    prompts = [random_ids(cfg["vocab_size"], n, 400 + n) for n in TINY_B_PROMPTS]
+    requests = [GenerateRequest(f"w{i}", p, TINY_B_STEPS, TINY_B_TEMPERATURE, TINY_B_SEED + i) for i, p in enumerate(prompts)]
+    forced, seen = [], []
+
+    def on_token(request_id, token, finished):
+        # Called between steps (a step ahead may already be in flight: its row for this request is dropped).
+        if request_id == "w4":
+            seen.append(token)
+            if len(seen) == 5:
+                forced.append(engine.scheduler.force_preempt("w4"))
+
+    results = engine.run(requests, ignore_eos=True, on_token=on_token)
+    assert forced == [True], "the forced preemption did not happen"
+    return prompts, results

@@ -44,7 +44,7 @@ def rope_tables(positions: torch.Tensor, head_dim: int, theta: float):
 
     worker/src/inference/qwen2/model.py:101-105
     """
-    freqs = positions.float()[:, None] * rope_inverse_frequencies(head_dim, theta)[None, :]
+    freqs = positions.float()[:, None] * rope_inverse_frequencies(head_dim, theta).to(positions.device)[None, :]
     emb = torch.cat((freqs, freqs), dim=-1)
     return emb.cos(), emb.sin()
 
@@ -60,15 +60,15 @@ def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.T
     return x * cos[:, None, :] + rotate_half(x) * sin[:, None, :]
 
 
-def visible_mask(num_tokens: int, window: int | None = None) -> torch.Tensor:
+def visible_mask(num_tokens: int, window: int | None = None, device=None) -> torch.Tensor:
     """True where query ``i`` may see key ``j``: ``j <= i`` (model.py:128-135).
 
     ``window`` (not in the reference, which rejects windowed layers at
     model.py:58-60) additionally hides keys with ``i - j >= window``; toy layers of
     the tests use it.
     """
-    i = torch.arange(num_tokens)[:, None]
-    j = torch.arange(num_tokens)[None, :]
+    i = torch.arange(num_tokens, device=device)[:, None]
+    j = torch.arange(num_tokens, device=device)[None, :]
     mask = j <= i
     if window is not None:
         mask &= (i - j) < window
@@ -95,7 +95,7 @@ def attention_mix(
     kk = k.repeat_interleave(rep, dim=1)
     vv = v.repeat_interleave(rep, dim=1)
     scores = torch.einsum("thd,shd->hts", q, kk) * scale
-    mask = visible_mask(num_tokens, window)
+    mask = visible_mask(num_tokens, window, q.device)
     scores = scores.masked_fill(~mask[None], torch.finfo(scores.dtype).min)
     weights = torch.softmax(scores, dim=-1, dtype=torch.float32).to(q.dtype)
     return torch.einsum("hts,shd->thd", weights, vv)
@@ -188,8 +188,9 @@ def forward_logits(ids, w: dict, cfg: dict, order=None) -> torch.Tensor:
     ``order`` is a list of ``(layer, window, reads_kv_of)`` for toy arrangements;
     the architecture itself runs every layer once, in order, with full attention.
     """
-    ids = torch.as_tensor(ids, dtype=torch.long)
-    positions = torch.arange(ids.shape[0])
+    device = w["model.embed_tokens.weight"].device  # tensors on another device than the CPU: everything runs there
+    ids = torch.as_tensor(ids, dtype=torch.long, device=device)
+    positions = torch.arange(ids.shape[0], device=device)
     h = embedding(ids, w["model.embed_tokens.weight"])
     if order is None:
         order = [(i, None, None) for i in range(cfg["num_hidden_layers"])]

@@ -152,3 +152,76 @@ def test_safetensors_reader_rejects_damage(tmp_path):
         SafetensorsFile(str(path))
     with pytest.raises(FileNotFoundError):
         ModelTensors(str(tmp_path / "nothing"))
+
+
+def test_a_float32_checkpoint_is_cast_by_a_16_bit_engine_unless_told_otherwise():
+    """Every matrix stored in 32-bit: the checkpoint simply is a float32 one, and a bfloat16 engine casts
+    it as the reference does (worker/src/inference/torch_engine.py:135-141); vectors stay 32-bit."""
+    import plain_qwen2 as plain
+
+    cfg = Qwen2Config.from_dict(helpers.TINY_A)
+    spec = get_architecture("Qwen2ForCausalLM").recipe(cfg)
+    specs = model_tensor_specs(spec)
+    tensors = plain.random_weights(helpers.TINY_A, 0)  # all float32
+    name = "model.layers.1.self_attn.o_proj.weight"
+    auto = open_weights(tensors, specs, spec.tolerated, torch.bfloat16, None)
+    assert auto.matrix(name).dtype == torch.bfloat16 and auto.table("model.embed_tokens.weight").dtype == torch.bfloat16
+    assert auto.vector("model.norm.weight").dtype == torch.float32
+    keep = open_weights(tensors, specs, spec.tolerated, torch.bfloat16, None, float32_weights="keep")
+    assert keep.matrix(name).dtype == torch.float32
+    mixed = {k: v.to(torch.bfloat16) for k, v in tensors.items()}
+    mixed[name] = tensors[name]
+    assert open_weights(mixed, specs, spec.tolerated, torch.bfloat16, None).matrix(name).dtype == torch.float32
+    cast = open_weights(mixed, specs, spec.tolerated, torch.bfloat16, None, float32_weights="cast")
+    assert cast.matrix(name).dtype == torch.bfloat16
+    with pytest.raises(ValueError, match="float32_weights"):
+        open_weights(tensors, specs, spec.tolerated, torch.bfloat16, None, float32_weights="sometimes")
+    with pytest.raises(ValueError, match="float32_weights"):
+        EngineConfig(float32_weights="sometimes")
+
+
+def test_sharded_checkpoint_round_trip(tmp_path):
+    """``model.safetensors.index.json`` with two shards reads like one file; a name in the wrong shard is an error."""
+    import plain_qwen2 as plain
+    from distie_b200.weights import SafetensorsError
+
+    cfg = Qwen2Config.from_dict(helpers.TINY_B)
+    spec = get_architecture("Qwen2ForCausalLM").recipe(cfg)
+    tensors = {k: v.to(torch.bfloat16) for k, v in plain.random_weights(helpers.TINY_B, 1).items()}
+    names = sorted(tensors)
+    shards = {"model-00001-of-00002.safetensors": names[::2], "model-00002-of-00002.safetensors": names[1::2]}
+    weight_map = {}
+    for shard, members in shards.items():
+        save_file({n: tensors[n] for n in members}, str(tmp_path / shard))
+        weight_map.update({n: shard for n in members})
+    (tmp_path / "model.safetensors.index.json").write_text(json.dumps({"metadata": {}, "weight_map": weight_map}))
+    stored = ModelTensors(str(tmp_path))
+    assert sorted(stored.keys()) == names
+    for name in names:
+        assert stored.shape(name) == tuple(tensors[name].shape) and torch.equal(stored.tensor(name), tensors[name])
+    store = open_weights(str(tmp_path), model_tensor_specs(spec), spec.tolerated, torch.bfloat16, None)
+    assert torch.equal(store.matrix("lm_head.weight"), tensors["lm_head.weight"])
+    weight_map[names[0]] = "model-00002-of-00002.safetensors"
+    (tmp_path / "model.safetensors.index.json").write_text(json.dumps({"weight_map": weight_map}))
+    with pytest.raises(SafetensorsError, match="not in shard"):
+        ModelTensors(str(tmp_path))
+
+
+def test_cache_sizing_from_a_memory_budget(monkeypatch):
+    from distie_b200.cache import pages_that_fit
+    from distie_b200.parts import CacheNeed
+
+    # 28 slots of 2 kv heads x 128 in bfloat16, pages of 16: 28,672 bytes a token, 458,752 a page.
+    needs = {slot: CacheNeed(2, 128, None) for slot in range(28)}
+    assert pages_that_fit(needs, 16, 2, 458_752 * 1001) == 1000, "one page of the budget is the spare page"
+    assert pages_that_fit(needs, 16, 4, 458_752 * 1001) == 499
+    with pytest.raises(ValueError):
+        pages_that_fit({}, 16, 2, 1 << 30)
+    assert EngineConfig(gpu_mem_fraction=0.5).sized(77).num_blocks == 77
+    assert EngineConfig(gpu_mem_fraction=0.5).sized(77).gpu_mem_fraction is None
+    with pytest.raises(ValueError, match="gpu_mem_fraction"):
+        EngineConfig(gpu_mem_fraction=1.5)
+    monkeypatch.setenv("WORKER_GPU_MEM_FRACTION", "0.25")
+    assert EngineConfig.from_env().gpu_mem_fraction == 0.25
+    assert EngineConfig.from_env(num_blocks=64).gpu_mem_fraction is None, "an explicit page count wins"
+    assert EngineConfig.from_env(num_blocks=64, gpu_mem_fraction=0.5).gpu_mem_fraction == 0.5

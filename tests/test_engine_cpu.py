@@ -156,3 +156,92 @@ def test_run_order_is_data(mode):
     error, rid, at = helpers.worst_error(got, expected)
     assert error <= helpers.FP32_TOL, f"{mode}: request {rid} position {at} off by {error:.2e} of the logit scale"
     assert cache.free_pages() == cache.total_pages() and cache.free_seats == cache.max_seats
+
+
+def test_a_refused_request_leaves_nothing_behind():
+    """A batch whose second request can never fit is refused as a whole: nothing waits in the scheduler
+    for the next call to pick up, and no page or seat is held."""
+    from distie_b200.cache import CacheExhausted
+    from distie_b200.engine.engine import GenerateRequest
+
+    engine, cfg, weights = cpu_engine("A", num_blocks=8, max_seqs=4)  # 128 tokens of cache
+    fits = helpers.random_ids(cfg["vocab_size"], 9, 1)
+    never = helpers.random_ids(cfg["vocab_size"], 200, 2)
+    with pytest.raises(CacheExhausted, match="can never fit"):
+        engine.run([GenerateRequest("a", fits, 4), GenerateRequest("b", never, 4), GenerateRequest("c", fits, 4)])
+    assert not engine.scheduler.has_work() and not engine.has_work()
+    assert engine.cache.free_pages() == engine.cache.total_pages() and engine.cache.free_seats == engine.cache.max_seats
+    with pytest.raises(ValueError, match="duplicate"):
+        engine.run([GenerateRequest("a", fits, 4), GenerateRequest("a", fits, 4)])
+    assert not engine.scheduler.has_work()
+    steps_before = engine.steps
+    out = engine.run([GenerateRequest("a", fits, 4)])
+    assert out[0].token_ids == plain.greedy_generate(fits, weights, cfg, 4)
+    assert engine.steps - steps_before == 4, "only the one request ran: nothing was left over from the refused batch"
+
+
+def kv_rows(engine, seat: int, tokens: int) -> dict:
+    """The keys and values a request holds, gathered through its block table: {slot: (k, v) [tokens, heads, dim]}."""
+    cache = engine.cache
+    out = {}
+    for group, ids in zip(cache.groups, cache.pages_held(seat).values()):
+        pages = torch.tensor(ids, dtype=torch.long, device=group.slab.device)
+        for index, slot in enumerate(group.slots):
+            k, v = (group.slab[index, which].index_select(0, pages) for which in (0, 1))  # [pages, heads, page, dim]
+            out[slot] = tuple(t.permute(0, 2, 1, 3).reshape(-1, t.shape[1], t.shape[3])[:tokens].float().cpu() for t in (k, v))
+    return out
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_two_slabs_hold_equal_keys_and_values(name):
+    """The same requests cut two ways (whole, and in portions mixed with single tokens) leave the same keys
+    and values in their pages, not only the same logits (the reference's two-slab comparison,
+    worker/tests/test_qwen2_batch.py:71-109)."""
+    cfg, page, _ = helpers.tiny(name)
+    requests = requests_for(cfg, [40, 67, 33, 50])
+    slabs = []
+    for schedule in (helpers.schedule_whole, helpers.schedule_mixed):
+        steps = [dict(step, end=[]) for step in schedule(requests)]  # nobody ends: the pages stay held
+        engine, _, _ = cpu_engine(name, num_blocks=4 * 128 // page)
+        session = TraceSession(engine)
+        helpers.run_schedule(session, steps)
+        slabs.append({rid: kv_rows(engine, session.live[rid][0], len(ids)) for rid, ids in requests.items()})
+    for rid in requests:
+        for slot, (k, v) in slabs[0][rid].items():
+            k2, v2 = slabs[1][rid][slot]
+            for a, b in ((k, k2), (v, v2)):  # 1e-5 of the largest entry: the sums run in another order, nothing more
+                assert float(a.abs().max()) > 0
+                assert float((a - b).abs().max()) <= 1e-5 * max(1.0, float(a.abs().max())), (rid, slot)
+
+
+def test_second_tiny_workload_against_the_sampling_oracle():
+    """Prompts of 1/5/17/40/63 tokens in portions of 11 beside decoding requests, temperature 0.8 from
+    seed 1, 24 tokens each, one forced preemption: every token is the oracle's inverse-CDF pick."""
+    engine, cfg, weights = cpu_engine("B", num_blocks=64, max_seqs=8, token_budget=24, prefill_chunk=helpers.TINY_B_CHUNK)
+    prompts, results = helpers.run_tiny_b_workload(engine, cfg)
+    assert results[4].preemptions == 1 and all(len(r.token_ids) == helpers.TINY_B_STEPS for r in results)
+    for index, (prompt, result) in enumerate(zip(prompts, results)):
+        helpers.check_sampled_tokens(prompt, result.token_ids, weights, cfg, helpers.TINY_B_TEMPERATURE, helpers.TINY_B_SEED + index)
+    assert engine.cache.free_pages() == engine.cache.total_pages()
+
+
+def test_step_statistics_split_and_line():
+    from distie_b200.engine.step_stats import StepStats
+
+    stats = StepStats(every=3)
+    stats.record("prefill", 2, 40, 3.0, sched=0.5, gpu=4.0, emit=0.5)
+    stats.record("decode", 4, 4, None, sched=0.25, gpu=1.0, emit=0.25)
+    assert stats.lines == []
+    stats.record("decode", 2, 2, 0.5, sched=0.25, gpu=1.5, emit=0.25)
+    assert len(stats.lines) == 1 and stats.flush() is None, "the third step closed the window"
+    line, numbers = stats.lines[0], stats.summaries[0]
+    assert line.startswith("step stats steps=3 | decode n=2 rows=3.0 tok=3 ms/step[sched=0.25 gpu=1.25 emit=0.25 (kernel=0.50 host=1.00)]")
+    assert "prefill n=1 rows=2.0 tok=40 ms/step[sched=0.50 gpu=4.00 emit=0.50 (kernel=3.00 host=1.00)] share=59%" in line
+    assert line.endswith("wall sched=12% gpu=76% emit=12%")
+    assert numbers["kinds"]["decode"]["n"] == 2 and abs(numbers["wall"]["gpu"] - 6.5 / 8.5) < 1e-9
+    with pytest.raises(ValueError):
+        StepStats(0)
+    engine, cfg, _ = cpu_engine("A", num_blocks=32, max_seqs=4, step_stats=4)
+    engine.generate([helpers.random_ids(cfg["vocab_size"], n, n) for n in (5, 9)], max_new_tokens=6)
+    assert engine.stats.lines and "decode n=" in " ".join(engine.stats.lines)
+    assert sum(s["steps"] for s in engine.stats.summaries) == engine.steps

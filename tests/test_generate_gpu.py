@@ -16,7 +16,7 @@ def folder_for(name, tmp_path_factory, dtype="bfloat16"):
 
     cfg, page, _ = helpers.tiny(name)
     folder = str(tmp_path_factory.mktemp(f"gen{name}"))
-    write_random_model(folder, cfg, seed=helpers.TINY[name][2], std=helpers.TEST_STD, norm_noise=helpers.TINY[name][3], dtype=dtype)
+    write_random_model(folder, cfg, seed=helpers.TINY[name][2], std=helpers.STD[name], norm_noise=helpers.TINY[name][3], dtype=dtype)
     stored = ModelTensors(folder)
     return folder, cfg, page, {n: stored.tensor(n).float() for n in stored.keys()}
 
@@ -117,6 +117,119 @@ def test_preemption_and_chunked_prefill_on_gpu(tmp_path_factory):
     again = engine.generate(prompts, max_new_tokens=24, temperature=0.8, seed=1)
     assert [r.token_ids for r in sampled] == [r.token_ids for r in again]
     assert engine.cache.free_pages() == engine.cache.total_pages()
+
+
+def test_second_tiny_workload_against_the_sampling_oracle(tmp_path_factory):
+    """The workload of the second tiny configuration with an oracle: prompts of 1/5/17/40/63 tokens in
+    portions of 11 beside decoding requests, temperature 0.8 from seed 1, 24 tokens each, one forced
+    preemption; decode graphs and a step ahead on.  Every token must be the inverse-CDF pick of the plain
+    implementation's distribution at the request's own uniform number."""
+    from distie_b200.engine.engine import Engine
+
+    folder, cfg, page, weights = folder_for("B", tmp_path_factory)
+    engine = Engine.load(folder, dtype="float32", num_blocks=64, page_size=page, max_seqs=8, token_budget=24,
+                         prefill_chunk=helpers.TINY_B_CHUNK)
+    prompts, results = helpers.run_tiny_b_workload(engine, cfg)
+    assert results[4].preemptions == 1 and all(len(r.token_ids) == helpers.TINY_B_STEPS for r in results)
+    for index, (prompt, result) in enumerate(zip(prompts, results)):
+        helpers.check_sampled_tokens(prompt, result.token_ids, weights, cfg, helpers.TINY_B_TEMPERATURE, helpers.TINY_B_SEED + index)
+    assert engine.runner.graph_replays > 0
+    assert engine.cache.free_pages() == engine.cache.total_pages()
+
+
+def kv_rows(engine, seat: int, tokens: int) -> dict:
+    """The keys and values a request holds, gathered through its block table: {slot: (k, v) [tokens, heads, dim]}."""
+    cache = engine.cache
+    out = {}
+    for group, ids in zip(cache.groups, cache.pages_held(seat).values()):
+        pages = torch.tensor(ids, dtype=torch.long, device=group.slab.device)
+        for index, slot in enumerate(group.slots):
+            k, v = (group.slab[index, which].index_select(0, pages) for which in (0, 1))  # [pages, heads, page, dim]
+            out[slot] = tuple(t.permute(0, 2, 1, 3).reshape(-1, t.shape[1], t.shape[3])[:tokens].float().cpu() for t in (k, v))
+    return out
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", 1e-5), ("bfloat16", 2.0**-7)])
+@pytest.mark.parametrize("name", ["B", "D"])
+def test_two_slabs_hold_equal_keys_and_values(name, dtype, tol, tmp_path_factory):
+    """The same requests cut three ways (whole; the tail token by token through the captured decode step;
+    portions mixed with single tokens) leave the same keys and values in their pages, not only the same
+    logits (the reference's two-slab comparison, worker/tests/test_qwen2_batch.py:71-109).  bfloat16: a
+    key may differ by one rounding where the product that made it ran on another kernel."""
+    from distie_b200.engine.trace_replay import TraceSession
+
+    folder, cfg, page, _ = folder_for(name, tmp_path_factory)
+    requests = {f"r{i}": helpers.random_ids(cfg["vocab_size"], n, 20 + i) for i, n in enumerate([40, 167, 33, 150])}
+    slabs = []
+    for schedule in (helpers.schedule_whole, helpers.schedule_tail, helpers.schedule_mixed):
+        steps = [dict(step, end=[]) for step in schedule(requests)]  # nobody ends: the pages stay held
+        session = TraceSession.open(folder, dtype, 4 * 192, page_size=page)
+        helpers.run_schedule(session, steps)
+        slabs.append({rid: kv_rows(session.engine, session.live[rid][0], len(ids)) for rid, ids in requests.items()})
+    for other in slabs[1:]:
+        for rid in requests:
+            for slot, pair in slabs[0][rid].items():
+                for a, b in zip(pair, other[rid][slot]):
+                    assert float(a.abs().max()) > 0
+                    worst = float(((a - b).abs() / a.abs().clamp_min(float(a.abs().max()) * 2.0**-6)).max())
+                    assert worst <= tol, (rid, slot, worst)
+
+
+def test_a_bad_request_does_not_switch_the_graphs_off(tmp_path_factory):
+    """A device-side check that fails on one request's data (here: its block table names a page outside the
+    pool) raises to the caller; it is not mistaken for a failure of the captured step, so later requests
+    still replay graphs."""
+    from distie_b200.engine.engine import Engine
+    from distie_b200.kernels.library import KernelError
+
+    folder, cfg, page, weights = folder_for("A", tmp_path_factory)
+    engine = Engine.load(folder, dtype="float32", num_blocks=32, page_size=page, max_seqs=4, decode_ahead=False)
+    prompt = helpers.random_ids(cfg["vocab_size"], 9, 3)
+    want = plain.greedy_generate(prompt, weights, cfg, 6)
+    assert engine.generate(prompt, max_new_tokens=6)[0].token_ids == want
+    replays = engine.runner.graph_replays
+    assert replays > 0 and engine.runner.use_graphs
+    group = engine.cache.groups[0]
+    spoiled = []
+
+    def spoil(request_id, token, finished):
+        if not spoiled:  # after the first token: the request's table now names a page the pool does not have
+            seat = engine.scheduler.running()[0].seat
+            group.device_table[seat, 0] = group.num_pages + 7
+            spoiled.append(seat)
+
+    with pytest.raises(KernelError, match="block table"):
+        engine.generate(prompt, max_new_tokens=6, on_token=spoil)
+    assert engine.runner.use_graphs, "a bad request must not cost every later request its graphs"
+    assert engine.cache.free_pages() == engine.cache.total_pages() and not engine.has_work()
+    group.device_table[spoiled[0]] = -1
+    assert engine.generate(prompt, max_new_tokens=6)[0].token_ids == want
+    assert engine.runner.graph_replays > replays
+
+
+def test_float32_checkpoint_in_the_bfloat16_engine_runs_the_bfloat16_kernels(tmp_path_factory):
+    """A checkpoint stored wholly in float32 is cast by the bfloat16 engine, as the reference casts on load
+    (worker/src/inference/torch_engine.py:135-141): the tensor-core kernels run and the logits stay within
+    the bfloat16 budget.  With ``float32_weights="keep"`` the matrices stay wide and none of them runs."""
+    from distie_b200.engine.engine import Engine
+
+    folder, cfg, page, weights = folder_for("D", tmp_path_factory, dtype="float32")
+    ids = helpers.random_ids(cfg["vocab_size"], 200, 5)
+    rounded = helpers.bf16_rounded(weights)
+    want = {"x": plain.forward_logits(ids, rounded, cfg)}
+    budget = helpers.Bf16Budget({"x": ids}, rounded, cfg, want)
+    engine = Engine.load(folder, dtype="bfloat16", num_blocks=16, page_size=page, max_seqs=2)
+    got = {"x": engine.trace(ids[:160], 41, ids[160:] + [0]).logits[:40]}
+    budget_want = {"x": want["x"][159:199]}
+    worst, rms, top1 = helpers.pooled_stats(got, budget_want)
+    assert rms <= 2 * budget.rms_error and top1 >= budget.top1 - 0.05, (worst, rms, top1, budget.rms_error)
+    ran = {name for name, count in engine.model.kernels.kernel_counts.items() if count}
+    assert {"gemm_tcgen05", "gemm_tcgen05_skinny", "attention_prefill_tcgen05", "attention_decode_mma"} <= ran, sorted(ran)
+    del engine
+    wide = Engine.load(folder, dtype="bfloat16", num_blocks=16, page_size=page, max_seqs=2, float32_weights="keep")
+    wide.trace(ids[:160], 2, ids[160:162])
+    ran = {name for name, count in wide.model.kernels.kernel_counts.items() if count}
+    assert not ({"gemm_tcgen05", "gemm_tcgen05_skinny"} & ran), sorted(ran)
 
 
 def test_missing_extension_fails_loudly(monkeypatch):

@@ -460,3 +460,26 @@ def test_sampling(kernel_sets, vocab):
     ks.sample(small, torch.ones(4000, device="cuda"), us, outs)
     freq = torch.bincount(outs.long(), minlength=4).float() / 4000
     assert torch.allclose(freq.cpu(), torch.softmax(small[0].cpu(), -1), atol=0.03)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("head_dim,tokens", [(32, 1), (128, 1), (48, 3), (128, 3)])
+def test_position_beyond_the_block_table_sets_the_error_word(kernel_sets, dtype, head_dim, tokens):
+    """A token whose position lies past the last column of its block table reads nothing outside the
+    table: its keys count as missing pages and the error word says so (every attention kernel checks the
+    column before it reads the table)."""
+    from distie_b200.kernels.library import KernelError
+
+    ks = kernel_sets[dtype]
+    page, heads, kv_heads = 16, 4, 2
+    kv = filled_cache_for(dtype, kv_heads, head_dim, page, [40, 40])
+    width = kv.block_table.shape[1]
+    pasts = [40 - tokens, width * page + 5]
+    step = step_of([tokens, tokens], pasts, [0, 1])
+    qkv = torch.randn(step.num_tokens, (heads + 2 * kv_heads) * head_dim, device="cuda").to(dtype)
+    out = torch.zeros(step.num_tokens, heads * head_dim, dtype=dtype, device="cuda")
+    ks.attention(qkv, out, step, kv, heads, kv_heads, head_dim, None, head_dim**-0.5)
+    with pytest.raises(KernelError, match="block table"):
+        ks.check_errors()
+    ks.check_errors()  # the word was cleared
+    assert torch.isfinite(out.float()).all()

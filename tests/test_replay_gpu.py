@@ -21,12 +21,22 @@ MODES = {
     "whole": helpers.schedule_whole,
     "tail": helpers.schedule_tail,
     "portions": helpers.schedule_portions,
-    "mixed": helpers.schedule_mixed,
+    # two requests are ended early and fed again from position 0, as a preemption does
+    "mixed": lambda requests: helpers.schedule_mixed(requests, refeed=2),
 }
 LENGTHS = [40, 67, 33, 300, 50, 36, 129, 64]
+# What a bfloat16 engine with head sizes 64 or 128 must have launched in each mode: prompts of 128 tokens
+# and more take the tensor-core product, shorter steps the weight-streaming one; portions take the
+# tensor-core prefill attention, steps of single tokens the tensor-core decode attention.
+SERVING_KERNELS = {
+    "whole": {"attention_prefill_tcgen05", "gemm_tcgen05", "gemm_tcgen05_skinny"},
+    "tail": {"attention_prefill_tcgen05", "attention_decode_mma", "gemm_tcgen05", "gemm_tcgen05_skinny"},
+    "portions": {"attention_prefill_tcgen05", "gemm_tcgen05_skinny"},
+    "mixed": {"attention_prefill_tcgen05", "attention_decode_mma", "gemm_tcgen05_skinny"},
+}
 
 
-@pytest.fixture(scope="module", params=["A", "B"])
+@pytest.fixture(scope="module", params=["A", "B", "C", "D"])
 def model(request, tmp_path_factory):
     """A model folder of the tiny configuration, written by the random-weights mode, and its plain logits."""
     from distie_b200.weights import ModelTensors, write_random_model
@@ -34,13 +44,14 @@ def model(request, tmp_path_factory):
     cfg, page, _ = helpers.tiny(request.param)
     noise = helpers.TINY[request.param][3]
     folder = str(tmp_path_factory.mktemp(f"tiny{request.param}"))
-    write_random_model(folder, cfg, seed=helpers.TINY[request.param][2], std=helpers.TEST_STD, norm_noise=noise, dtype="bfloat16")
+    write_random_model(folder, cfg, seed=helpers.TINY[request.param][2], std=helpers.STD[request.param], norm_noise=noise, dtype="bfloat16")
     stored = ModelTensors(folder)
     weights = {name: stored.tensor(name).float() for name in stored.keys()}
     requests = {f"r{i}": helpers.random_ids(cfg["vocab_size"], n, 10 + i) for i, n in enumerate(LENGTHS)}
     expected = {rid: plain.forward_logits(ids, weights, cfg) for rid, ids in requests.items()}
     budget = helpers.Bf16Budget(requests, weights, cfg, expected)
-    return {"folder": folder, "cfg": cfg, "page": page, "requests": requests, "expected": expected, "budget": budget}
+    return {"folder": folder, "cfg": cfg, "page": page, "requests": requests, "expected": expected, "budget": budget,
+            "name": request.param}
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -51,18 +62,46 @@ def test_replay_matches_plain(model, mode, dtype):
     steps = MODES[mode](model["requests"])
     session = TraceSession.open(model["folder"], dtype, helpers.peak_tokens(steps), page_size=model["page"])
     got = helpers.collect(steps, helpers.run_schedule(session, steps))
+    expected = helpers.expected_for(got, model["expected"])
+    if mode == "mixed":
+        assert any("#" in key for key in got), "the schedule was meant to give a request up and feed it again"
     if dtype == "float32":
-        error, rid, at = helpers.worst_error(got, model["expected"])
+        error, rid, at = helpers.worst_error(got, expected)
         if error > helpers.FP32_TOL:
-            first = helpers.first_bad_position(got[rid], model["expected"][rid], helpers.FP32_TOL)
+            first = helpers.first_bad_position(got[rid], expected[rid], helpers.FP32_TOL)
             pytest.fail(
-                f"{mode}: request {rid} (length {len(model['requests'][rid])}) first wrong at position {first}, "
+                f"{mode}: request {rid} (length {len(model['requests'][rid.split('#')[0]])}) first wrong at position {first}, "
                 f"worst {error:.2e} of the logit scale at {at}"
             )
     else:
-        model["budget"].check(got, model["expected"], mode)
+        model["budget"].check(got, expected, mode)
+    runner = session.engine.runner
+    if mode == "tail":  # the last 32 tokens one by one are steps of single tokens: the captured decode step ran them
+        assert runner.graph_replays > 0, "steps of single tokens were meant to replay the captured decode step"
+    if dtype == "bfloat16" and model["name"] in "CD":
+        # The kernels serving runs on are the ones that were held to the oracle here.
+        ran = {name for name, count in runner.kernels.kernel_counts.items() if count}
+        assert SERVING_KERNELS[mode] <= ran, f"{mode}: expected {sorted(SERVING_KERNELS[mode] - ran)} to have run; ran {sorted(ran)}"
     cache = session.engine.cache
     assert cache.free_pages() == cache.total_pages() and cache.free_seats == cache.max_seats
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_tail_without_graphs_matches_too(model, dtype):
+    """The same steps of single tokens run eagerly: both forms of the decode step are held to the oracle."""
+    from distie_b200.engine.trace_replay import TraceSession
+
+    if model["name"] in "AB":
+        pytest.skip("covered at the head sizes the serving kernels take")
+    steps = helpers.schedule_tail(model["requests"])
+    session = TraceSession.open(model["folder"], dtype, helpers.peak_tokens(steps), page_size=model["page"], decode_graphs=False)
+    got = helpers.collect(steps, helpers.run_schedule(session, steps))
+    assert session.engine.runner.graph_replays == 0
+    if dtype == "float32":
+        error, rid, at = helpers.worst_error(got, model["expected"])
+        assert error <= helpers.FP32_TOL, f"request {rid} position {at} off by {error:.2e} of the logit scale"
+    else:
+        model["budget"].check(got, model["expected"], "tail, eager")
 
 
 def test_trace_run_program(model, tmp_path):
@@ -80,7 +119,7 @@ def test_trace_run_program(model, tmp_path):
     vocab = model["cfg"]["vocab_size"]
     outputs = {s["step"]: np.fromfile(out_dir / f"{s['step']}.f32", dtype="<f4").reshape(-1, vocab) for s in steps}
     got = helpers.collect(steps, outputs)
-    error, rid, at = helpers.worst_error(got, model["expected"])
+    error, rid, at = helpers.worst_error(got, helpers.expected_for(got, model["expected"]))
     assert error <= helpers.FP32_TOL, f"request {rid} position {at} off by {error:.2e}"
 
 

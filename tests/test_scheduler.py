@@ -132,7 +132,7 @@ def test_running_out_of_pages_preempts_the_newest_and_recomputes_it():
     assert [i.seq.request_id for i in plan.items] == ["a"]
     assert b.state is SeqState.WAITING and b.preemptions == 1 and b.num_cached == 0 and b.seat is None
     assert len(b.output_ids) == 2, "what it generated is kept and never emitted twice"
-    assert sched._waiting[0] is b, "a preempted request goes to the front of the queue"
+    assert sched.waiting()[0] is b, "a preempted request goes to the front of the queue"
     sched.complete(plan, [7])
     while a.state is not SeqState.FINISHED:
         run_step(sched)
