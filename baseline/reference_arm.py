@@ -355,7 +355,7 @@ def run(args, shape: dict, layers: int, peaks: dict, peaks_kind: str, constants:
             "tied": shape["tie_word_embeddings"], "global_batch": args.batch, "prompt_len": prompt_len,
             "seq_len": context, "page_size": ref.kv.page_size, "parallelism": "none (1 GPU)",
             "decode": "CUDA graph per batch bucket" if head["graphs"] else "eager",
-            "l2": "inputs larger than L2 (3 GB of weights per step)", "peaks": peaks_kind,
+            "l2": "inputs larger than L2 (the weights alone, read once per step)", "peaks": peaks_kind,
         },
         "e2e": {k: (round(v, 1) if isinstance(v, float) else v) for k, v in e2e.items()} if e2e else None,
         "points": points,

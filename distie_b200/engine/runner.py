@@ -3,7 +3,8 @@
 ``ModelRunner.step(entries)`` runs only the tokens it is given, as one batch,
 against what earlier steps left in the cache, and returns float32 logits
 ``[wanted, vocab]`` on the device.  Trace replay and generation both go through
-it; generation adds sampling on the device (``run_plan``).
+it; generation adds sampling on the device (``run_plan``).  A step in which every
+entry is a single token replays the captured decode step of its bucket in both.
 
 Steps in which every request decodes one token are replayed from CUDA graphs, one
 per batch-size bucket, like the reference's (worker/src/inference/qwen2/
@@ -45,7 +46,6 @@ class _Bucket:
         self.ints = torch.zeros(5 * size, dtype=torch.int32, device=device)
         self.floats = torch.zeros(2 * size, dtype=torch.float32, device=device)  # temperatures | uniforms
         self.tokens = torch.zeros(size, dtype=torch.int32, device=device)
-        self.advance = torch.zeros(size, dtype=torch.int32, device=device)  # added to the positions after every replay
         self.logits: torch.Tensor | None = None
         self.graph: torch.cuda.CUDAGraph | None = None
         self.kernels_per_replay = 0  # own kernels inside the captured step
@@ -278,54 +278,6 @@ class ModelRunner:
             self.kernels.check_errors()  # raises with the code's text and clears the word
         return [token for token, wanted in zip(host, samples) if wanted]
 
-    @torch.inference_mode()
-    def decode_burst(self, items, steps: int) -> torch.Tensor:
-        """``steps`` greedy decode steps back to back on the device, each feeding the next.
-
-        The sampled tokens of a step become the next step's inputs without a trip to the
-        host; the caller has grown every request's pages for ``past_len + steps`` tokens
-        beforehand and advances its own bookkeeping afterwards.  Returns the tokens
-        ``[steps, rows]`` (int32, on the device).  Used to time the step itself.
-        """
-        rows = len(items)
-        size = self.bucket_for(rows)
-        bucket = self._buckets.get(size)
-        if bucket is None:
-            bucket = _Bucket(size, self.device)
-            self._buckets[size] = bucket
-        if any(item.seq.temperature > 0 or len(item.token_ids) != 1 for item in items):
-            raise ValueError("a burst decodes greedily, one token per request and step")
-        bucket.before_write()
-        ints = bucket.host_ints.numpy()
-        ints[:size] = 0
-        ints[size : 2 * size] = 0
-        ints[2 * size : 3 * size] = np.arange(size, dtype=np.int32)
-        ints[3 * size : 4 * size] = self.cache.pad_seat
-        ints[4 * size :] = np.arange(size, dtype=np.int32)
-        bucket.host_floats.zero_()
-        advance = torch.zeros(size, dtype=torch.int32)
-        for row, item in enumerate(items):
-            ints[row] = item.token_ids[0]
-            ints[size + row] = item.past_len
-            ints[3 * size + row] = item.seq.seat
-            advance[row] = 1
-        self.cache.upload_tables([item.seq.seat for item in items])
-        bucket.upload()
-        if bucket.graph is None:
-            self._capture(bucket)  # runs the first step once more than asked: same tokens, same slots
-            bucket.upload()        # (and fed its tokens back: start again from the given ones)
-        out = torch.empty((steps, size), dtype=torch.int32, device=self.device)
-        bucket.advance.copy_(advance, non_blocking=False)
-        try:
-            for k in range(steps):
-                bucket.graph.replay()  # feeds its tokens back as the next ids and moves the positions on
-                out[k].copy_(bucket.tokens)
-        finally:
-            bucket.advance.zero_()
-        self.graph_replays += steps
-        self.steps += steps
-        return out[:, :rows]
-
     def _forward_bucket(self, bucket: _Bucket) -> None:
         layout = bucket.layout
         layout.max_kv_len = self.cache.max_tokens_per_request  # a fixed bound: the graph must not depend on lengths
@@ -335,7 +287,6 @@ class ModelRunner:
         self.sampler.pick(bucket.logits, bucket.floats[:size], bucket.floats[size:], bucket.tokens)
         # The sampled tokens are also the next step's token ids, should it be launched before they reach the host.
         bucket.ints[:size].copy_(bucket.tokens)
-        bucket.ints[size : 2 * size].add_(bucket.advance)  # zeros, except while a burst runs steps back to back
 
     def _capture(self, bucket: _Bucket) -> None:
         # Warm up on a side stream (library workspaces, lazy kernel loading), then capture.
