@@ -200,8 +200,9 @@ def fill_requests(engine, batch: int, prompt_len: int, total_new: int, tag: str)
     from distie_b200.engine.scheduler import Sequence
 
     vocab = engine.model.vocab_size
+    # Requests admitted first decode while the later ones are still being prefilled: room for those tokens too.
     for b in range(batch):
-        engine.scheduler.submit(Sequence(f"{tag}-{b}", random_prompt(vocab, prompt_len, 100 + b), total_new + 8))
+        engine.scheduler.submit(Sequence(f"{tag}-{b}", random_prompt(vocab, prompt_len, 100 + b), total_new + 8 + 2 * batch))
     while True:
         plan = engine.scheduler.schedule()
         if plan.kind == "decode" and len(plan.items) == batch and engine.scheduler.num_waiting == 0:
@@ -457,7 +458,7 @@ def main() -> int:
         pages = 2 * -(-(args.past + PREFILL_TOKENS) // PAGE)
         engine = build_engine(shape, layers, 8, pages, max(CONTEXT, args.past + PREFILL_TOKENS), dtype)
     elif args.shape == "1.5b":
-        pages = 64 * -(-(prompt_len + new_tokens + 1) // PAGE) + 2 * (PREFILL_TOKENS // PAGE)
+        pages = 64 * -(-(prompt_len + new_tokens + 2 * 64 + 1) // PAGE) + 2 * (PREFILL_TOKENS // PAGE)
         engine = build_engine(shape, layers, 64, pages, context, dtype)
     else:
         engine = build_engine(shape, layers, 64, None, context, dtype, gpu_mem_fraction=0.85)

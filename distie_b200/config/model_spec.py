@@ -68,6 +68,10 @@ class ModelSpec:
     max_positions: int | None = None
     eos_token_id: int | None = None
     init: Mapping[str, float] = field(default_factory=dict)  # hints for random weights
+    # Constants some architectures put around the stack of layers; all off (None) for the plain decoder.
+    embedding_scale: float | None = None  # the embedded tokens are multiplied by it
+    logit_scale: float | None = None      # the logits are multiplied by it
+    logit_softcap: float | None = None    # then logits = cap * tanh(logits / cap)
 
     def __post_init__(self) -> None:
         if not self.layers or not self.order:

@@ -191,15 +191,10 @@ inline cudaError_t launch_dependent_cluster(int family, dim3 cluster, void (*ker
   config.blockDim = block;
   config.dynamicSmemBytes = shared;
   config.stream = stream;
-  // DISTIE_DEPENDENT_LAUNCH=0 turns the early start off (every kernel then waits for the one before it).
-  static const int mask = [] {
-    const char* flag = getenv("DISTIE_DEPENDENT_LAUNCH");
-    return flag == nullptr ? 0xff : atoi(flag);
-  }();
-  const bool enabled = (mask & family) != 0;
+  (void)family;  // names the kind of kernel at the call site; every kind starts early
   cudaLaunchAttribute attribute[2];
   attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attribute[0].val.programmaticStreamSerializationAllowed = enabled ? 1 : 0;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
   config.attrs = attribute;
   config.numAttrs = 1;
   if (cluster.x > 0) {

@@ -253,7 +253,7 @@ template <typename T>
 __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
                                      const int* __restrict__ token_seq, const int* __restrict__ seq_seat,
                                      const int* __restrict__ block_table, int table_width,
-                                     const float* __restrict__ inv_freq, T* __restrict__ k_cache,
+                                     const float* __restrict__ inv_freq, float trig_factor, T* __restrict__ k_cache,
                                      T* __restrict__ v_cache, int row_stride, int num_heads, int num_kv_heads,
                                      int head_dim, int rotary_dim, int interleaved, int page_size, int num_pages,
                                      int write_cache, int* __restrict__ error) {
@@ -265,8 +265,8 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict_
     for (int j = threadIdx.x; j < half; j += blockDim.x) {
       float s, c;
       sincosf((float)pos * inv_freq[j], &s, &c);
-      trig[j] = c;
-      trig[half + j] = s;
+      trig[j] = c * trig_factor;  // the factor scales cos and sin alike (1 for the plain rotation)
+      trig[half + j] = s * trig_factor;
     }
   }
   __syncthreads();
@@ -341,7 +341,7 @@ __global__ void rope_kv_write_vec_kernel(const QT* in, int splits, size_t split_
                                          const float* __restrict__ bias, T* q_out, int q_out_stride,
                                          const int* __restrict__ positions, const int* __restrict__ token_seq,
                                          const int* __restrict__ seq_seat, const int* __restrict__ block_table,
-                                         int table_width, const float* __restrict__ inv_freq, T* __restrict__ k_cache,
+                                         int table_width, const float* __restrict__ inv_freq, float trig_factor, T* __restrict__ k_cache,
                                          T* __restrict__ v_cache, int num_heads, int num_kv_heads, int head_dim,
                                          int page_size, int num_pages, int write_cache, int* __restrict__ error) {
   extern __shared__ float trig[];  // cos[head_dim/2], sin[head_dim/2]
@@ -353,7 +353,11 @@ __global__ void rope_kv_write_vec_kernel(const QT* in, int splits, size_t split_
   const int half = head_dim >> 1;
   for (int j = threadIdx.x; j < half; j += blockDim.x) {
     float s = 0.f, c = 1.f;
-    if (inv_freq) sincosf((float)pos * inv_freq[j], &s, &c);
+    if (inv_freq) {
+      sincosf((float)pos * inv_freq[j], &s, &c);
+      c *= trig_factor;  // the factor scales cos and sin alike (1 for the plain rotation)
+      s *= trig_factor;
+    }
     trig[j] = c;
     trig[half + j] = s;
   }
@@ -530,7 +534,7 @@ extern "C" int distie_add_rmsnorm(const void* delta, float* residual, const floa
 }
 
 extern "C" int distie_rope_kv_write(void* qkv, const int* positions, const int* token_seq, const int* seq_seat,
-                                    const int* block_table, int table_width, const float* inv_freq, void* k_cache,
+                                    const int* block_table, int table_width, const float* inv_freq, float trig_factor, void* k_cache,
                                     void* v_cache, int tokens, int row_stride, int num_heads, int num_kv_heads,
                                     int head_dim, int rotary_dim, int interleaved, int page_size, int num_pages,
                                     int write_cache, int dtype, int* error, cudaStream_t stream) {
@@ -548,12 +552,12 @@ extern "C" int distie_rope_kv_write(void* qkv, const int* positions, const int* 
     if (dtype == DISTIE_BF16)
       rope_kv_write_vec_kernel<<<tokens, threads, bytes, stream>>>(
           (const __nv_bfloat16*)qkv, 1, (size_t)0, row_stride, (const float*)nullptr, (__nv_bfloat16*)qkv, row_stride,
-          positions, token_seq, seq_seat, block_table, table_width, inv_freq, (__nv_bfloat16*)k_cache,
+          positions, token_seq, seq_seat, block_table, table_width, inv_freq, trig_factor, (__nv_bfloat16*)k_cache,
           (__nv_bfloat16*)v_cache, num_heads, num_kv_heads, head_dim, page_size, num_pages, write_cache, error);
     else
       rope_kv_write_vec_kernel<<<tokens, threads, bytes, stream>>>(
           (const float*)qkv, 1, (size_t)0, row_stride, (const float*)nullptr, (float*)qkv, row_stride, positions,
-          token_seq, seq_seat, block_table, table_width, inv_freq, (float*)k_cache, (float*)v_cache, num_heads,
+          token_seq, seq_seat, block_table, table_width, inv_freq, trig_factor, (float*)k_cache, (float*)v_cache, num_heads,
           num_kv_heads, head_dim, page_size, num_pages, write_cache, error);
     DISTIE_LAUNCH_CHECK();
     return 0;
@@ -562,12 +566,12 @@ extern "C" int distie_rope_kv_write(void* qkv, const int* positions, const int* 
   const size_t shared = (size_t)rotary_dim * sizeof(float);
   if (dtype == DISTIE_BF16)
     rope_kv_write_kernel<<<tokens, threads, shared, stream>>>(
-        (__nv_bfloat16*)qkv, positions, token_seq, seq_seat, block_table, table_width, inv_freq,
+        (__nv_bfloat16*)qkv, positions, token_seq, seq_seat, block_table, table_width, inv_freq, trig_factor,
         (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, row_stride, num_heads, num_kv_heads, head_dim, rotary_dim,
         interleaved, page_size, num_pages, write_cache, error);
   else if (dtype == DISTIE_F32)
     rope_kv_write_kernel<<<tokens, threads, shared, stream>>>(
-        (float*)qkv, positions, token_seq, seq_seat, block_table, table_width, inv_freq, (float*)k_cache,
+        (float*)qkv, positions, token_seq, seq_seat, block_table, table_width, inv_freq, trig_factor, (float*)k_cache,
         (float*)v_cache, row_stride, num_heads, num_kv_heads, head_dim, rotary_dim, interleaved, page_size, num_pages,
         write_cache, error);
   else
@@ -600,7 +604,7 @@ extern "C" int distie_add_rmsnorm_split(const float* partials, int splits, long 
 extern "C" int distie_rope_kv_write_split(const float* partials, int splits, long long split_stride, int row_stride,
                                           const float* bias, void* q_out, int q_out_stride, const int* positions,
                                           const int* token_seq, const int* seq_seat, const int* block_table,
-                                          int table_width, const float* inv_freq, void* k_cache, void* v_cache,
+                                          int table_width, const float* inv_freq, float trig_factor, void* k_cache, void* v_cache,
                                           int tokens, int num_heads, int num_kv_heads, int head_dim, int rotary_dim,
                                           int interleaved, int page_size, int num_pages, int write_cache, int dtype,
                                           int* error, cudaStream_t stream) {
@@ -621,13 +625,13 @@ extern "C" int distie_rope_kv_write_split(const float* partials, int splits, lon
   if (dtype == DISTIE_BF16)
     err = launch_dependent_family(4, rope_kv_write_vec_kernel<__nv_bfloat16, float>, dim3(tokens), dim3(threads), bytes, stream,
                            partials, splits, (size_t)split_stride, row_stride, bias, (__nv_bfloat16*)q_out, q_out_stride,
-                           positions, token_seq, seq_seat, block_table, table_width, inv_freq, (__nv_bfloat16*)k_cache,
+                           positions, token_seq, seq_seat, block_table, table_width, inv_freq, trig_factor, (__nv_bfloat16*)k_cache,
                            (__nv_bfloat16*)v_cache, num_heads, num_kv_heads, head_dim, page_size, num_pages, write_cache,
                            error);
   else
     err = launch_dependent_family(4, rope_kv_write_vec_kernel<float, float>, dim3(tokens), dim3(threads), bytes, stream, partials,
                            splits, (size_t)split_stride, row_stride, bias, (float*)q_out, q_out_stride, positions,
-                           token_seq, seq_seat, block_table, table_width, inv_freq, (float*)k_cache, (float*)v_cache,
+                           token_seq, seq_seat, block_table, table_width, inv_freq, trig_factor, (float*)k_cache, (float*)v_cache,
                            num_heads, num_kv_heads, head_dim, page_size, num_pages, write_cache, error);
   return err == cudaSuccess ? 0 : (int)err;
 }

@@ -692,8 +692,7 @@ extern "C" int distie_gemm_tcgen05(const void* x, int ldx, const void* w, void* 
   CUtensorMap map_a, map_b;
   int status = make_map(&map_a, x, M, K, ldx, kGemmBM);
   if (status != 0) return status;
-  static const bool pairs_enabled = [] { const char* v = getenv("DISTIE_GEMM_PAIRS"); return v == nullptr || atoi(v) != 0; }();
-  if (M >= 2 * kGemmBM && sm_count >= 2 && pairs_enabled) {
+  if (M >= 2 * kGemmBM && sm_count >= 2) {
     // Pairs of CTAs on 256-row tiles; each CTA stages half of the tile's rows of W.
     if (epi == GEMM_EPI_SWIGLU) {
       if ((status = make_map(&map_b, w, N, K, K, 128)) != 0) return status;

@@ -32,6 +32,8 @@ class DecodeBurst:
             raise ValueError("a burst decodes greedily, one token per request and step")
         if not runner.use_graphs:
             raise RuntimeError("a burst replays captured decode steps: the runner has its graphs switched off")
+        if runner.cache.states:
+            raise RuntimeError("a burst runs its first step twice, which per-request state does not survive")
         rows = [(item.token_ids[0], item.past_len, item.seq.seat, 0.0, 0.0) for item in items]
         # Stage the rows and make sure the bucket's step is captured (this runs the first step once more than
         # asked: same tokens, same slots), then stage again, because the step fed its tokens back as ids.

@@ -294,7 +294,12 @@ class ModelRunner:
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
             ids = bucket.ints[: bucket.size].clone()
+            # The warm-up runs the step for real.  Keys and values it writes are the ones the replay writes
+            # again; per-request state is not idempotent, so it is put back as it was.
+            states = {slot: state.clone() for slot, state in self.cache.states.items()}
             self._forward_bucket(bucket)
+            for slot, state in states.items():
+                self.cache.states[slot].copy_(state)
             bucket.ints[: bucket.size].copy_(ids)  # the warm-up fed its tokens back; the replay starts from the step's own ids
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize(self.device)

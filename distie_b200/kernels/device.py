@@ -15,8 +15,6 @@ There is no CPU path here and no fallback: a missing library raises.
 
 from __future__ import annotations
 
-import os
-
 import torch
 
 from . import library
@@ -229,6 +227,7 @@ class DeviceKernels(KernelSet):
             step.positions.data_ptr(), step.token_seq.data_ptr(), step.seq_seat.data_ptr(),
             table.data_ptr(), table.shape[-1] if write else 1,
             rotary.inv_freq.data_ptr() if rotary is not None else None,
+            float(rotary.factor) if rotary is not None else 1.0,
             kv.k.data_ptr() if write else None, kv.v.data_ptr() if write else None,
         ]
         sizes = [
@@ -339,8 +338,6 @@ class DeviceKernels(KernelSet):
 
     def _attention_tcgen05(self, qkv, out, step, kv, num_heads, num_kv_heads, head_dim, window, scale) -> bool:
         """Prompt portions on the tcgen05 kernel; False when it refuses the page size or an alignment."""
-        if os.environ.get("DISTIE_PREFILL_ATTENTION") == "mma":
-            return False
         code = function("distie_attention_prefill_tcgen05")(
             qkv.data_ptr(), qkv.stride(0), out.data_ptr(), out.stride(0), step.q_tiles.data_ptr(), step.num_q_tiles,
             step.positions.data_ptr(), step.token_seq.data_ptr(), step.seq_seat.data_ptr(),

@@ -57,6 +57,7 @@ class RotaryTable:
     inv_freq: torch.Tensor  # [rotary_dim / 2] float32
     rotary_dim: int
     interleaved: bool = False
+    factor: float = 1.0  # cos and sin are multiplied by it (the attention factor of scaled rotary encodings)
 
 
 class KernelSet(ABC):

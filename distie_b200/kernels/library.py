@@ -22,11 +22,11 @@ L = c_longlong
 _SIGNATURES: dict[str, tuple[str, list]] = {
     "distie_embed": ("base", [P, P, P, I, I, I, I, P, P]),
     "distie_add_rmsnorm": ("base", [P, P, P, P, P, I, I, F, I, P]),
-    "distie_rope_kv_write": ("base", [P, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, I, I, I, P, P]),
+    "distie_rope_kv_write": ("base", [P, P, P, P, P, I, P, F, P, P, I, I, I, I, I, I, I, I, I, I, I, P, P]),
     "distie_swiglu": ("base", [P, P, I, I, I, P]),
     "distie_add_rmsnorm_split": ("base", [P, I, L, P, P, P, P, I, I, F, I, P]),
     "distie_rope_kv_write_split": (
-        "base", [P, I, L, I, P, P, I, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, I, I, P, P]
+        "base", [P, I, L, I, P, P, I, P, P, P, P, I, P, F, P, P, I, I, I, I, I, I, I, I, I, I, P, P]
     ),
     "distie_bias_cast": ("base", [P, P, P, L, I, I, P]),
     "distie_attention_generic": ("base", [P, I, P, I, P, P, P, P, I, P, P, I, I, I, I, I, I, I, F, I, P, P]),

@@ -4,6 +4,8 @@ Nothing here names an architecture.  ``forward`` runs only the tokens of the ste
 it is given, against the cache slots the step's :class:`CacheView` hands out, and
 returns float32 logits at the wanted rows (embedding -> layers -> row select ->
 final norm -> head, the order of worker/src/inference/qwen2/model.py:369-380).
+A spec may put constants around the stack (a scale on the embedded tokens, a scale
+and a soft cap on the logits); the architecture built here sets none of them.
 """
 
 from __future__ import annotations
@@ -93,6 +95,8 @@ class DecoderModel:
         k = self.kernels
         residual = torch.empty((step.num_tokens, self.spec.hidden_size), dtype=torch.float32, device=k.device)
         k.embed(step, self.embedding, residual)
+        if self.spec.embedding_scale is not None:
+            residual.mul_(float(self.spec.embedding_scale))
         stream = ResidualStream(residual)
         for call in self.spec.order:
             run = LayerRun(
@@ -107,4 +111,10 @@ class DecoderModel:
             return None
         x = torch.empty((logit_rows.numel(), self.spec.hidden_size), dtype=k.dtype, device=k.device)
         self.final_norm.apply(stream.pending, residual, x, logit_rows)
-        return self.head(x, out_dtype=torch.float32)
+        logits = self.head(x, out_dtype=torch.float32)
+        if self.spec.logit_scale is not None:
+            logits.mul_(float(self.spec.logit_scale))
+        if self.spec.logit_softcap is not None:
+            cap = float(self.spec.logit_softcap)
+            logits = torch.tanh(logits / cap).mul_(cap)
+        return logits

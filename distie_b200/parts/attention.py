@@ -103,21 +103,21 @@ class GqaAttention:
         if run.kv is None:
             raise RuntimeError("attention needs a cache slot")
         k = self.kernels
-        # The projection's float32 slices go straight into the kernel that adds the bias, rotates q
-        # and k and stores k and v in their pages; q comes back in a buffer of its own.
-        slices = k.linear_split(x, self.qkv.weight)
         q = torch.empty((x.shape[0], self.num_heads * self.head_dim), dtype=x.dtype, device=x.device)
-        k.rope_kv_write(
-            slices,
-            run.step,
-            run.kv if run.writes_cache else None,
-            self.position.rotary_table(),
-            self.num_heads,
-            self.num_kv_heads,
-            self.head_dim,
-            bias=self.qkv.bias,
-            q_out=q,
-        )
+        kv = run.kv if run.writes_cache else None
+        table = self.position.rotary_table()
+        if table is None and hasattr(self.position, "apply"):
+            # An encoding of its own: the projection is finished here, the encoding changes q and k in
+            # place, and the fused kernel only stores k and v and copies q out.
+            qkv = k.linear(x, self.qkv.weight, self.qkv.bias)
+            self.position.apply(qkv, run.step, self.num_heads, self.num_kv_heads, self.head_dim)
+            k.rope_kv_write(qkv, run.step, kv, None, self.num_heads, self.num_kv_heads, self.head_dim, q_out=q)
+        else:
+            # The projection's float32 slices go straight into the kernel that adds the bias, rotates q
+            # and k and stores k and v in their pages; q comes back in a buffer of its own.
+            slices = k.linear_split(x, self.qkv.weight)
+            k.rope_kv_write(slices, run.step, kv, table, self.num_heads, self.num_kv_heads, self.head_dim,
+                            bias=self.qkv.bias, q_out=q)
         mixed = torch.empty_like(q)
         k.attention(q, mixed, run.step, run.kv, self.num_heads, self.num_kv_heads, self.head_dim, self.window, self.scale)
         if self.out.bias is not None:

@@ -39,10 +39,11 @@ def swiglu(gate_up):
 def rotate(x, positions, rotary: RotaryTable | None):
     """x [T, heads, d] -> rotated, float32 arithmetic, stored back in x.dtype."""
     if rotary is None:
-        return x
+        return x.clone()
     rot = rotary.rotary_dim
     angles = positions.float()[:, None] * rotary.inv_freq.float()[None, :]
-    cos, sin = angles.cos()[:, None, :], angles.sin()[:, None, :]
+    factor = float(getattr(rotary, "factor", 1.0))
+    cos, sin = angles.cos()[:, None, :] * factor, angles.sin()[:, None, :] * factor
     xf = x.float()
     out = xf.clone()
     if rotary.interleaved:
@@ -71,6 +72,8 @@ def rope_kv_write(qkv, step: StepTensors, kv: KvSlot | None, rotary, num_heads, 
     positions = step.positions[:tokens]
     q = rotate(qkv[:tokens, :q_end].reshape(tokens, num_heads, head_dim), positions, rotary)
     qkv[:tokens, :q_end] = q.reshape(tokens, q_end)
+    if q_out is not None:
+        q_out.copy_(qkv[:tokens, :q_end])
     if kv is None:
         return
     k = rotate(qkv[:tokens, q_end:k_end].reshape(tokens, num_kv_heads, head_dim), positions, rotary)

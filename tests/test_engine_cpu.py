@@ -245,3 +245,109 @@ def test_step_statistics_split_and_line():
     engine.generate([helpers.random_ids(cfg["vocab_size"], n, n) for n in (5, 9)], max_new_tokens=6)
     assert engine.stats.lines and "decode n=" in " ".join(engine.stats.lines)
     assert sum(s["steps"] for s in engine.stats.summaries) == engine.steps
+
+
+def test_constants_around_the_stack_and_a_position_encoding_of_its_own():
+    """What another architecture may need of the model builder, set from outside the package: a scale on
+    the embedded tokens, a scale and a soft cap on the logits, a factor on the rotation's cos and sin, and
+    a position encoding that is no table of frequencies at all (it offers ``apply`` and the mixer calls it)."""
+    from dataclasses import replace
+
+    from distie_b200.config import PartSpec
+    from distie_b200.engine.engine import build_cache
+    from distie_b200.models.decoder import DecoderModel, model_tensor_specs
+    from distie_b200.parts import POSITION_ENCODINGS
+    from distie_b200.weights import open_weights
+
+    cfg, page, weights = helpers.tiny("A")
+    hidden, heads, kv_heads, d = cfg["hidden_size"], cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    arch = get_architecture(cfg["architectures"][0])
+    spec = arch.recipe(arch.config_cls.from_dict(cfg))
+
+    def angles(positions):  # a rotation whose angle is no multiple of the position: not a table of frequencies
+        inv = plain.rope_inverse_frequencies(d, 10000.0)
+        return torch.sqrt(positions.float() + 1.0)[:, None] * inv[None, :]
+
+    class RootRotation:
+        applied = 0
+
+        @classmethod
+        def build(cls, part, ctx):
+            return cls()
+
+        def rotary_table(self):
+            return None
+
+        def apply(self, qkv, step, num_heads, num_kv_heads, head_dim):
+            RootRotation.applied += 1
+            a = angles(step.positions[: step.num_tokens])
+            cos, sin = torch.cat((a, a), -1).cos(), torch.cat((a, a), -1).sin()
+            rot = qkv[:, : (num_heads + num_kv_heads) * head_dim].reshape(step.num_tokens, num_heads + num_kv_heads, head_dim)
+            rot.copy_(plain.apply_rope(rot.float(), cos, sin).to(qkv.dtype))
+
+    def build(layers_position, **around):
+        layers = tuple(
+            replace(layer, mixer=PartSpec(layer.mixer.kind, {**layer.mixer.params, "position": layers_position}, layer.mixer.prefix))
+            for layer in spec.layers
+        )
+        changed = replace(spec, layers=layers, **around)
+        kernels = RefKernels(torch.float32)
+        config = EngineConfig(num_blocks=8, page_size=page, max_seqs=2, dtype="float32", decode_graphs=False, device="cpu")
+        store = open_weights(weights, model_tensor_specs(changed), changed.tolerated, kernels.dtype, kernels.device)
+        return Engine(DecoderModel(changed, kernels, store), build_cache(changed, config, kernels.dtype, kernels.device), config)
+
+    def plain_logits(ids, rope, embedding_scale=1.0, logit_scale=1.0, softcap=None):
+        """The plain implementation's parts, put together with another rotation and the constants around the stack."""
+        positions = torch.arange(len(ids))
+        h = plain.embedding(torch.tensor(ids), weights["model.embed_tokens.weight"]) * embedding_scale
+        for layer in range(cfg["num_hidden_layers"]):
+            p = f"model.layers.{layer}."
+            x = plain.rms_norm(h, weights[p + "input_layernorm.weight"], cfg["rms_norm_eps"])
+            q, k, v = (torch.nn.functional.linear(x, weights[p + f"self_attn.{n}_proj.weight"], weights[p + f"self_attn.{n}_proj.bias"])
+                       for n in "qkv")
+            cos, sin = rope(positions)
+            q = plain.apply_rope(q.view(-1, heads, d), cos, sin)
+            k = plain.apply_rope(k.view(-1, kv_heads, d), cos, sin)
+            mixed = plain.attention_mix(q, k, v.view(-1, kv_heads, d))
+            h = h + torch.nn.functional.linear(mixed.reshape(-1, heads * d), weights[p + "self_attn.o_proj.weight"])
+            h = h + plain.swiglu_mlp(plain.rms_norm(h, weights[p + "post_attention_layernorm.weight"], cfg["rms_norm_eps"]), weights, p + "mlp.")
+        logits = plain.output_head(h, weights, cfg).float() * logit_scale
+        return softcap * torch.tanh(logits / softcap) if softcap else logits
+
+    ids = helpers.random_ids(cfg["vocab_size"], 37, 8)
+
+    def engine_logits(engine):
+        session = TraceSession(engine)
+        first = session.run_step([{"id": "x", "tokens": ids[:20], "want": list(range(20))}])
+        rest = [session.run_step([{"id": "x", "tokens": [t], "want": [0]}]) for t in ids[20:]]
+        return torch.cat([torch.as_tensor(first)] + [torch.as_tensor(r) for r in rest])
+
+    # 1. constants around the stack and a factor on cos and sin
+    factor = 1.3
+    scaled = build(PartSpec("rotary", {"head_dim": d, "theta": cfg["rope_theta"], "factor": factor}),
+                   embedding_scale=hidden**0.5, logit_scale=0.25, logit_softcap=30.0)
+
+    def scaled_rope(positions):
+        cos, sin = plain.rope_tables(positions, d, cfg["rope_theta"])
+        return cos * factor, sin * factor
+
+    want = plain_logits(ids, scaled_rope, hidden**0.5, 0.25, 30.0)
+    assert float((engine_logits(scaled) - want).abs().max()) <= helpers.FP32_TOL * plain.logit_scale(want)
+    assert float(want.abs().max()) <= 30.0
+
+    # 2. a position encoding with an ``apply`` of its own
+    POSITION_ENCODINGS.register("test_root_rotation", RootRotation)
+    try:
+        own = build(PartSpec("test_root_rotation", {}))
+
+        def root_rope(positions):
+            a = angles(positions)
+            return torch.cat((a, a), -1).cos(), torch.cat((a, a), -1).sin()
+
+        want = plain_logits(ids, root_rope)
+        assert float((engine_logits(own) - want).abs().max()) <= helpers.FP32_TOL * plain.logit_scale(want)
+        assert RootRotation.applied > 0
+        differs = plain.forward_logits(ids, weights, cfg)
+        assert float((differs - want).abs().max()) > 100 * helpers.FP32_TOL * plain.logit_scale(want), "the rotation must matter"
+    finally:
+        POSITION_ENCODINGS.unregister("test_root_rotation")

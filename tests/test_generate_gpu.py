@@ -475,6 +475,118 @@ def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
         unregister_architecture("ToyRunningMean")
 
 
+def test_toy_mixer_with_state_on_the_device_keeps_the_graphs(tmp_path):
+    """The same running mean written against the step's device tensors only (the token's seat through
+    ``step.seq_seat[step.token_seq]``, its count through ``step.positions``): state of fixed size then costs
+    no graphs, and a captured decode step reads and updates the slots of whatever seats it is replayed for."""
+    from distie_b200.config import LayerCall, LayerSpec, ModelSpec, PartSpec, register_architecture, unregister_architecture
+    from distie_b200.engine.engine import Engine
+    from distie_b200.engine.trace_replay import TraceSession
+    from distie_b200.parts import MIXERS, StateNeed, TensorSpec
+    from distie_b200.weights import write_random_model
+
+    hidden, vocab = 48, 64
+
+    class DeviceRunningMeanMixer:
+        """delta[t] = W @ mean(x[0..t]) of the token's request; state = the sum so far [hidden]."""
+
+        graph_safe = True  # nothing below looks at run.seqs or any other host-side batch data
+
+        def __init__(self, weight, kernels):
+            self.weight, self.kernels = weight, kernels
+
+        @classmethod
+        def tensor_specs(cls, spec, hidden_size):
+            return [TensorSpec(spec.prefix + "mix.weight", (hidden_size, hidden_size))]
+
+        @classmethod
+        def cache_need(cls, spec):
+            return None
+
+        @classmethod
+        def state_need(cls, spec):
+            return StateNeed((hidden,), torch.float32)
+
+        @classmethod
+        def build(cls, spec, ctx):
+            return cls(ctx.weights.matrix(spec.prefix + "mix.weight"), ctx.kernels)
+
+        def forward(self, x, run):
+            step = run.step
+            rows = x.float()
+            token_seq = step.token_seq.long()
+            seats = step.seq_seat.long()[token_seq]  # the slot of each token's request
+            index = torch.arange(rows.shape[0], device=x.device)
+            starts = torch.ones_like(token_seq, dtype=torch.bool)
+            starts[1:] = token_seq[1:] != token_seq[:-1]
+            first = torch.cummax(torch.where(starts, index, torch.zeros_like(index)), 0).values  # first token of the request's portion
+            running = torch.cumsum(rows, 0)
+            before = torch.cat([torch.zeros_like(running[:1]), running[:-1]])[first]
+            sums = run.state[seats] + (running - before)
+            means = sums / (step.positions.float() + 1.0)[:, None]
+            run.state.index_add_(0, seats, rows)  # every request's slot moves on by its portion
+            return self.kernels.linear(means.to(x.dtype), self.weight)
+
+    class ToyConfig:
+        def __init__(self, raw):
+            self.raw = raw
+            self.eos_token_id = None
+
+        @classmethod
+        def from_dict(cls, raw):
+            return cls(dict(raw))
+
+    def recipe(cfg):
+        layers = tuple(
+            LayerSpec(
+                "pre_norm",
+                PartSpec("test_device_running_mean", {}, f"l{i}."),
+                PartSpec("swiglu", {"intermediate_size": 80}, f"l{i}.ff."),
+                {"input": PartSpec("rmsnorm", {"eps": 1e-5}, f"l{i}.n1."), "post_mixer": PartSpec("rmsnorm", {"eps": 1e-5}, f"l{i}.n2.")},
+            )
+            for i in range(2)
+        )
+        return ModelSpec("ToyDeviceRunningMean", vocab, hidden, layers, (LayerCall(0, 0), LayerCall(1, 1)),
+                         PartSpec("rmsnorm", {"eps": 1e-5}, "norm."), "embed.weight", None)
+
+    MIXERS.register("test_device_running_mean", DeviceRunningMeanMixer)
+    register_architecture("ToyDeviceRunningMean", ToyConfig, recipe)
+    try:
+        folder = write_random_model(str(tmp_path / "toy"), {"architectures": ["ToyDeviceRunningMean"]}, seed=4, std=0.3, dtype="float32")
+        engine = Engine.load(folder, dtype="float32", num_blocks=4, page_size=16, max_seqs=4, decode_graphs=True)
+        assert engine.runner.use_graphs, "state indexed on the device keeps the captured decode steps"
+        session = TraceSession(engine)
+        ids_a, ids_b, ids_c = (helpers.random_ids(vocab, n, seed) for n, seed in ((21, 1), (12, 2), (7, 3)))
+        whole = {name: torch.as_tensor(session.run_step([{"id": name, "tokens": ids, "want": list(range(len(ids)))}], [name]))
+                 for name, ids in (("a", ids_a), ("b", ids_b), ("c", ids_c))}
+        assert engine.runner.graph_replays == 0
+        # Portions, then single tokens of two and three requests at once (captured steps of bucket 2 and 4,
+        # replayed for changing seats), compared with each request run whole.
+        got = {"a": [], "b": [], "c": []}
+        out = session.run_step([{"id": "a", "tokens": ids_a[:8], "want": list(range(8))}, {"id": "b", "tokens": ids_b[:5], "want": list(range(5))}])
+        got["a"].append(torch.as_tensor(out[:8])), got["b"].append(torch.as_tensor(out[8:]))
+        for at in range(5):
+            entries = [{"id": "a", "tokens": [ids_a[8 + at]], "want": [0]}, {"id": "b", "tokens": [ids_b[5 + at]], "want": [0]}]
+            if at >= 2:
+                entries.append({"id": "c", "tokens": [ids_c[at - 2]], "want": [0]})
+            out = torch.as_tensor(session.run_step(entries))
+            for row, entry in enumerate(entries):
+                got[entry["id"]].append(out[row : row + 1])
+        assert engine.runner.graph_replays >= 3
+        for name, ids in (("a", ids_a), ("b", ids_b), ("c", ids_c)):
+            have = torch.cat(got[name])
+            want = whole[name][: have.shape[0]]
+            assert float((have - want).abs().max()) <= 1e-4 * max(1.0, float(want.abs().max())), name
+        for name in "abc":
+            session.run_step([], [name])
+        seat = engine.cache.open_seat()  # a reopened seat starts from zero state
+        assert float(engine.cache.states[0][seat].abs().sum()) == 0.0
+        engine.cache.close_seat(seat)
+    finally:
+        MIXERS.unregister("test_device_running_mean")
+        unregister_architecture("ToyDeviceRunningMean")
+
+
 # -- a toy feed-forward with routing and a toy position encoding, registered from outside the package ------
 def test_toy_routed_feed_forward_and_position_encoding(tmp_path):
     """Two experts chosen per token by a router, and a rotation with frequencies of its own: both defined

@@ -244,10 +244,11 @@ def test_linear_swiglu(kernel_sets, dtype, m, k, inter):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize(
-    "heads,kv_heads,head_dim,rotary_dim,interleaved,page",
-    [(4, 2, 16, 16, False, 16), (3, 1, 32, 32, False, 8), (12, 2, 128, 128, False, 16), (5, 5, 48, 24, True, 4), (6, 3, 80, 80, False, 32)],
+    "heads,kv_heads,head_dim,rotary_dim,interleaved,page,factor",
+    [(4, 2, 16, 16, False, 16, 1.0), (3, 1, 32, 32, False, 8, 1.0), (12, 2, 128, 128, False, 16, 1.0), (5, 5, 48, 24, True, 4, 1.0),
+     (6, 3, 80, 80, False, 32, 1.0), (4, 2, 64, 64, False, 16, 1.25), (2, 1, 48, 16, True, 8, 0.8)],
 )
-def test_rope_kv_write(kernel_sets, dtype, heads, kv_heads, head_dim, rotary_dim, interleaved, page):
+def test_rope_kv_write(kernel_sets, dtype, heads, kv_heads, head_dim, rotary_dim, interleaved, page, factor):
     from distie_b200.kernels.interface import RotaryTable
 
     ks = kernel_sets[dtype]
@@ -257,7 +258,7 @@ def test_rope_kv_write(kernel_sets, dtype, heads, kv_heads, head_dim, rotary_dim
     kv = make_cache(dtype, 64, kv_heads, page, head_dim, 4, width, fill=False)
     kv_ref = make_cache(dtype, 64, kv_heads, page, head_dim, 4, width, fill=False)
     inv_freq = (1.0 / (10000.0 ** (torch.arange(0, rotary_dim, 2, dtype=torch.float32) / rotary_dim))).cuda()
-    rotary = RotaryTable(inv_freq, rotary_dim, interleaved)
+    rotary = RotaryTable(inv_freq, rotary_dim, interleaved, factor)  # the factor scales cos and sin
     qkv = torch.randn(step.num_tokens, (heads + 2 * kv_heads) * head_dim, device="cuda").to(dtype)
     mine, theirs = qkv.clone(), qkv.clone()
     ks.rope_kv_write(mine, step, kv, rotary, heads, kv_heads, head_dim)
@@ -373,10 +374,13 @@ def test_attention_finds_one_far_key(kernel_sets, dtype, head_dim, page, far):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("head_dim,page,window", [(128, 16, None), (64, 8, None), (128, 16, 70), (64, 16, 200), (128, 32, 1)])
+@pytest.mark.parametrize("head_dim,page,window", [(128, 16, None), (64, 8, None), (128, 16, 70), (64, 16, 200), (128, 32, 1),
+                                                  (128, 4, None), (64, 24, 100)])
 def test_prompt_portion_attention_long_context(kernel_sets, dtype, head_dim, page, window):
-    """A portion of 150 tokens after 900 cached ones beside a whole short prompt: tiles, diagonal, window edges."""
+    """A portion of 150 tokens after 900 cached ones beside a whole short prompt: tiles, diagonal, window edges.
+    Pages of 4 and of 24 rows are sizes the tcgen05 kernel refuses: in bfloat16 the mma.sync kernel takes over."""
     ks = kernel_sets[dtype]
+    before = dict(ks.kernel_counts)
     heads, kv_heads = 6, 2
     tokens_per_seq, pasts = [150, 1, 70, 64], [900, 40, 0, 64]
     kv = filled_cache_for(dtype, kv_heads, head_dim, page, [p + n for p, n in zip(pasts, tokens_per_seq)], seed=3)
@@ -387,6 +391,9 @@ def test_prompt_portion_attention_long_context(kernel_sets, dtype, head_dim, pag
     ks.check_errors()
     want = ref.attention(qkv, step, kv, heads, kv_heads, head_dim, window, head_dim**-0.5)
     close(out, want, dtype, "attention over a long context")
+    if dtype == torch.bfloat16:
+        ran = {name for name, count in ks.kernel_counts.items() if count > before.get(name, 0)}
+        assert ("attention_prefill" if page in (4, 24) else "attention_prefill_tcgen05") in ran, sorted(ran)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
