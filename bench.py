@@ -232,14 +232,16 @@ def time_decode(engine, burst, batch: int, prompt_len: int, steps: int, warmup: 
     advanced = [type(item)(item.seq, item.token_ids, item.past_len + max(warmup, 1), True) for item in plan.items]
     torch.cuda.synchronize()
     begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.profiler.start()  # a profiler started with "profile from start off" sees the timed steps only
     begin.record()
     tokens = burst.run(advanced, steps)
     end.record()
     torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
     ms = begin.elapsed_time(end)
     engine.runner.finish_step()
     assert tokens.shape == (steps, batch)
-    mean_context = plan.items[0].past_len + 1 + max(warmup, 1) + steps / 2
+    mean_context = sum(item.past_len for item in plan.items) / batch + 1 + max(warmup, 1) + steps / 2
     release(engine, batch, tag)
     return {
         "ms_per_step": ms / steps,
@@ -289,7 +291,7 @@ def time_prefill(engine, repeats: int = 5, past: int = 0) -> dict:
     vocab = engine.model.vocab_size
     prompt = random_prompt(vocab, past + PREFILL_TOKENS, 7)
     times = []
-    for _ in range(repeats + 2):
+    for index in range(repeats + 2):
         seat = engine.cache.open_seat()
         assert engine.cache.grow(seat, past + PREFILL_TOKENS)
         for start in range(0, past, PREFILL_TOKENS):  # the earlier portions, untimed
@@ -297,10 +299,14 @@ def time_prefill(engine, repeats: int = 5, past: int = 0) -> dict:
             engine.runner.finish_step()
         torch.cuda.synchronize()
         begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if index == repeats + 1:
+            torch.cuda.profiler.start()  # a profiler started with "profile from start off" sees the last repeat only
         begin.record()
         engine.runner.step([BatchEntry(seat, prompt[past:], past, (PREFILL_TOKENS - 1,))])
         end.record()
         torch.cuda.synchronize()
+        if index == repeats + 1:
+            torch.cuda.profiler.stop()
         times.append(begin.elapsed_time(end))
         engine.runner.finish_step()
         engine.cache.close_seat(seat)
@@ -393,6 +399,8 @@ def main() -> int:
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--only", default=None, choices=["decode", "prefill", "serving"],
                         help="run one part and print a short line (for profiling captures; not a bench value)")
+    parser.add_argument("--pages", type=int, default=None,
+                        help="cache pages instead of sizing from free memory (small captures under a profiler)")
     parser.add_argument("--past", type=int, default=0,
                         help="with --only prefill: tokens already in the cache ahead of the timed 2,048-token portion")
     parser.add_argument("--ref-attn", default=None, choices=["auto", "flash", "torch"],
@@ -436,7 +444,7 @@ def main() -> int:
         "data": "synthetic: random N(0,0.02) weights, uniform random token ids", "impl": "ours",
     }
 
-    if args.shape == "7b" or args.only == "serving":
+    if args.only == "serving" or (args.shape == "7b" and args.only is None):
         # BASELINE.json configs[3]: mixed continuous batching through the Python entry point.
         engine = build_engine(shape, layers, 32, None, 2048 + 256 + 64, dtype, gpu_mem_fraction=0.85, step_stats=100000)
         with ClockSampler() as sampler:
@@ -457,11 +465,11 @@ def main() -> int:
     if args.only == "prefill" and args.past > 0:
         pages = 2 * -(-(args.past + PREFILL_TOKENS) // PAGE)
         engine = build_engine(shape, layers, 8, pages, max(CONTEXT, args.past + PREFILL_TOKENS), dtype)
-    elif args.shape == "1.5b":
+    elif args.shape == "1.5b" and args.pages is None:
         pages = 64 * -(-(prompt_len + new_tokens + 2 * 64 + 1) // PAGE) + 2 * (PREFILL_TOKENS // PAGE)
         engine = build_engine(shape, layers, 64, pages, context, dtype)
     else:
-        engine = build_engine(shape, layers, 64, None, context, dtype, gpu_mem_fraction=0.85)
+        engine = build_engine(shape, layers, 64, args.pages, context, dtype, gpu_mem_fraction=0.85)
         config["cache_pages"] = engine.config.num_blocks
     burst = DecodeBurst(engine.runner)
     weight_bytes = engine.model.weight_bytes()
