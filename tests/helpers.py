@@ -66,11 +66,28 @@ TINY_D = {
     "tie_word_embeddings": False,
     "max_position_embeddings": 4096,
 }
+# Sizes chosen to be awkward: a head size that is no power of two, as many kv heads as heads, an intermediate
+# size that is no multiple of 8, an odd vocabulary, pages of 4 tokens.
+TINY_E = {
+    "architectures": ["Qwen2ForCausalLM"],
+    "vocab_size": 1001,
+    "hidden_size": 240,
+    "intermediate_size": 250,
+    "num_hidden_layers": 2,
+    "num_attention_heads": 5,
+    "num_key_value_heads": 5,
+    "head_dim": 48,
+    "rms_norm_eps": 1e-6,
+    "rope_theta": 50000.0,
+    "tie_word_embeddings": False,
+    "max_position_embeddings": 1024,
+}
 # config, page size, seed, norm noise
-TINY = {"A": (TINY_A, 16, 0, 0.0), "B": (TINY_B, 8, 1, 0.02), "C": (TINY_C, 16, 2, 0.0), "D": (TINY_D, 32, 3, 0.02)}
+TINY = {"A": (TINY_A, 16, 0, 0.0), "B": (TINY_B, 8, 1, 0.02), "C": (TINY_C, 16, 2, 0.0), "D": (TINY_D, 32, 3, 0.02),
+        "E": (TINY_E, 4, 4, 0.02)}
 # Standard deviation of the test weights per configuration: wide layers need smaller weights for logits
 # of a scale at which a wrong key shows without saturating the softmax.
-STD = {"A": 0.2, "B": 0.2, "C": 0.1, "D": 0.07}
+STD = {"A": 0.2, "B": 0.2, "C": 0.1, "D": 0.07, "E": 0.1}
 
 # Weights far larger than N(0, 0.02): logits then have a scale at which a wrong key shows.
 TEST_STD = 0.2

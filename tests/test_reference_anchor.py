@@ -70,7 +70,7 @@ def _reference_model(ref, cfg, weights):
     return model, dims
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_plain_matches_the_reference_model_live(reference, name):
     cfg, page, weights = helpers.tiny(name)
     model, dims = _reference_model(reference, cfg, weights)

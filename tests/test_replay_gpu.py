@@ -36,7 +36,7 @@ SERVING_KERNELS = {
 }
 
 
-@pytest.fixture(scope="module", params=["A", "B", "C", "D"])
+@pytest.fixture(scope="module", params=["A", "B", "C", "D", "E"])
 def model(request, tmp_path_factory):
     """A model folder of the tiny configuration, written by the random-weights mode, and its plain logits."""
     from distie_b200.weights import ModelTensors, write_random_model
