@@ -425,7 +425,7 @@ def main() -> int:
     name = SHAPE_NAME[args.shape]
     # The default run decodes behind 1,024-token prompts; the 14B configuration asks for 2,048-token contexts,
     # which its requests reach at the end of the timed steps.
-    context = CONTEXT if args.shape == "1.5b" else 2048 + 64
+    context = CONTEXT if args.shape == "1.5b" else 2048 + 256  # room for the tokens requests decode while others are still prefilled
     prompt_len = PROMPT_LEN if args.shape == "1.5b" else 2048 - (max(args.warmup, 1) + args.steps + 1)
     if prompt_len < 64:
         print(json.dumps({"unsupported": "--steps too large for a 2,048-token context"}))
