@@ -117,14 +117,16 @@ def test_trace_free_running_and_forced():
     assert engine.cache.free_pages() == engine.cache.total_pages()
 
 
-def test_corrupted_cache_is_detected():
-    """The comparison can fail: a page overwritten between steps changes later logits."""
+@pytest.mark.parametrize("layer,which", [(0, 0), (0, 1), (1, 0), (1, 1)])
+def test_corrupted_cache_is_detected(layer, which):
+    """The comparison can fail: ONE page of ONE layer's keys (or values) overwritten between steps changes
+    the logits that follow, whichever layer and whichever of the two it is."""
     engine, cfg, weights = cpu_engine("A", num_blocks=16)
     ids = helpers.random_ids(cfg["vocab_size"], 40, 3)
     session = TraceSession(engine)
     session.run_step([{"id": "x", "tokens": ids[:30], "want": []}])
     page = engine.cache.pages_held(session.live["x"][0])[0][0]
-    engine.cache.groups[0].slab[:, 0, page] += 1.0
+    engine.cache.groups[0].slab[layer, which, page] += 1.0
     got = session.run_step([{"id": "x", "tokens": ids[30:], "want": list(range(10))}], ["x"])
     want = plain.forward_logits(ids, weights, cfg)[30:]
     assert float((torch.as_tensor(got) - want).abs().max()) > 100 * helpers.FP32_TOL * plain.logit_scale(want)
