@@ -580,6 +580,60 @@ extern "C" int distie_rope_kv_write(void* qkv, const int* positions, const int* 
   return 0;
 }
 
+// What the q/k/v product's fused epilogue reads per token, made once per step and shared by the layers of a
+// cache group: trig[t] = (cos of the token's angles | sin of them) * factor, [head_dim] float32 (1 | 0 without
+// a table of frequencies), and cache_row[t] = page * kv_heads * page_size + pos % page_size, the row of the
+// token's slot for kv head 0 in a cache of [pages, kv_heads, page_size, head_dim], or -1 (with the error flag
+// set) where the block table has no page for it.
+__global__ void rope_rows_kernel(const int* __restrict__ positions, const int* __restrict__ token_seq,
+                                 const int* __restrict__ seq_seat, const int* __restrict__ block_table, int table_width,
+                                 const float* __restrict__ inv_freq, float trig_factor, int tokens, int head_dim,
+                                 int num_kv_heads, int page_size, int num_pages, float* __restrict__ trig,
+                                 int* __restrict__ cache_row, int* __restrict__ error) {
+  const int t = blockIdx.x;
+  if (t >= tokens) return;
+  const int pos = positions[t];
+  const int half = head_dim >> 1;
+  for (int j = threadIdx.x; j < half; j += blockDim.x) {
+    float s = 0.f, c = 1.f;
+    if (inv_freq) {
+      sincosf((float)pos * inv_freq[j], &s, &c);
+      c *= trig_factor;
+      s *= trig_factor;
+    }
+    trig[(size_t)t * head_dim + j] = c;
+    trig[(size_t)t * head_dim + half + j] = s;
+  }
+  if (threadIdx.x == 0 && cache_row != nullptr) {
+    const int seat = seq_seat[token_seq[t]];
+    const int column = pos / page_size;
+    const int page = (pos >= 0 && column < table_width) ? block_table[(size_t)seat * table_width + column] : -1;
+    if (page < 0 || page >= num_pages) {
+      if (error) atomicExch(error, 2);
+      cache_row[t] = -1;
+    } else {
+      cache_row[t] = page * num_kv_heads * page_size + (pos % page_size);
+    }
+  }
+}
+
+extern "C" int distie_rope_rows(const int* positions, const int* token_seq, const int* seq_seat, const int* block_table,
+                                int table_width, const float* inv_freq, float trig_factor, int tokens, int head_dim,
+                                int num_kv_heads, int page_size, int num_pages, float* trig, int* cache_row, int* error,
+                                cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (head_dim < 2 || (head_dim & 1) || trig == nullptr || positions == nullptr) return DISTIE_ERR_ARG;
+  if (cache_row != nullptr) {
+    if (num_kv_heads < 1 || page_size < 1 || table_width < 1 || num_pages < 1 || block_table == nullptr) return DISTIE_ERR_ARG;
+    if ((long long)num_pages * num_kv_heads * page_size > 0x7fffffffLL) return DISTIE_ERR_UNSUPPORTED;  // rows are int32
+  }
+  rope_rows_kernel<<<tokens, 64, 0, stream>>>(positions, token_seq, seq_seat, block_table, table_width, inv_freq,
+                                              trig_factor, tokens, head_dim, num_kv_heads, page_size, num_pages, trig,
+                                              cache_row, error);
+  DISTIE_LAUNCH_CHECK();
+  return 0;
+}
+
 // The same two kernels fed with the float32 partial sums of a product whose K was split
 // (`splits` slices of [rows, width], `split_stride` elements apart).  They exist only in the
 // vectorised form: other shapes return DISTIE_ERR_UNSUPPORTED and the caller adds the slices up itself.

@@ -33,6 +33,7 @@ constexpr int kGemmWideThreads = 320;  // the tile kernels: producer, MMA issuer
 constexpr int GEMM_EPI_BF16 = 0;
 constexpr int GEMM_EPI_F32 = 1;
 constexpr int GEMM_EPI_SWIGLU = 2;
+constexpr int GEMM_EPI_QKV = 3;  // bias, rotation and the write of q, k and v (store_qkv_rope); tiles of 256 columns
 
 template <int BN, int STAGES>
 struct GemmShared {
@@ -129,6 +130,117 @@ __device__ __forceinline__ void store_accumulator(uint32_t lane_base, int row0, 
   }
 }
 
+// What the q/k/v epilogue needs beside the accumulator: see store_qkv_rope.
+struct QkvEpilogue {
+  const float* bias;     // [N] or null
+  const float* trig;     // [M, head_dim]: cos of the row's angles in the first half, sin in the second (already scaled)
+  const int* cache_row;  // [M]: row of the token's slot in the cache for kv head 0 (page * kv_heads * page_size + pos % page_size), -1: none
+  __nv_bfloat16* k_cache;
+  __nv_bfloat16* v_cache;
+  int num_heads, num_kv_heads, head_dim, page_size;
+};
+
+// The epilogue of the q/k/v projection of prompt portions: bias, rotation of q and k (pairs (j, j + head_dim / 2),
+// cos and sin of the row's position from a table made once per step), q to its buffer and k and v straight into
+// the token's slot of the paged cache, all as bfloat16.  The float32 product never goes to memory, and the
+// rotation kernel that used to read it back is not launched.
+//
+// A warp has 32 rows of the tile; the two warps of a quarter of the rows split every head of the tile's 256
+// columns by pairs: warp `part` takes pairs [part * HD / 4, (part + 1) * HD / 4) of each head, so it needs
+// only that quarter of the cos and of the sin of its rows.  It copies them into shared memory of its own
+// (qkv_stage_trig, asynchronously, while the MMAs of the tile still run), because 32 rows reading their
+// own 512 bytes of the table from L2 piece by piece would wait for every piece.  `out` is the q buffer.
+constexpr int kQkvStageFloats = 32 * (128 / 2 + 4);  // per epilogue warp: 32 rows of (cos quarter | sin quarter), padded
+
+template <int HD>
+__device__ __forceinline__ void qkv_stage_trig(float* stage, int row0, int lane, int part, int M, const float* trig) {
+  constexpr int QW = HD / 4, STRIDE = HD / 2 + 4, PIECES = QW / 4;  // 16-byte pieces per row and segment
+#pragma unroll
+  for (int idx = lane; idx < 32 * 2 * PIECES; idx += 32) {
+    const int row = idx / (2 * PIECES), rem = idx % (2 * PIECES), seg = rem / PIECES, piece = rem % PIECES;
+    if (row0 + row < M) {
+      const float* src = trig + (size_t)(row0 + row) * HD + seg * (HD / 2) + part * QW + piece * 4;
+      asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(smem_u32(stage + row * STRIDE + seg * QW + piece * 4)),
+                   "l"(src) : "memory");
+    }
+  }
+  asm volatile("cp.async.commit_group;" ::: "memory");
+}
+
+template <int HD>
+__device__ __forceinline__ void store_qkv_rope(uint32_t lane_base, int row0, int lane, int n0, int part,
+                                               __nv_bfloat16* __restrict__ q_out, int ldq, int M, int N,
+                                               const QkvEpilogue& e, const float* stage) {
+  constexpr int QW = HD / 4, STRIDE = HD / 2 + 4;
+  const int t = row0 + lane;
+  const bool valid = t < M;
+  const int slot = (valid && e.cache_row) ? e.cache_row[t] : -1;
+  const float* cs_row = stage + lane * STRIDE;
+  const float* sn_row = cs_row + QW;
+  const int lo_off = part * QW, hi_off = HD / 2 + part * QW;
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  __syncwarp();
+#pragma unroll
+  for (int h = 0; h < 256 / HD; ++h) {
+    const int col0 = h * HD;               // first column of the head inside the tile
+    if (n0 + col0 >= N) break;             // (uniform over the warp)
+    const int head = (n0 + col0) / HD;     // q heads, then k heads, then v heads
+    const bool is_q = head < e.num_heads, is_k = !is_q && head < e.num_heads + e.num_kv_heads;
+    const int kv_head = head - e.num_heads - (is_k ? 0 : e.num_kv_heads);
+    __nv_bfloat16* dst = nullptr;
+    if (valid) {
+      if (is_q)
+        dst = q_out + (size_t)t * ldq + (size_t)head * HD;
+      else if (slot >= 0)
+        dst = (is_k ? e.k_cache : e.v_cache) + ((size_t)slot + (size_t)kv_head * e.page_size) * HD;
+    }
+    const float* bias = e.bias ? e.bias + (size_t)head * HD : nullptr;
+    uint32_t lo[QW], hi[QW];
+    if constexpr (QW == 32) {
+      tmem_load_32(lane_base + col0 + lo_off, reinterpret_cast<uint32_t(&)[32]>(lo));
+      tmem_load_32(lane_base + col0 + hi_off, reinterpret_cast<uint32_t(&)[32]>(hi));
+    } else {
+      tmem_load_16(lane_base + col0 + lo_off, reinterpret_cast<uint32_t(&)[16]>(lo));
+      tmem_load_16(lane_base + col0 + hi_off, reinterpret_cast<uint32_t(&)[16]>(hi));
+    }
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+    if (dst != nullptr) {
+#pragma unroll
+      for (int j = 0; j < QW; j += 8) {
+        float a[8], b[8], y_lo[8], y_hi[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          a[i] = __uint_as_float(lo[j + i]);
+          b[i] = __uint_as_float(hi[j + i]);
+        }
+        if (bias) {
+          float ba[8], bb[8];
+          load8(bias + lo_off + j, ba);
+          load8(bias + hi_off + j, bb);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) { a[i] += ba[i]; b[i] += bb[i]; }
+        }
+        if (is_q || is_k) {
+          float cs[8], sn[8];
+          load8(cs_row + j, cs);
+          load8(sn_row + j, sn);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            y_lo[i] = a[i] * cs[i] - b[i] * sn[i];
+            y_hi[i] = b[i] * cs[i] + a[i] * sn[i];
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) { y_lo[i] = a[i]; y_hi[i] = b[i]; }
+        }
+        store8(dst + lo_off + j, y_lo);
+        store8(dst + hi_off + j, y_hi);
+      }
+    }
+    __syncwarp();  // the loads from tensor memory are warp-wide: rows without a destination rejoin here
+  }
+}
+
 // Persistent: a CTA walks the tiles blockIdx.x, blockIdx.x + gridDim.x, ...  The accumulator is
 // double-buffered in tensor memory (2 x 256 columns), so the epilogue of one tile runs while the
 // MMAs of the next fill the other buffer; the ring of shared-memory stages runs across tiles.
@@ -136,7 +248,7 @@ template <int BN, int STAGES, int EPI>
 __global__ void __launch_bounds__(kGemmWideThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     void* __restrict__ out, int ldo, int M, int N, int K, int inter, int m_tiles, int num_tiles,
-                    int* __restrict__ error) {
+                    const QkvEpilogue qkv, int* __restrict__ error) {
   extern __shared__ unsigned char raw[];
   auto& sm = *reinterpret_cast<GemmShared<BN, STAGES>*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
   constexpr uint32_t TMEM_COLS = 512;   // two accumulators, the second at column 256
@@ -227,20 +339,32 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   } else {
     // ---- epilogue: warps w and w + 4 share rows 32 * (w % 4) .. + 31 and take half of the columns each ------
     const int quadrant = warp & 3, part = (warp - 2) >> 2;
+    float* trig_stage = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(&sm) + ((sizeof(sm) + 15) & ~size_t(15))) +
+                        (warp - 2) * kQkvStageFloats;  // (behind the stages; only the q/k/v epilogue asks for the room)
     uint32_t round = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++round) {
       const uint32_t buffer = round & 1;
-      if (!mbar_wait(&sm.accum_full[buffer], (round >> 1) & 1) || sm.failed) { atomicExch(&sm.failed, 1u); break; }
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int m0 = (tile % m_tiles) * kGemmBM;
       const int n0 = (tile / m_tiles) * PER_TILE;
+      if (EPI == GEMM_EPI_QKV) {  // this warp's cos and sin, on their way while the tile's MMAs run
+        if (qkv.head_dim == 128) qkv_stage_trig<128>(trig_stage, m0 + quadrant * 32, lane, part, M, qkv.trig);
+        else qkv_stage_trig<64>(trig_stage, m0 + quadrant * 32, lane, part, M, qkv.trig);
+      }
+      if (!mbar_wait(&sm.accum_full[buffer], (round >> 1) & 1) || sm.failed) { atomicExch(&sm.failed, 1u); break; }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t lane_base = tmem + buffer * ACC_STRIDE + ((uint32_t)(quadrant * 32) << 16);
-      store_accumulator<BN, EPI>(lane_base, m0 + quadrant * 32, lane, n0, out, ldo, M, N, inter, part);
+      if (EPI == GEMM_EPI_QKV) {
+        if (qkv.head_dim == 128) store_qkv_rope<128>(lane_base, m0 + quadrant * 32, lane, n0, part, (__nv_bfloat16*)out, ldo, M, N, qkv, trig_stage);
+        else store_qkv_rope<64>(lane_base, m0 + quadrant * 32, lane, n0, part, (__nv_bfloat16*)out, ldo, M, N, qkv, trig_stage);
+      } else {
+        store_accumulator<BN, EPI>(lane_base, m0 + quadrant * 32, lane, n0, out, ldo, M, N, inter, part);
+      }
       // This warp has read its part of the accumulator: hand the buffer back to the MMA issuer.
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(&sm.accum_empty[buffer]);
     }
+    if (EPI == GEMM_EPI_QKV) asm volatile("cp.async.wait_all;" ::: "memory");  // (a loop left early: nothing stays in flight)
   }
 
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -280,7 +404,7 @@ template <int BN, int STAGES, int KB, int EPI>
 __global__ void __launch_bounds__(kGemmWideThreads, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                          void* __restrict__ out, int ldo, int M, int N, int K, int inter, int m_tiles, int num_tiles,
-                         int* __restrict__ error) {
+                         const QkvEpilogue qkv, int* __restrict__ error) {
   extern __shared__ unsigned char raw[];
   auto& sm = *reinterpret_cast<PairShared<BN, STAGES, KB>*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
   constexpr uint32_t TMEM_COLS = 512;   // two accumulators, the second at column 256
@@ -379,20 +503,32 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   } else {
     // ---- epilogue (both CTAs, each its own 128 rows; two warps per quarter of the rows, half the columns each) --
     const int quadrant = warp & 3, part = (warp - 2) >> 2;
+    float* trig_stage = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(&sm) + ((sizeof(sm) + 15) & ~size_t(15))) +
+                        (warp - 2) * kQkvStageFloats;  // (behind the stages; only the q/k/v epilogue asks for the room)
     uint32_t round = 0;
     for (int tile = pair; tile < num_tiles; tile += pairs, ++round) {
       const uint32_t buffer = round & 1;
+      const int m0 = (tile % m_tiles) * 2 * kGemmBM + (int)rank * kGemmBM;
+      const int n0 = (tile / m_tiles) * PER_TILE;
+      if (EPI == GEMM_EPI_QKV) {  // this warp's cos and sin, on their way while the tile's MMAs run
+        if (qkv.head_dim == 128) qkv_stage_trig<128>(trig_stage, m0 + quadrant * 32, lane, part, M, qkv.trig);
+        else qkv_stage_trig<64>(trig_stage, m0 + quadrant * 32, lane, part, M, qkv.trig);
+      }
       const bool ready = __all_sync(0xffffffffu, mbar_wait_unless(&sm.accum_full[buffer], (round >> 1) & 1, &sm.failed));
       if (!ready) { atomicExch(&sm.failed, 1u); break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const int m0 = (tile % m_tiles) * 2 * kGemmBM + (int)rank * kGemmBM;
-      const int n0 = (tile / m_tiles) * PER_TILE;
       const uint32_t lane_base = tmem + buffer * ACC_STRIDE + ((uint32_t)(quadrant * 32) << 16);
-      store_accumulator<BN, EPI>(lane_base, m0 + quadrant * 32, lane, n0, out, ldo, M, N, inter, part);
+      if (EPI == GEMM_EPI_QKV) {
+        if (qkv.head_dim == 128) store_qkv_rope<128>(lane_base, m0 + quadrant * 32, lane, n0, part, (__nv_bfloat16*)out, ldo, M, N, qkv, trig_stage);
+        else store_qkv_rope<64>(lane_base, m0 + quadrant * 32, lane, n0, part, (__nv_bfloat16*)out, ldo, M, N, qkv, trig_stage);
+      } else {
+        store_accumulator<BN, EPI>(lane_base, m0 + quadrant * 32, lane, n0, out, ldo, M, N, inter, part);
+      }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(cluster_address(&sm.accum_empty[buffer], 0));
     }
+    if (EPI == GEMM_EPI_QKV) asm volatile("cp.async.wait_all;" ::: "memory");  // (a loop left early: nothing stays in flight)
   }
 
   // Neither CTA may leave while the other can still reach its shared memory, barriers or tensor memory.
@@ -601,8 +737,8 @@ gemm_tcgen05_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
 // ---- host side ---------------------------------------------------------------------------------------------
 template <int BN, int STAGES, int EPI>
 static int launch_gemm(const CUtensorMap& map_a, const CUtensorMap& map_b, void* out, int ldo, int M, int N, int K,
-                       int inter, int sm_count, int* error, cudaStream_t stream) {
-  const size_t shared = sizeof(GemmShared<BN, STAGES>) + 1024;
+                       int inter, int sm_count, int* error, cudaStream_t stream, const QkvEpilogue& qkv = QkvEpilogue()) {
+  const size_t shared = sizeof(GemmShared<BN, STAGES>) + 1024 + (EPI == GEMM_EPI_QKV ? 16 + 8 * kQkvStageFloats * sizeof(float) : 0);
   static bool configured = false;
   if (!configured) {
     const cudaError_t err =
@@ -617,14 +753,14 @@ static int launch_gemm(const CUtensorMap& map_a, const CUtensorMap& map_b, void*
   const int grid = num_tiles < sm_count ? num_tiles : sm_count;
   const cudaError_t err =
       launch_dependent_family(64, gemm_tcgen05_kernel<BN, STAGES, EPI>, dim3(grid), dim3(kGemmWideThreads), shared, stream,
-                              map_a, map_b, out, ldo, M, N, K, inter, m_tiles, num_tiles, error);
+                              map_a, map_b, out, ldo, M, N, K, inter, m_tiles, num_tiles, qkv, error);
   return err == cudaSuccess ? 0 : (int)err;
 }
 
 template <int BN, int STAGES, int KB, int EPI>
 static int launch_gemm_pair(const CUtensorMap& map_a, const CUtensorMap& map_b, void* out, int ldo, int M, int N, int K,
-                            int inter, int sm_count, int* error, cudaStream_t stream) {
-  const size_t shared = sizeof(PairShared<BN, STAGES, KB>) + 1024;
+                            int inter, int sm_count, int* error, cudaStream_t stream, const QkvEpilogue& qkv = QkvEpilogue()) {
+  const size_t shared = sizeof(PairShared<BN, STAGES, KB>) + 1024 + (EPI == GEMM_EPI_QKV ? 16 + 8 * kQkvStageFloats * sizeof(float) : 0);
   static bool configured = false;
   static int resident_pairs = 0;  // pairs that can run at the same time (an SM left over in a GPC hosts none)
   if (!configured) {
@@ -655,7 +791,7 @@ static int launch_gemm_pair(const CUtensorMap& map_a, const CUtensorMap& map_b, 
   const int pairs = num_tiles < slots ? num_tiles : slots;
   const cudaError_t err = launch_dependent_cluster(64, dim3(2, 1, 1), gemm_tcgen05_pair_kernel<BN, STAGES, KB, EPI>,
                                                    dim3(2 * pairs), dim3(kGemmWideThreads), shared, stream, map_a, map_b, out,
-                                                   ldo, M, N, K, inter, m_tiles, num_tiles, error);
+                                                   ldo, M, N, K, inter, m_tiles, num_tiles, qkv, error);
   return err == cudaSuccess ? 0 : (int)err;
 }
 
@@ -735,6 +871,42 @@ extern "C" int distie_gemm_tcgen05(const void* x, int ldx, const void* w, void* 
   if (width == 192) { DISTIE_GEMM(192, 5); }
   DISTIE_GEMM(128, 6);
 #undef DISTIE_GEMM
+}
+
+// The q/k/v projection of prompt portions with its epilogue fused in: x[M >= 128, K] w[N, K]^T + bias, q and k
+// rotated, q to q_out[M, num_heads * head_dim] (row stride ldq) and k and v into the paged cache, all bfloat16.
+// `trig` [M, head_dim] float32 and `cache_row` [M] int32 come from distie_rope_rows (once per step); `cache_row`
+// null: nothing is written to the cache.  head_dim 64 or 128; N = (num_heads + 2 * num_kv_heads) * head_dim.
+extern "C" int distie_gemm_tcgen05_qkv(const void* x, int ldx, const void* w, const float* bias, const float* trig,
+                                       const int* cache_row, void* q_out, int ldq, void* k_cache, void* v_cache, int M,
+                                       int N, int K, int num_heads, int num_kv_heads, int head_dim, int page_size,
+                                       int sm_count, int* error, cudaStream_t stream) {
+  if (M <= 0) return 0;
+  if (M < kGemmBM || N < 1 || K < 8 || (K & 7) || (ldx & 7) || (ldq & 7) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15) ||
+      ((uintptr_t)q_out & 15) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15) || ((uintptr_t)bias & 15) ||
+      ((uintptr_t)trig & 15) || trig == nullptr || (head_dim != 64 && head_dim != 128) ||
+      N != (num_heads + 2 * num_kv_heads) * head_dim || (cache_row != nullptr && (k_cache == nullptr || v_cache == nullptr)))
+    return DISTIE_ERR_UNSUPPORTED;
+  if (sm_count < 1) sm_count = 148;
+  QkvEpilogue qkv;
+  qkv.bias = bias;
+  qkv.trig = trig;
+  qkv.cache_row = cache_row;
+  qkv.k_cache = (__nv_bfloat16*)k_cache;
+  qkv.v_cache = (__nv_bfloat16*)v_cache;
+  qkv.num_heads = num_heads;
+  qkv.num_kv_heads = num_kv_heads;
+  qkv.head_dim = head_dim;
+  qkv.page_size = page_size;
+  CUtensorMap map_a, map_b;
+  int status = make_map(&map_a, x, M, K, ldx, kGemmBM);
+  if (status != 0) return status;
+  if (M >= 2 * kGemmBM && sm_count >= 2) {
+    if ((status = make_map(&map_b, w, N, K, K, 128)) != 0) return status;
+    return launch_gemm_pair<256, 4, 1, GEMM_EPI_QKV>(map_a, map_b, q_out, ldq, M, N, K, 0, sm_count, error, stream, qkv);
+  }
+  if ((status = make_map(&map_b, w, N, K, K, 256)) != 0) return status;
+  return launch_gemm<256, 3, GEMM_EPI_QKV>(map_a, map_b, q_out, ldq, M, N, K, 0, sm_count, error, stream, qkv);
 }
 
 // ---- few rows of x: the weight-streaming orientation ------------------------------------------------------------

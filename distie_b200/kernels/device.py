@@ -275,6 +275,60 @@ class DeviceKernels(KernelSet):
         if q_out is not None:
             q_out.copy_(qkv[:, : num_heads * head_dim])
 
+    def qkv_rope_write(self, x, weight, bias, step, kv, rotary, num_heads, num_kv_heads, head_dim, q_out) -> None:
+        """Prompt portions of 128 rows and more: bias, rotation and the stores of q, k and v happen in the
+        epilogue of the tcgen05 product, which reads the step's angles and cache rows from a table made once
+        per step.  Everything else: the product's float32 slices into the rotation kernel."""
+        fused = (
+            self._tensor_core(x, weight) and head_dim in (64, 128)
+            and weight.shape[0] == (num_heads + 2 * num_kv_heads) * head_dim
+            and (rotary is None or (rotary.rotary_dim == head_dim and not rotary.interleaved))
+            and (bias is None or bias.dtype == torch.float32)
+            and (kv is None or kv.k.dtype == torch.bfloat16)
+            and q_out.dtype == torch.bfloat16 and q_out.stride(1) == 1 and q_out.stride(0) % 8 == 0
+            and not self._underfilled(x, weight)
+        )
+        if not fused:
+            return super().qkv_rope_write(x, weight, bias, step, kv, rotary, num_heads, num_kv_heads, head_dim, q_out)
+        trig, cache_row = self._rope_rows(step, kv, rotary, num_kv_heads, head_dim)
+        check(
+            function("distie_gemm_tcgen05_qkv")(
+                x.data_ptr(), x.stride(0), weight.data_ptr(), bias.data_ptr() if bias is not None else None,
+                trig.data_ptr(), cache_row.data_ptr() if cache_row is not None else None, q_out.data_ptr(),
+                q_out.stride(0), kv.k.data_ptr() if kv is not None else None, kv.v.data_ptr() if kv is not None else None,
+                x.shape[0], weight.shape[0], weight.shape[1], num_heads, num_kv_heads, head_dim,
+                kv.page_size if kv is not None else 1, self.sm_count, self.error_flag.data_ptr(), self._stream(),
+            ),
+            "gemm_tcgen05_qkv",
+        )
+        self._ran("gemm_tcgen05_qkv")
+
+    def _rope_rows(self, step, kv, rotary, num_kv_heads: int, head_dim: int):
+        """(trig [T, head_dim] float32, cache_row [T] int32 or None) of this step: made by the first layer that
+        asks and kept with the step for the others of its cache group and encoding."""
+        key = (
+            "rope_rows", head_dim, num_kv_heads, kv.block_table.data_ptr() if kv is not None else 0,
+            rotary.inv_freq.data_ptr() if rotary is not None else 0, float(rotary.factor) if rotary is not None else 1.0,
+        )
+        made = step.derived.get(key)
+        if made is None:
+            trig = torch.empty((step.num_tokens, head_dim), dtype=torch.float32, device=self.device)
+            cache_row = torch.empty(step.num_tokens, dtype=torch.int32, device=self.device) if kv is not None else None
+            check(
+                function("distie_rope_rows")(
+                    step.positions.data_ptr(), step.token_seq.data_ptr(), step.seq_seat.data_ptr(),
+                    kv.block_table.data_ptr() if kv is not None else None, kv.block_table.shape[-1] if kv is not None else 1,
+                    rotary.inv_freq.data_ptr() if rotary is not None else None,
+                    float(rotary.factor) if rotary is not None else 1.0, step.num_tokens, head_dim, num_kv_heads,
+                    kv.page_size if kv is not None else 1, kv.num_pages if kv is not None else 1, trig.data_ptr(),
+                    cache_row.data_ptr() if cache_row is not None else None, self.error_flag.data_ptr(), self._stream(),
+                ),
+                "rope_rows",
+            )
+            self._ran("rope_rows")
+            made = step.derived[key] = (trig, cache_row)
+        return made
+
     def plan_splits(self, tokens: int, num_heads: int, num_kv_heads: int, max_kv_len: int) -> int:
         group = num_heads // num_kv_heads
         chunks = (group + 7) // 8 if group > 8 else 1

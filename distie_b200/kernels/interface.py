@@ -19,7 +19,7 @@ Shapes (``T`` tokens of this step, ``B`` requests of this step):
 from __future__ import annotations
 
 from abc import ABC, abstractmethod
-from dataclasses import dataclass
+from dataclasses import dataclass, field
 
 import torch
 
@@ -39,6 +39,7 @@ class StepTensors:
     max_kv_len: int = 0  # bound on the keys any token sees; a captured step uses a fixed bound
     q_tiles: torch.Tensor | None = None  # [n, 2] int32: (first token, rows <= Q_TILE) of each tile of the
     num_q_tiles: int = 0                 # multi-token entries; a tile holds consecutive tokens of one request
+    derived: dict = field(default_factory=dict)  # what a kernel set made of this step once and its layers share
 
 
 @dataclass
@@ -111,6 +112,14 @@ class KernelSet(ABC):
         which case the slices are summed, ``bias`` is added and the rotated q is written to
         ``q_out [T, heads * head_dim]``.
         """
+
+    def qkv_rope_write(self, x, weight, bias, step: StepTensors, kv: KvSlot | None, rotary: RotaryTable | None,
+                       num_heads: int, num_kv_heads: int, head_dim: int, q_out) -> None:
+        """The q/k/v projection with what follows it: ``x @ weight.T + bias``, q and k rotated, q to
+        ``q_out`` and k and v into their pages (if kv).  The default is the two ops after one another;
+        a set may do it in the product's epilogue."""
+        slices = self.linear_split(x, weight)
+        self.rope_kv_write(slices, step, kv, rotary, num_heads, num_kv_heads, head_dim, bias=bias, q_out=q_out)
 
     @abstractmethod
     def attention(self, qkv, out, step: StepTensors, kv: KvSlot, num_heads: int, num_kv_heads: int,

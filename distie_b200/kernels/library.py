@@ -28,6 +28,7 @@ _SIGNATURES: dict[str, tuple[str, list]] = {
     "distie_rope_kv_write_split": (
         "base", [P, I, L, I, P, P, I, P, P, P, P, I, P, F, P, P, I, I, I, I, I, I, I, I, I, I, P, P]
     ),
+    "distie_rope_rows": ("base", [P, P, P, P, I, P, F, I, I, I, I, I, P, P, P, P]),
     "distie_bias_cast": ("base", [P, P, P, L, I, I, P]),
     "distie_attention_generic": ("base", [P, I, P, I, P, P, P, P, I, P, P, I, I, I, I, I, I, I, F, I, P, P]),
     "distie_attention_decode": ("base", [P, I, P, I, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, F, I, I, P, P]),
@@ -41,6 +42,7 @@ _SIGNATURES: dict[str, tuple[str, list]] = {
     "distie_attention_decode_mma_stages": ("bf16", [I, I, I, I]),
     "distie_attention_decode_mma": ("bf16", [P, I, P, I, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, F, I, P, P]),
     "distie_gemm_tcgen05": ("bf16", [P, I, P, P, I, I, I, I, I, I, I, P, P]),
+    "distie_gemm_tcgen05_qkv": ("bf16", [P, I, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, P, P]),
     "distie_gemm_tcgen05_skinny_splits": ("bf16", [I, I, I]),
     "distie_gemm_tcgen05_skinny": ("bf16", [P, I, P, P, P, I, I, I, I, I, I, I, P, P]),
 }

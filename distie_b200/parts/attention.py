@@ -113,11 +113,10 @@ class GqaAttention:
             self.position.apply(qkv, run.step, self.num_heads, self.num_kv_heads, self.head_dim)
             k.rope_kv_write(qkv, run.step, kv, None, self.num_heads, self.num_kv_heads, self.head_dim, q_out=q)
         else:
-            # The projection's float32 slices go straight into the kernel that adds the bias, rotates q
-            # and k and stores k and v in their pages; q comes back in a buffer of its own.
-            slices = k.linear_split(x, self.qkv.weight)
-            k.rope_kv_write(slices, run.step, kv, table, self.num_heads, self.num_kv_heads, self.head_dim,
-                            bias=self.qkv.bias, q_out=q)
+            # The projection, the bias, the rotation of q and k and the store of k and v in their pages
+            # as one op of the kernel set; q comes back in a buffer of its own.
+            k.qkv_rope_write(x, self.qkv.weight, self.qkv.bias, run.step, kv, table, self.num_heads,
+                             self.num_kv_heads, self.head_dim, q)
         mixed = torch.empty_like(q)
         k.attention(q, mixed, run.step, run.kv, self.num_heads, self.num_kv_heads, self.head_dim, self.window, self.scale)
         if self.out.bias is not None:

@@ -22,6 +22,11 @@ from ..kernels.interface import RotaryTable
 from .base import POSITION_ENCODINGS, BuildContext
 
 
+# Layers with the same parameters share one table (and one tensor of frequencies): what a kernel set derives
+# from a table and a step's positions is then made once per step, not once per layer.
+_TABLES: dict[tuple, RotaryTable] = {}
+
+
 @POSITION_ENCODINGS.register("rotary")
 class RotaryEncoding:
     """params: ``head_dim``, ``theta``, optional ``rotary_dim``, ``interleaved``, ``factor``."""
@@ -36,9 +41,13 @@ class RotaryEncoding:
         theta = float(spec.params["theta"])
         if rotary_dim % 2 or rotary_dim > head_dim:
             raise ValueError(f"rotary_dim {rotary_dim} must be even and at most head_dim {head_dim}")
-        inv_freq = 1.0 / (theta ** (torch.arange(0, rotary_dim, 2, dtype=torch.float32) / rotary_dim))
-        return cls(RotaryTable(inv_freq.to(ctx.device), rotary_dim, bool(spec.params.get("interleaved", False)),
-                               float(spec.params.get("factor", 1.0))))
+        key = (theta, rotary_dim, bool(spec.params.get("interleaved", False)), float(spec.params.get("factor", 1.0)),
+               str(ctx.device))
+        table = _TABLES.get(key)
+        if table is None:
+            inv_freq = 1.0 / (theta ** (torch.arange(0, rotary_dim, 2, dtype=torch.float32) / rotary_dim))
+            table = _TABLES[key] = RotaryTable(inv_freq.to(ctx.device), *key[1:4])
+        return cls(table)
 
     def rotary_table(self) -> RotaryTable | None:
         return self._table

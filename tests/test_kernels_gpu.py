@@ -290,6 +290,51 @@ def test_rope_kv_write(kernel_sets, dtype, heads, kv_heads, head_dim, rotary_dim
     assert torch.equal(again, qkv) and float(kv_none.k.float().abs().sum()) == 0
 
 
+@pytest.mark.parametrize(
+    "heads,kv_heads,head_dim,hidden,page,tokens,pasts,with_bias,with_table,factor",
+    [(12, 2, 128, 1536, 16, [200, 1, 90], [13, 70, 0], True, True, 1.0),      # pairs of CTAs, 2,048 columns
+     (3, 1, 64, 200, 8, [150], [5], True, True, 1.25),                         # one CTA; 320 columns: a tile's second half ends inside v
+     (5, 5, 64, 72, 4, [129, 2, 140], [0, 9, 30], False, True, 1.0),           # as many kv heads as heads, no bias, pages of 4
+     (2, 2, 128, 264, 32, [300], [31], True, False, 1.0),                      # no rotation: bias and stores only
+     (7, 1, 128, 96, 16, [128], [0], True, True, 0.8)],                        # exactly one tile of rows; 1,152 columns
+)
+def test_qkv_projection_with_fused_rotation_and_cache_write(kernel_sets, heads, kv_heads, head_dim, hidden, page, tokens,
+                                                            pasts, with_bias, with_table, factor):
+    """The q/k/v product whose epilogue adds the bias, rotates and stores (128 rows and more, bfloat16) against
+    the plain product followed by the plain rotation and cache write; also without a cache to write."""
+    from distie_b200.kernels.interface import RotaryTable
+
+    ks = kernel_sets[torch.bfloat16]
+    step = step_of(tokens, pasts, list(range(len(tokens))))
+    width = max(-(-(p + n) // page) for p, n in zip(pasts, tokens)) + 1
+    pages = len(tokens) * width
+    n = (heads + 2 * kv_heads) * head_dim
+    x = torch.randn(step.num_tokens, hidden, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(n, hidden, device="cuda") / hidden**0.5).to(torch.bfloat16)
+    bias = torch.randn(n, device="cuda") if with_bias else None
+    inv_freq = (1.0 / (10000.0 ** (torch.arange(0, head_dim, 2, dtype=torch.float32) / head_dim))).cuda()
+    rotary = RotaryTable(inv_freq, head_dim, False, factor) if with_table else None
+    product = torch.nn.functional.linear(x.float(), w.float()).unsqueeze(0)
+    for write in (True, False):
+        kv_a = make_cache(torch.bfloat16, pages, kv_heads, page, head_dim, len(tokens), width, fill=False)
+        kv_b = make_cache(torch.bfloat16, pages, kv_heads, page, head_dim, len(tokens), width, fill=False)
+        q_a = torch.full((step.num_tokens, heads * head_dim), float("nan"), dtype=torch.bfloat16, device="cuda")
+        q_b = torch.zeros_like(q_a)
+        before = ks.kernel_counts.get("gemm_tcgen05_qkv", 0)
+        step.derived.clear()
+        ks.qkv_rope_write(x, w, bias, step, kv_a if write else None, rotary, heads, kv_heads, head_dim, q_a)
+        ks.check_errors()
+        assert ks.kernel_counts.get("gemm_tcgen05_qkv", 0) == before + 1, "the fused kernel was meant to run"
+        ref.rope_kv_write(product, step, kv_b if write else None, rotary, heads, kv_heads, head_dim, bias=bias, q_out=q_b)
+        close(q_a, q_b, torch.bfloat16, "rotated q")
+        close(kv_a.k, kv_b.k, torch.bfloat16, "cached keys")
+        close(kv_a.v, kv_b.v, torch.bfloat16, "cached values")
+        assert (float(kv_a.k.float().abs().sum()) > 0) == write
+        # every slot that the reference left alone is still zero: nothing was written beside the tokens' slots
+        assert torch.equal(kv_a.k == 0, kv_b.k == 0) or float(((kv_a.k != 0) & (kv_b.k == 0)).sum()) == 0
+        assert float(((kv_a.v != 0) & (kv_b.v == 0)).sum()) == 0
+
+
 def filled_cache_for(dtype, kv_heads, head_dim, page, lengths, seed=1):
     """A cache whose tables cover `lengths[i]` tokens for seat i, pages in scrambled order."""
     pages_each = [-(-n // page) for n in lengths]

@@ -26,11 +26,12 @@ MODES = {
 }
 LENGTHS = [40, 67, 33, 300, 50, 36, 129, 64]
 # What a bfloat16 engine with head sizes 64 or 128 must have launched in each mode: prompts of 128 tokens
-# and more take the tensor-core product, shorter steps the weight-streaming one; portions take the
-# tensor-core prefill attention, steps of single tokens the tensor-core decode attention.
+# and more take the tensor-core product (q/k/v with the rotation and the cache write in its epilogue), shorter
+# steps the weight-streaming one; portions take the tensor-core prefill attention, steps of single tokens the
+# tensor-core decode attention.
 SERVING_KERNELS = {
-    "whole": {"attention_prefill_tcgen05", "gemm_tcgen05", "gemm_tcgen05_skinny"},
-    "tail": {"attention_prefill_tcgen05", "attention_decode_mma", "gemm_tcgen05", "gemm_tcgen05_skinny"},
+    "whole": {"attention_prefill_tcgen05", "gemm_tcgen05", "gemm_tcgen05_qkv", "gemm_tcgen05_skinny"},
+    "tail": {"attention_prefill_tcgen05", "attention_decode_mma", "gemm_tcgen05", "gemm_tcgen05_qkv", "gemm_tcgen05_skinny"},
     "portions": {"attention_prefill_tcgen05", "gemm_tcgen05_skinny"},
     "mixed": {"attention_prefill_tcgen05", "attention_decode_mma", "gemm_tcgen05_skinny"},
 }
