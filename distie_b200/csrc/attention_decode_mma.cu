@@ -378,14 +378,25 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_row_strid
     const int end = min(total, (split + 1) * share);
     for (int idx = split * share + threadIdx.x; idx < end; idx += kMmaDecodeWarps * 32) {
       const int hd = idx / D, e = idx % D;
+      // All loads from the other CTAs' shared memory are issued before the first is used: one trip through
+      // the cluster's network instead of one per split.
+      float ms[kMmaDecodeClusterSplits], ls[kMmaDecodeClusterSplits], os[kMmaDecodeClusterSplits];
+#pragma unroll
+      for (int s = 0; s < kMmaDecodeClusterSplits; ++s) {
+        const bool there = s < num_splits;
+        ms[s] = there ? cluster_load(&cl_m[hd], s) : -INFINITY;
+        ls[s] = there ? cluster_load(&cl_l[hd], s) : 0.f;
+        os[s] = there ? cluster_load(&cl_o[hd][e], s) : 0.f;
+      }
       float m_all = -INFINITY;
-      for (int s = 0; s < num_splits; ++s) m_all = fmaxf(m_all, cluster_load(&cl_m[hd], s));
+#pragma unroll
+      for (int s = 0; s < kMmaDecodeClusterSplits; ++s) m_all = fmaxf(m_all, ms[s]);
       float l_all = 0.f, acc = 0.f;
-      for (int s = 0; s < num_splits; ++s) {
-        const float ms = cluster_load(&cl_m[hd], s);
-        const float weight = ms == -INFINITY ? 0.f : exp2f(ms - m_all);
-        l_all += cluster_load(&cl_l[hd], s) * weight;
-        acc += cluster_load(&cl_o[hd][e], s) * weight;
+#pragma unroll
+      for (int s = 0; s < kMmaDecodeClusterSplits; ++s) {
+        const float weight = ms[s] == -INFINITY ? 0.f : exp2f(ms[s] - m_all);
+        l_all += ls[s] * weight;
+        acc += os[s] * weight;
       }
       out[(size_t)t * out_row_stride + (size_t)(head0 + hd) * D + e] = __float2bfloat16_rn(l_all > 0.f ? acc / l_all : 0.f);
     }

@@ -76,7 +76,17 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, int vocab,
     cluster_barrier();
     best = -INFINITY;
     at = 0x7fffffff;
-    for (uint32_t r = 0; r < (uint32_t)ctas; ++r) better(best, at, cluster_load(&cl_best, r), cluster_load_int(&cl_at, r));
+    // (all loads from the other CTAs are issued before the first is used: one trip, not one per CTA)
+    float their_best[kSampleCluster];
+    int their_at[kSampleCluster];
+#pragma unroll
+    for (int r = 0; r < kSampleCluster; ++r) {
+      their_best[r] = r < ctas ? cluster_load(&cl_best, r) : -INFINITY;
+      their_at[r] = r < ctas ? cluster_load_int(&cl_at, r) : 0x7fffffff;
+    }
+#pragma unroll
+    for (int r = 0; r < kSampleCluster; ++r)
+      if (r < ctas) better(best, at, their_best[r], their_at[r]);
   } else if (threadIdx.x == 0) {
     cl_pick = -1;
   }
@@ -108,9 +118,13 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, int vocab,
     if (threadIdx.x == 0) cl_total = total;
     cluster_barrier();
     float all = 0.f, ahead = 0.f;
-    for (uint32_t r = 0; r < (uint32_t)ctas; ++r) {
-      if (r == rank) ahead = all;
-      all += cluster_load(&cl_total, r);
+    float their_total[kSampleCluster];
+#pragma unroll
+    for (int r = 0; r < kSampleCluster; ++r) their_total[r] = r < ctas ? cluster_load(&cl_total, r) : 0.f;
+#pragma unroll
+    for (int r = 0; r < kSampleCluster; ++r) {
+      if ((uint32_t)r == rank) ahead = all;
+      if (r < ctas) all += their_total[r];
     }
     before += ahead;
     total = all;
