@@ -70,6 +70,7 @@ struct AttnShared {
   uint64_t p_full[2][2];  // [group][S buffer]
   uint64_t pv_done[2];    // [group]
   uint64_t merge_ready;
+  uint64_t store_ready;   // the eight softmax warps have put their part of the output tile into shared memory
   float row_max[2][kAttnRows], row_sum[2][kAttnRows];  // [group][row]: what the groups exchange at the end
   uint32_t tmem_base;
   uint32_t failed;
@@ -84,7 +85,8 @@ __device__ __forceinline__ float exp2_approx(float x) {
 template <int D>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                                 const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
+                                 const __grid_constant__ CUtensorMap map_v,
+                                 const __grid_constant__ CUtensorMap map_out, __nv_bfloat16* __restrict__ out,
                                  int out_row_stride, const int* __restrict__ q_tiles,
                                  const int* __restrict__ positions, const int* __restrict__ token_seq,
                                  const int* __restrict__ seq_seat, const int* __restrict__ block_table,
@@ -117,6 +119,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       mbar_init(&sm.pv_done[b], 1);
     }
     mbar_init(&sm.merge_ready, kAttnSoftmaxWarps);
+    mbar_init(&sm.store_ready, kAttnSoftmaxWarps);
     sm.failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -131,8 +134,9 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   const uint32_t tmem = sm.tmem_base;
 
   grid_dependency_release();
-  grid_dependency_wait();  // q and the newest keys and values come from the kernel before this one
-
+  // The tile's place in the step (tiles, positions, seats and block tables are inputs of the step, written by
+  // no kernel) is looked up before the wait for the kernel that makes q and the newest keys and values: four
+  // loads that depend on one another, which then cost the CTAs of the first wave nothing.
   // Tiles late in a request see the most keys and take longest: they start first, for every head
   // (blockIdx.x, the heads, runs fastest in the order in which CTAs are handed out).
   const int tile = gridDim.y - 1 - blockIdx.y, head = blockIdx.x;
@@ -145,31 +149,33 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   const int block_first = first_key / kAttnKeys;
   const int blocks = last_pos / kAttnKeys - block_first + 1;
   const int page_size = 1 << page_shift;
+  const int* table = block_table + (size_t)seat * table_width;
+  const int pages_per_block = kAttnKeys >> page_shift;  // at most 16
+  auto pages_of = [&](int j) {  // pages of block j that hold keys the tile needs
+    return min(pages_per_block, ((last_pos - (block_first + j) * kAttnKeys) >> page_shift) + 1);
+  };
+  auto read_table = [&](int j) {  // this lane's page of block j, -1 beyond the block's pages
+    if (j >= blocks) return -1;
+    const int column = (((block_first + j) * kAttnKeys) >> page_shift) + lane;
+    return (lane < pages_of(j) && column < table_width) ? __ldg(table + column) : -1;
+  };
+  const bool producer = warp == 0 || warp == kAttnVProducerWarp;
+  int page_ahead = producer ? read_table(0) : -1;
+  grid_dependency_wait();  // q and the newest keys and values come from the kernel before this one
 
-  if (warp == 0 || warp == kAttnVProducerWarp) {
+  if (producer) {
     // ---- producers: warp 0 fetches Q and K, the last warp V; lane pg takes page pg of a block -----------------
     const bool for_k = warp == 0;
     if (for_k && lane == 0) {
       mbar_expect_tx(&sm.q_full, kAttnRows * D * 2);
       for (int h = 0; h < HALVES; ++h) tma_load_2d(sm.q + h * kAttnHalf, &map_q, &sm.q_full, head * D + h * 64, t0);
     }
-    const int* table = block_table + (size_t)seat * table_width;
-    const int pages_per_block = kAttnKeys >> page_shift;  // at most 16
     const int stages = for_k ? kAttnKStages : kAttnVStages;
     const CUtensorMap* map = for_k ? &map_k : &map_v;
     uint64_t* full = for_k ? sm.k_full : sm.v_full;
     uint64_t* empty = for_k ? sm.k_empty : sm.v_empty;
-    auto pages_of = [&](int j) {  // pages of block j that hold keys the tile needs
-      return min(pages_per_block, ((last_pos - (block_first + j) * kAttnKeys) >> page_shift) + 1);
-    };
-    auto read_table = [&](int j) {  // this lane's page of block j, -1 beyond the block's pages
-      if (j >= blocks) return -1;
-      const int column = (((block_first + j) * kAttnKeys) >> page_shift) + lane;
-      return (lane < pages_of(j) && column < table_width) ? __ldg(table + column) : -1;
-    };
     int issued = 0;
     bool ok = true;
-    int page_ahead = read_table(0);
     for (int j = 0; j < blocks && ok; ++j) {
       const int s = j % stages, use = j / stages;
       const int page = page_ahead;
@@ -363,8 +369,13 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       const float l_all = sm.row_sum[0][r] * w0 + sm.row_sum[1][r] * w1;
       const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
       const float f0 = w0 * inv, f1 = w1 * inv;
-      // Group g writes columns g * D / 2 ... of the row, from both accumulators.
+      // Group g writes columns g * D / 2 ... of the row, from both accumulators.  A whole tile of 128 rows goes
+      // into the shared memory that held Q (all products with Q are done), in the layout of a tile copy, and
+      // leaves as one: 128 rows of whole lines, where the threads' own stores are 16 bytes of 32 different
+      // rows per instruction and take a microsecond and a half to drain.  A partial tile (the end of a
+      // request) is stored by the threads, row by row.
       constexpr int SIDE_DIMS = D / 2;
+      const bool whole = rows == kAttnRows;  // (the same for every thread of the CTA)
       __nv_bfloat16* dst = out + (size_t)(t0 + r) * out_row_stride + (size_t)head * D + g * SIDE_DIMS;
 #pragma unroll
       for (int c0 = 0; c0 < SIDE_DIMS; c0 += 32) {
@@ -372,14 +383,39 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         tmem_load_32(lane_base + O_COL + g * SIDE_DIMS + c0, a);
         tmem_load_32(lane_base + O_COL + D + g * SIDE_DIMS + c0, b);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (r < rows) {
+        if (whole || r < rows) {
 #pragma unroll
           for (int i = 0; i < 32; i += 8) {
             float y[8];
 #pragma unroll
             for (int e = 0; e < 8; ++e) y[e] = __uint_as_float(a[i + e]) * f0 + __uint_as_float(b[i + e]) * f1;
-            store8(dst + c0 + i, y);
+            if (whole) {
+              const int dim = g * SIDE_DIMS + c0 + i;  // 8 dims = one 16-byte piece of the row's 128-byte line
+              const uint32_t at = smem_u32(sm.q) + (dim >> 6) * kAttnHalf + r * 128 + ((((dim & 63) >> 3) ^ (r & 7)) << 4);
+              uint32_t w[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const __nv_bfloat162 pair = __floats2bfloat162_rn(y[2 * e], y[2 * e + 1]);
+                w[e] = *reinterpret_cast<const uint32_t*>(&pair);
+              }
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(at), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
+            } else {
+              store8(dst + c0 + i, y);
+            }
           }
+        }
+      }
+      if (whole) {
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the stores above, before the copy reads them
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sm.store_ready);
+        if (warp == 2 && wait_all(&sm.store_ready, 0) && lane == 0) {
+#pragma unroll
+          for (int h = 0; h < HALVES; ++h)
+            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(&map_out),
+                         "r"(head * D + h * 64), "r"(t0), "r"(smem_u32(sm.q + h * kAttnHalf)) : "memory");
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // shared memory is read before the CTA may end
         }
       }
     } else {
@@ -396,7 +432,8 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
 }
 
 template <int D>
-static int launch_attention_tc(const CUtensorMap& map_q, const CUtensorMap& map_k, const CUtensorMap& map_v, void* out,
+static int launch_attention_tc(const CUtensorMap& map_q, const CUtensorMap& map_k, const CUtensorMap& map_v,
+                               const CUtensorMap& map_out, void* out,
                                int out_row_stride, const int* q_tiles, int num_tiles, const int* positions,
                                const int* token_seq, const int* seq_seat, const int* block_table, int table_width,
                                int num_heads, int num_kv_heads, int page_shift, int num_pages, int window,
@@ -411,7 +448,7 @@ static int launch_attention_tc(const CUtensorMap& map_q, const CUtensorMap& map_
   }
   const cudaError_t err = launch_dependent_family(
       32, attention_prefill_tcgen05_kernel<D>, dim3(num_heads, num_tiles), dim3(kAttnThreads), shared, stream, map_q,
-      map_k, map_v, (__nv_bfloat16*)out, out_row_stride, q_tiles, positions, token_seq, seq_seat, block_table,
+      map_k, map_v, map_out, (__nv_bfloat16*)out, out_row_stride, q_tiles, positions, token_seq, seq_seat, block_table,
       table_width, num_heads / num_kv_heads, num_kv_heads, page_shift, num_pages, window, scale_log2, error);
   return err == cudaSuccess ? 0 : (int)err;
 }
@@ -441,19 +478,20 @@ extern "C" int distie_attention_prefill_tcgen05(const void* q, int q_row_stride,
     return DISTIE_ERR_UNSUPPORTED;
   int page_shift = 0;
   while ((1 << page_shift) < page_size) ++page_shift;
-  CUtensorMap map_q, map_k, map_v;
+  CUtensorMap map_q, map_k, map_v, map_out;
   int status = make_map(&map_q, q, tokens, num_heads * head_dim, q_row_stride, kAttnRows);
   if (status != 0) return status;
+  if ((status = make_map(&map_out, out, tokens, num_heads * head_dim, out_row_stride, kAttnRows)) != 0) return status;
   const long long cache_rows = (long long)num_pages * num_kv_heads * page_size;
   if (cache_rows > 0x7fffffffLL) return DISTIE_ERR_UNSUPPORTED;
   if ((status = make_map(&map_k, k_cache, (int)cache_rows, head_dim, head_dim, page_size)) != 0) return status;
   if ((status = make_map(&map_v, v_cache, (int)cache_rows, head_dim, head_dim, page_size)) != 0) return status;
   const float scale_log2 = scale * 1.4426950408889634f;
   if (head_dim == 64)
-    return launch_attention_tc<64>(map_q, map_k, map_v, out, out_row_stride, q_tiles, num_tiles, positions, token_seq,
+    return launch_attention_tc<64>(map_q, map_k, map_v, map_out, out, out_row_stride, q_tiles, num_tiles, positions, token_seq,
                                    seq_seat, block_table, table_width, num_heads, num_kv_heads, page_shift, num_pages,
                                    window, scale_log2, error, stream);
-  return launch_attention_tc<128>(map_q, map_k, map_v, out, out_row_stride, q_tiles, num_tiles, positions, token_seq,
+  return launch_attention_tc<128>(map_q, map_k, map_v, map_out, out, out_row_stride, q_tiles, num_tiles, positions, token_seq,
                                   seq_seat, block_table, table_width, num_heads, num_kv_heads, page_shift, num_pages,
                                   window, scale_log2, error, stream);
 }
