@@ -144,93 +144,31 @@ __global__ void __launch_bounds__(512) add_rmsnorm_vec_kernel(const DT* __restri
   }
 }
 
-// Many rows (prompt portions): a warp per row, the whole row in registers (VEC pieces of 4 per lane),
-// the sum of squares by shuffles.  No block-wide barrier, and every lane has 2 * VEC loads in flight,
-// which is what a kernel that only moves memory needs.  hidden <= 128 * VEC.
-template <typename T, typename DT, int VEC>
-__global__ void __launch_bounds__(256) add_rmsnorm_rows_kernel(const DT* __restrict__ delta, int splits, size_t split_stride,
-                                                               float* __restrict__ residual,
-                                                               const float* __restrict__ weight, T* __restrict__ out,
-                                                               const int* __restrict__ rows_index, int rows, int hidden,
-                                                               float eps) {
-  const int lane = threadIdx.x & 31;
-  const int out_row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  grid_dependency_release();
-  grid_dependency_wait();
-  if (out_row >= rows) return;
-  const int row = rows_index ? rows_index[out_row] : out_row;
-  float* res = residual + (size_t)row * hidden;
-  const DT* del = delta ? delta + (size_t)row * hidden : nullptr;
-  const bool write_back = (delta != nullptr) && (rows_index == nullptr);
-  const int chunks = hidden >> 2;
-  float4 v[VEC];
-#pragma unroll
-  for (int i = 0; i < VEC; ++i) {
-    const int ch = lane + 32 * i;
-    v[i] = ch < chunks ? load4(res + 4 * ch) : make_float4(0.f, 0.f, 0.f, 0.f);
-  }
-  if (del) {
-    for (int sp = 0; sp < splits; ++sp) {
-      float4 d[VEC];
-#pragma unroll
-      for (int i = 0; i < VEC; ++i) {
-        const int ch = lane + 32 * i;
-        d[i] = ch < chunks ? load4_cg(del + sp * split_stride + 4 * ch) : make_float4(0.f, 0.f, 0.f, 0.f);
-      }
-#pragma unroll
-      for (int i = 0; i < VEC; ++i) { v[i].x += d[i].x; v[i].y += d[i].y; v[i].z += d[i].z; v[i].w += d[i].w; }
-    }
-  }
-  float sumsq = 0.f;
-#pragma unroll
-  for (int i = 0; i < VEC; ++i) {
-    const int ch = lane + 32 * i;
-    if (write_back && ch < chunks) store4(res + 4 * ch, v[i]);
-    sumsq += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
-  }
-  const float rstd = rsqrtf(warp_sum(sumsq) / (float)hidden + eps);
-  T* dst = out + (size_t)out_row * hidden;
-#pragma unroll
-  for (int i = 0; i < VEC; ++i) {
-    const int ch = lane + 32 * i;
-    if (ch >= chunks) continue;
-    const float4 w = load4(weight + 4 * ch);
-    float4 y;
-    y.x = w.x * to_float(from_float<T>(v[i].x * rstd));
-    y.y = w.y * to_float(from_float<T>(v[i].y * rstd));
-    y.z = w.z * to_float(from_float<T>(v[i].z * rstd));
-    y.w = w.w * to_float(from_float<T>(v[i].w * rstd));
-    store4(dst + 4 * ch, y);
-  }
-}
-
-constexpr int kNormRowsThreshold = 1024;  // from this many rows on, a warp per row (fewer rows: a CTA per row)
-
-// Threads and elements per thread for a row of `hidden` (a multiple of 4, at most 8192): as few
-// elements per thread as 512 threads allow, so that a short batch still has many loads in flight.
+// Threads and elements per thread for a row of `hidden` (a multiple of 4, at most 8192).  A CTA per row in
+// every case.  Many rows (prompt portions) want small CTAs, at most 256 threads with four or eight pieces of
+// 4 per thread: many CTAs fit an SM and each thread has eight or sixteen loads in flight (2,048 rows of
+// 3,584: 11.3 us against 18.6 us with two pieces and against 20.2 us with a warp per row and the row in
+// registers, a form that was removed; the same bytes take a plain copy 8.5 us).  Few rows (decoding) want
+// as many threads per row as 512 allow: alone, the kernel is as fast with four pieces per thread there too,
+// but a decode step of 8 rows was 15 % longer with them (1.42 against 1.23 ms), so the rule for few rows
+// stays as the whole step measured it.
 template <typename T, typename DT>
 static cudaError_t launch_add_rmsnorm_vec(const DT* delta, int splits, size_t split_stride, float* residual,
                                           const float* weight, T* out, const int* rows_index, int rows, int hidden,
                                           float eps, cudaStream_t stream) {
   const int chunks = hidden >> 2;
-  if (rows >= kNormRowsThreshold && hidden <= 128 * 32) {
-    const dim3 grid((rows + 3) / 4), block(128);
-    if (hidden <= 128 * 8)
-      return launch_dependent_family(2, add_rmsnorm_rows_kernel<T, DT, 8>, grid, block, 0, stream, delta, splits,
-                                     split_stride, residual, weight, out, rows_index, rows, hidden, eps);
-    if (hidden <= 128 * 16)
-      return launch_dependent_family(2, add_rmsnorm_rows_kernel<T, DT, 16>, grid, block, 0, stream, delta, splits,
-                                     split_stride, residual, weight, out, rows_index, rows, hidden, eps);
-    return launch_dependent_family(2, add_rmsnorm_rows_kernel<T, DT, 32>, grid, block, 0, stream, delta, splits,
-                                   split_stride, residual, weight, out, rows_index, rows, hidden, eps);
-  }
-  const int vpt = chunks <= 512 ? 1 : (chunks <= 1024 ? 2 : 4);
+  int vpt;
+  if (rows >= 256) vpt = chunks <= 1024 ? 4 : 8;
+  else vpt = chunks <= 512 ? 1 : (chunks <= 1024 ? 2 : 4);
   const int threads = (((chunks + vpt - 1) / vpt) + 31) & ~31;
   if (vpt == 1)
     return launch_dependent_family(2, add_rmsnorm_vec_kernel<T, DT, 1>, dim3(rows), dim3(threads), 0, stream, delta, splits,
                                    split_stride, residual, weight, out, rows_index, hidden, eps);
   if (vpt == 2)
     return launch_dependent_family(2, add_rmsnorm_vec_kernel<T, DT, 2>, dim3(rows), dim3(threads), 0, stream, delta, splits,
+                                   split_stride, residual, weight, out, rows_index, hidden, eps);
+  if (vpt == 8)
+    return launch_dependent_family(2, add_rmsnorm_vec_kernel<T, DT, 8>, dim3(rows), dim3(threads), 0, stream, delta, splits,
                                    split_stride, residual, weight, out, rows_index, hidden, eps);
   return launch_dependent_family(2, add_rmsnorm_vec_kernel<T, DT, 4>, dim3(rows), dim3(threads), 0, stream, delta, splits,
                                  split_stride, residual, weight, out, rows_index, hidden, eps);
