@@ -81,9 +81,18 @@ __device__ __forceinline__ void store_row_f32(const float (&v)[32], float* __res
 // (tensor-memory address `lane_base`, first output column `n0`) to global memory as bfloat16, float32, or
 // silu(gate) * up with the gate in columns [0, BN / 2) and the up values in [BN / 2, BN).
 // Two warps share a quarter of the rows: `part` (0 or 1) selects this warp's half of the output columns.
+//
+// float32 results leave through `stage`, 4 KB of shared memory of the warp's own: a thread holds 32 columns of
+// one row, and stored from there an instruction would touch 32 rows with 32 bytes each, which the memory
+// system takes four times as long to absorb as whole lines.  So the 32 x 32 piece goes into shared memory
+// (16-byte pieces, piece ^ (row & 7): no bank conflicts either way) and comes back with eight lanes to a
+// row: an instruction then writes four whole 128-byte lines.
+constexpr int kEpilogueStageBytes = 32 * 32 * 4;  // per epilogue warp
+
 template <int BN, int EPI>
 __device__ __forceinline__ void store_accumulator(uint32_t lane_base, int row0, int lane, int n0,
-                                                  void* __restrict__ out, int ldo, int M, int N, int inter, int part) {
+                                                  void* __restrict__ out, int ldo, int M, int N, int inter, int part,
+                                                  unsigned char* stage) {
   const int rows_valid = M - row0;
   if (EPI == GEMM_EPI_SWIGLU) {
     constexpr int HALF = BN / 2;
@@ -113,9 +122,26 @@ __device__ __forceinline__ void store_accumulator(uint32_t lane_base, int row0, 
       const int col = n0 + c0;
       if (rows_valid > 0 && col < N) {
         if (EPI == GEMM_EPI_F32) {
-          // (uniform over the warp: whole rows of 32 columns, rows 32 bytes apart in alignment)
-          if (col + 32 <= N && ((ldo | col) & 7) == 0 && ((uintptr_t)out & 31) == 0) {
-            if (lane < rows_valid) store_row_f32(v, (float*)out + (size_t)(row0 + lane) * ldo + col);
+          // (uniform over the warp: whole rows of 32 columns, rows 16 bytes apart in alignment)
+          if (col + 32 <= N && ((ldo | col) & 3) == 0 && ((uintptr_t)out & 15) == 0) {
+            const uint32_t base = smem_u32(stage);
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(base + lane * 128 + ((j ^ (lane & 7)) << 4)),
+                           "r"(acc[4 * j]), "r"(acc[4 * j + 1]), "r"(acc[4 * j + 2]), "r"(acc[4 * j + 3]) : "memory");
+            __syncwarp();
+            const int piece = lane & 7;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int row = 4 * i + (lane >> 3);
+              uint32_t w0, w1, w2, w3;
+              asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(w0), "=r"(w1), "=r"(w2), "=r"(w3)
+                           : "r"(base + row * 128 + ((piece ^ (row & 7)) << 4)) : "memory");
+              if (row < rows_valid)
+                asm volatile("st.global.v4.b32 [%0], {%1, %2, %3, %4};" ::"l"((float*)out + (size_t)(row0 + row) * ldo + col + 4 * piece),
+                             "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
+            }
+            __syncwarp();  // before the next piece overwrites the stage
           } else if (lane < rows_valid) {
             float* dst = (float*)out + (size_t)(row0 + lane) * ldo + col;
 #pragma unroll
@@ -280,29 +306,41 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem = sm.tmem_base;
   // Launched as a dependent kernel: everything up to here overlaps the end of the kernel before this
-  // one; its results (the activations) are read, and anything is written, only after this wait.
+  // one.  Its results (the activations) are read, and anything is written, only after the wait; the
+  // weights are written by no kernel, so the producer has the first ring of weight tiles on its way
+  // before it waits.
   grid_dependency_release();
-  grid_dependency_wait();
 
   if (warp == 0) {
     // ---- producer ----------------------------------------------------------------------------------------
     if (lane == 0) {
       uint32_t it = 0;  // stages filled so far, over all tiles
       bool ok = true;
+      auto load_w = [&](int s, int kb, int n0) {
+        if (EPI == GEMM_EPI_SWIGLU) {
+          tma_load_2d(sm.b[s], &map_b, &sm.full[s], kb * kGemmBK, n0);
+          tma_load_2d(sm.b[s] + (BN / 2) * kGemmBK * 2, &map_b, &sm.full[s], kb * kGemmBK, inter + n0);
+        } else {
+          tma_load_2d(sm.b[s], &map_b, &sm.full[s], kb * kGemmBK, n0);
+        }
+      };
+      const int early = blockIdx.x < num_tiles ? min(k_blocks, STAGES) : 0;  // of this CTA's first tile
+      for (int kb = 0; kb < early; ++kb) {
+        mbar_expect_tx(&sm.full[kb], STAGE_BYTES);
+        load_w(kb, kb, (blockIdx.x / m_tiles) * PER_TILE);
+      }
+      grid_dependency_wait();
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         const int m0 = (tile % m_tiles) * kGemmBM;
         const int n0 = (tile / m_tiles) * PER_TILE;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % STAGES;
-          if (!mbar_wait(&sm.empty[s], ((it / STAGES) & 1) ^ 1)) { atomicExch(&sm.failed, 1u); ok = false; break; }
-          mbar_expect_tx(&sm.full[s], STAGE_BYTES);
-          tma_load_2d(sm.a[s], &map_a, &sm.full[s], kb * kGemmBK, m0);
-          if (EPI == GEMM_EPI_SWIGLU) {
-            tma_load_2d(sm.b[s], &map_b, &sm.full[s], kb * kGemmBK, n0);
-            tma_load_2d(sm.b[s] + (BN / 2) * kGemmBK * 2, &map_b, &sm.full[s], kb * kGemmBK, inter + n0);
-          } else {
-            tma_load_2d(sm.b[s], &map_b, &sm.full[s], kb * kGemmBK, n0);
+          if (it >= (uint32_t)early) {
+            if (!mbar_wait(&sm.empty[s], ((it / STAGES) & 1) ^ 1)) { atomicExch(&sm.failed, 1u); ok = false; break; }
+            mbar_expect_tx(&sm.full[s], STAGE_BYTES);
+            load_w(s, kb, n0);
           }
+          tma_load_2d(sm.a[s], &map_a, &sm.full[s], kb * kGemmBK, m0);
         }
       }
       if (!ok) {
@@ -338,9 +376,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
   } else {
     // ---- epilogue: warps w and w + 4 share rows 32 * (w % 4) .. + 31 and take half of the columns each ------
+    grid_dependency_wait();  // nothing is written before the earlier kernels are done
     const int quadrant = warp & 3, part = (warp - 2) >> 2;
-    float* trig_stage = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(&sm) + ((sizeof(sm) + 15) & ~size_t(15))) +
-                        (warp - 2) * kQkvStageFloats;  // (behind the stages; only the q/k/v epilogue asks for the room)
+    unsigned char* behind = reinterpret_cast<unsigned char*>(&sm) + ((sizeof(sm) + 15) & ~size_t(15));  // behind the stages:
+    float* trig_stage = reinterpret_cast<float*>(behind) + (warp - 2) * kQkvStageFloats;  // asked for by the q/k/v epilogue,
+    unsigned char* epilogue_stage = behind + (warp - 2) * kEpilogueStageBytes;            // by the float32 epilogue
     uint32_t round = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++round) {
       const uint32_t buffer = round & 1;
@@ -357,7 +397,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         if (qkv.head_dim == 128) store_qkv_rope<128>(lane_base, m0 + quadrant * 32, lane, n0, part, (__nv_bfloat16*)out, ldo, M, N, qkv, trig_stage);
         else store_qkv_rope<64>(lane_base, m0 + quadrant * 32, lane, n0, part, (__nv_bfloat16*)out, ldo, M, N, qkv, trig_stage);
       } else {
-        store_accumulator<BN, EPI>(lane_base, m0 + quadrant * 32, lane, n0, out, ldo, M, N, inter, part);
+        store_accumulator<BN, EPI>(lane_base, m0 + quadrant * 32, lane, n0, out, ldo, M, N, inter, part, epilogue_stage);
       }
       // This warp has read its part of the accumulator: hand the buffer back to the MMA issuer.
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -438,28 +478,45 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   cluster_barrier();  // both CTAs' barriers are initialised and tensor memory is allocated
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem = sm.tmem_base;
-  grid_dependency_release();
-  grid_dependency_wait();
+  grid_dependency_release();  // (the wait: by the producers behind their first weight tiles, by the epilogue warps)
 
   if (warp == 0) {
     // ---- producer (both CTAs) -------------------------------------------------------------------------------
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
+      // Rows of W this CTA stages: with SwiGLU the first CTA takes the gate rows, the second the up rows.
+      auto rows_of_w = [&](int tile) {
+        const int n_tile = (tile / m_tiles) * PER_TILE;
+        return EPI == GEMM_EPI_SWIGLU ? (rank == 0 ? n_tile : inter + n_tile) : n_tile + (int)rank * (BN / 2);
+      };
+      // The weights are written by no kernel: the first ring of them is on its way before the wait for
+      // the kernel that makes the activations.  (A copy of the second CTA may land on the first CTA's
+      // barrier before that one has announced the bytes; the phase cannot end before it has.)
+      const int early = pair < num_tiles ? min(k_blocks, STAGES) : 0;
+      for (int kb = 0; kb < early; ++kb) {
+        if (rank == 0) mbar_expect_tx(&sm.full[kb], STAGE_BYTES_PAIR);
+        const uint32_t full_addr = cluster_address(&sm.full[kb], 0);
+#pragma unroll
+        for (int box = 0; box < KB; ++box)
+          tma_load_2d_pair(sm.b[kb][box], &map_b, full_addr, kb * STAGE_K + box * kGemmBK, rows_of_w(pair));
+      }
+      grid_dependency_wait();
       for (int tile = pair; tile < num_tiles && ok; tile += pairs) {
         const int m0 = (tile % m_tiles) * 2 * kGemmBM + (int)rank * kGemmBM;
-        const int n_tile = (tile / m_tiles) * PER_TILE;
-        // Rows of W this CTA stages: with SwiGLU the first CTA takes the gate rows, the second the up rows.
-        const int w0 = EPI == GEMM_EPI_SWIGLU ? (rank == 0 ? n_tile : inter + n_tile) : n_tile + (int)rank * (BN / 2);
+        const int w0 = rows_of_w(tile);
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % STAGES;
-          if (!mbar_wait_unless(&sm.empty[s], ((it / STAGES) & 1) ^ 1, &sm.failed)) { ok = false; break; }
-          if (rank == 0) mbar_expect_tx(&sm.full[s], STAGE_BYTES_PAIR);
+          const bool ahead = it < (uint32_t)early;  // this stage's weights are under way already
+          if (!ahead) {
+            if (!mbar_wait_unless(&sm.empty[s], ((it / STAGES) & 1) ^ 1, &sm.failed)) { ok = false; break; }
+            if (rank == 0) mbar_expect_tx(&sm.full[s], STAGE_BYTES_PAIR);
+          }
           const uint32_t full_addr = cluster_address(&sm.full[s], 0);
 #pragma unroll
           for (int box = 0; box < KB; ++box) {  // a box past K is filled with zeros and still counted
             tma_load_2d_pair(sm.a[s][box], &map_a, full_addr, kb * STAGE_K + box * kGemmBK, m0);
-            tma_load_2d_pair(sm.b[s][box], &map_b, full_addr, kb * STAGE_K + box * kGemmBK, w0);
+            if (!ahead) tma_load_2d_pair(sm.b[s][box], &map_b, full_addr, kb * STAGE_K + box * kGemmBK, w0);
           }
         }
       }
@@ -502,9 +559,11 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     }
   } else {
     // ---- epilogue (both CTAs, each its own 128 rows; two warps per quarter of the rows, half the columns each) --
+    grid_dependency_wait();  // nothing is written before the earlier kernels are done
     const int quadrant = warp & 3, part = (warp - 2) >> 2;
-    float* trig_stage = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(&sm) + ((sizeof(sm) + 15) & ~size_t(15))) +
-                        (warp - 2) * kQkvStageFloats;  // (behind the stages; only the q/k/v epilogue asks for the room)
+    unsigned char* behind = reinterpret_cast<unsigned char*>(&sm) + ((sizeof(sm) + 15) & ~size_t(15));  // behind the stages:
+    float* trig_stage = reinterpret_cast<float*>(behind) + (warp - 2) * kQkvStageFloats;  // asked for by the q/k/v epilogue,
+    unsigned char* epilogue_stage = behind + (warp - 2) * kEpilogueStageBytes;            // by the float32 epilogue
     uint32_t round = 0;
     for (int tile = pair; tile < num_tiles; tile += pairs, ++round) {
       const uint32_t buffer = round & 1;
@@ -522,7 +581,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         if (qkv.head_dim == 128) store_qkv_rope<128>(lane_base, m0 + quadrant * 32, lane, n0, part, (__nv_bfloat16*)out, ldo, M, N, qkv, trig_stage);
         else store_qkv_rope<64>(lane_base, m0 + quadrant * 32, lane, n0, part, (__nv_bfloat16*)out, ldo, M, N, qkv, trig_stage);
       } else {
-        store_accumulator<BN, EPI>(lane_base, m0 + quadrant * 32, lane, n0, out, ldo, M, N, inter, part);
+        store_accumulator<BN, EPI>(lane_base, m0 + quadrant * 32, lane, n0, out, ldo, M, N, inter, part, epilogue_stage);
       }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
@@ -738,7 +797,8 @@ gemm_tcgen05_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
 template <int BN, int STAGES, int EPI>
 static int launch_gemm(const CUtensorMap& map_a, const CUtensorMap& map_b, void* out, int ldo, int M, int N, int K,
                        int inter, int sm_count, int* error, cudaStream_t stream, const QkvEpilogue& qkv = QkvEpilogue()) {
-  const size_t shared = sizeof(GemmShared<BN, STAGES>) + 1024 + (EPI == GEMM_EPI_QKV ? 16 + 8 * kQkvStageFloats * sizeof(float) : 0);
+  const size_t shared = sizeof(GemmShared<BN, STAGES>) + 1024 + (EPI == GEMM_EPI_QKV ? 16 + 8 * kQkvStageFloats * sizeof(float) : 0) +
+                        (EPI == GEMM_EPI_F32 ? 16 + 8 * kEpilogueStageBytes : 0);
   static bool configured = false;
   if (!configured) {
     const cudaError_t err =
@@ -760,7 +820,8 @@ static int launch_gemm(const CUtensorMap& map_a, const CUtensorMap& map_b, void*
 template <int BN, int STAGES, int KB, int EPI>
 static int launch_gemm_pair(const CUtensorMap& map_a, const CUtensorMap& map_b, void* out, int ldo, int M, int N, int K,
                             int inter, int sm_count, int* error, cudaStream_t stream, const QkvEpilogue& qkv = QkvEpilogue()) {
-  const size_t shared = sizeof(PairShared<BN, STAGES, KB>) + 1024 + (EPI == GEMM_EPI_QKV ? 16 + 8 * kQkvStageFloats * sizeof(float) : 0);
+  const size_t shared = sizeof(PairShared<BN, STAGES, KB>) + 1024 + (EPI == GEMM_EPI_QKV ? 16 + 8 * kQkvStageFloats * sizeof(float) : 0) +
+                        (EPI == GEMM_EPI_F32 ? 16 + 8 * kEpilogueStageBytes : 0);
   static bool configured = false;
   static int resident_pairs = 0;  // pairs that can run at the same time (an SM left over in a GPC hosts none)
   if (!configured) {
@@ -844,13 +905,14 @@ extern "C" int distie_gemm_tcgen05(const void* x, int ldx, const void* w, void* 
     const int width = tile_width ? tile_width : pick_tile_width(M, N, 2 * kGemmBM, sm_count / 2);
     if (width != 128 && width != 192 && width != 256) return DISTIE_ERR_ARG;
     if ((status = make_map(&map_b, w, N, K, K, width / 2)) != 0) return status;
-#define DISTIE_GEMM_PAIR(BNV, STAGESV)                                                                                   \
+    // (stages: what fits beside the float32 epilogue's 32 KB of staging, where that is asked for)
+#define DISTIE_GEMM_PAIR(BNV, STAGESV, STAGES32)                                                                          \
   return epi == GEMM_EPI_F32                                                                                             \
-             ? launch_gemm_pair<BNV, STAGESV, 1, GEMM_EPI_F32>(map_a, map_b, out, ldo, M, N, K, 0, sm_count, error, stream) \
+             ? launch_gemm_pair<BNV, STAGES32, 1, GEMM_EPI_F32>(map_a, map_b, out, ldo, M, N, K, 0, sm_count, error, stream) \
              : launch_gemm_pair<BNV, STAGESV, 1, GEMM_EPI_BF16>(map_a, map_b, out, ldo, M, N, K, 0, sm_count, error, stream)
-    if (width == 256) { DISTIE_GEMM_PAIR(256, 6); }
-    if (width == 192) { DISTIE_GEMM_PAIR(192, 7); }
-    DISTIE_GEMM_PAIR(128, 8);
+    if (width == 256) { DISTIE_GEMM_PAIR(256, 6, 6); }
+    if (width == 192) { DISTIE_GEMM_PAIR(192, 7, 6); }
+    DISTIE_GEMM_PAIR(128, 8, 8);
 #undef DISTIE_GEMM_PAIR
   }
   if (epi == GEMM_EPI_SWIGLU) {
@@ -863,13 +925,13 @@ extern "C" int distie_gemm_tcgen05(const void* x, int ldx, const void* w, void* 
   if (width != 128 && width != 192 && width != 256) return DISTIE_ERR_ARG;
   status = make_map(&map_b, w, N, K, K, width);
   if (status != 0) return status;
-#define DISTIE_GEMM(BNV, STAGESV)                                                                                       \
+#define DISTIE_GEMM(BNV, STAGESV, STAGES32)                                                                              \
   return epi == GEMM_EPI_F32                                                                                            \
-             ? launch_gemm<BNV, STAGESV, GEMM_EPI_F32>(map_a, map_b, out, ldo, M, N, K, 0, sm_count, error, stream) \
+             ? launch_gemm<BNV, STAGES32, GEMM_EPI_F32>(map_a, map_b, out, ldo, M, N, K, 0, sm_count, error, stream) \
              : launch_gemm<BNV, STAGESV, GEMM_EPI_BF16>(map_a, map_b, out, ldo, M, N, K, 0, sm_count, error, stream)
-  if (width == 256) { DISTIE_GEMM(256, 4); }
-  if (width == 192) { DISTIE_GEMM(192, 5); }
-  DISTIE_GEMM(128, 6);
+  if (width == 256) { DISTIE_GEMM(256, 4, 4); }
+  if (width == 192) { DISTIE_GEMM(192, 5, 4); }
+  DISTIE_GEMM(128, 6, 6);
 #undef DISTIE_GEMM
 }
 
