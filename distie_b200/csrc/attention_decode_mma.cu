@@ -400,7 +400,7 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_row_strid
       }
       out[(size_t)t * out_row_stride + (size_t)(head0 + hd) * D + e] = __float2bfloat16_rn(l_all > 0.f ? acc / l_all : 0.f);
     }
-    cluster_barrier();  // no CTA leaves while another may still read its shared memory
+    cluster_barrier_exit();  // no CTA leaves while another may still read its shared memory
   }
 }
 

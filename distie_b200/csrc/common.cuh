@@ -171,6 +171,13 @@ __device__ __forceinline__ void cluster_barrier() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+// The barrier at the end of a kernel whose only purpose is that no CTA of the cluster leaves while another may still
+// read its shared memory: it orders execution, not memory.  (With release semantics a thread would first wait until
+// its own stores to global memory have been acknowledged, about a microsecond that the end of the grid waits for anyway.)
+__device__ __forceinline__ void cluster_barrier_exit() {
+  asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
+}
 // The float at `local` (an address in this CTA's shared memory) as CTA `rank` of the cluster holds it.
 __device__ __forceinline__ float cluster_load(const float* local, uint32_t rank) {
   uint32_t remote;

@@ -585,7 +585,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(cluster_address(&sm.accum_empty[buffer], 0));
+      if (lane == 0) mbar_arrive_cluster_relaxed(cluster_address(&sm.accum_empty[buffer], 0));
     }
     if (EPI == GEMM_EPI_QKV) asm volatile("cp.async.wait_all;" ::: "memory");  // (a loop left early: nothing stays in flight)
   }
@@ -598,7 +598,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_address(&sm.failed, rank ^ 1)), "r"(1u) : "memory");
     __nanosleep(20000);
   }
-  cluster_barrier();
+  cluster_barrier_exit();
   if (warp == 1) {
     asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS));
   }

@@ -93,7 +93,7 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, int vocab,
   if (at == 0x7fffffff) at = 0;  // a row of NaNs: still a valid token id
   if (!(temperature > 0.f)) {
     if (threadIdx.x == 0 && rank == 0) tokens[row] = at;
-    if (ctas > 1) cluster_barrier();  // nobody leaves while its shared memory may still be read
+    if (ctas > 1) cluster_barrier_exit();  // nobody leaves while its shared memory may still be read
     return;
   }
 
@@ -158,7 +158,7 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, int vocab,
       for (uint32_t r = 0; r < (uint32_t)ctas && pick < 0; ++r) pick = cluster_load_int(&cl_pick, r);
       tokens[row] = pick >= 0 ? pick : at;
     }
-    cluster_barrier();
+    cluster_barrier_exit();
   } else if (threadIdx.x == 0) {
     tokens[row] = cl_pick >= 0 ? cl_pick : at;
   }

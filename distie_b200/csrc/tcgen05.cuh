@@ -176,6 +176,11 @@ __device__ __forceinline__ uint32_t cluster_address(const void* local, uint32_t 
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
+// The same without release semantics, for an arrival that hands back tensor memory (ordered by the tcgen05 fences)
+// and publishes nothing in memory: the thread does not wait for its stores to global memory first.
+__device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
 // A tile load whose bytes are counted by an mbarrier given as a shared::cluster address (the leader CTA's).
 __device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int x,
                                                  int y) {
