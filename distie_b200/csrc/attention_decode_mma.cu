@@ -72,9 +72,32 @@ __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
 // PAGE16: the page size is a power of two >= 16, so a group of 16 keys lies in one page.
 // (The kernel runs for microseconds; its code is kept small -- one form of the copy loop per
 // instantiation, few inlined copies of it -- because fetching instructions is part of that time.)
-template <int D, int STAGES, int NH, bool PAGE16>
+//
+// FUSED: the kernel starts from the q/k/v projection itself instead of from a rotated q and a cache that
+// already holds the token's key and value.  `proj` is the projection's float32 slices (see ProjectionInput).
+// The threads of the CTA share out its query heads (and, in the split that holds the token's own position,
+// the token's key and value of its kv head) in units of 4 dims and their partners half a head further on: a
+// thread adds up the slices of its unit, all loads in flight together, adds the bias, rotates with cos and
+// sin of the position (computed once per CTA before the dependency wait) and leaves the result as bfloat16
+// in shared memory, from where the lanes take their MMA fragments as they would from a q in global memory.
+// The token's key and value also go into their cache page, and the warp that owns the last group of keys
+// puts them over that row of its tile.  The kernel that did all this for a decode step, one link of the
+// chain of dependent kernels, is then not launched.
+struct ProjectionInput {
+  const float* slices;     // [splits, tokens, row_stride]: q heads, then k heads, then v heads, head_dim each
+  int splits;
+  long long split_stride;  // floats between slices
+  int row_stride;          // floats per token
+  const float* bias;       // [row_stride] or null
+  const float* inv_freq;   // [head_dim / 2] or null (nothing is rotated)
+  float trig_factor;
+  int write_new;           // 0: the cache already holds the token's key and value (a layer that reads another's cache)
+};
+
+template <int D, int STAGES, int NH, bool PAGE16, bool FUSED>
 __global__ void __launch_bounds__(kMmaDecodeWarps * 32)
-attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, __nv_bfloat16* __restrict__ out,
+attention_decode_mma_kernel(const ProjectionInput proj,
+                            const __nv_bfloat16* __restrict__ q, int q_row_stride, __nv_bfloat16* __restrict__ out,
                             int out_row_stride, float* __restrict__ scratch_o, float* __restrict__ scratch_ml,
                             const int* __restrict__ positions, const int* __restrict__ token_seq,
                             const int* __restrict__ seq_seat, const int* __restrict__ block_table, int table_width,
@@ -96,6 +119,12 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_row_strid
   __shared__ float sh_m[kMmaDecodeWarps][16], sh_l[kMmaDecodeWarps][16];
   __shared__ float cl_m[16], cl_l[16];
   __shared__ int sh_pages[kMmaDecodePages];           // the split's part of the block table
+  // FUSED: q of this CTA's heads (rows 0 .. 8 NH - 1), then the token's key and value of this kv head, rotated,
+  // as bfloat16 (rows 16 bytes longer than a head, against bank conflicts); and cos | sin of the position.
+  constexpr int HALF = D / 2;
+  constexpr int QROW = D + 8;
+  __shared__ __align__(16) __nv_bfloat16 sh_q[FUSED ? (NH * 8 + 2) * QROW : 8];
+  __shared__ __align__(16) float sh_trig[FUSED ? D : 4];
 
   grid_dependency_release();
   const int t = blockIdx.x;
@@ -116,6 +145,19 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_row_strid
   const int split_page = first_page + split * pages_per_split;
   const int lo = max(first, split_page * page_size);
   const int hi = min(pos, (split_page + pages_per_split) * page_size - 1);
+  if (FUSED && threadIdx.x < HALF) {  // the angles depend on the position alone, an input of the step
+    float sn = 0.f, cs = 1.f;
+    if (proj.inv_freq) {
+      sincosf((float)pos * proj.inv_freq[threadIdx.x], &sn, &cs);
+      cs *= proj.trig_factor;
+      sn *= proj.trig_factor;
+    }
+    sh_trig[threadIdx.x] = cs;
+    sh_trig[HALF + threadIdx.x] = sn;
+  }
+  if (FUSED) __syncthreads();  // (before the wait: it delays nothing)
+  // The split that holds the token's own position puts the token's key and value in place itself.
+  const bool owns_new = FUSED && proj.write_new && hi == pos && lo <= pos;
   // The split's page ids come into shared memory in one round of loads (requested here, stored after
   // the first copies are on their way); a row of keys then costs no dependent global load before its
   // copy can be issued.  Until they are there (`staged_ready`), the table itself is read.
@@ -217,20 +259,105 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_row_strid
   for (; issued < STAGES - 1; ++issued) issue(warp + issued * kMmaDecodeWarps, issued);
   // B fragments of S^T = K Q^T: for k-step ks, dims 16 ks + 2c, + 1 and 16 ks + 2c + 8, + 9 of head g.
   uint32_t qb[NH][MT][2];
+  if (!FUSED) {
 #pragma unroll
-  for (int nh = 0; nh < NH; ++nh) {
-    const int hd = nh * 8 + g;
-    const __nv_bfloat16* row = q + (size_t)t * q_row_stride + (size_t)(head0 + hd) * D + 2 * c;
+    for (int nh = 0; nh < NH; ++nh) {
+      const int hd = nh * 8 + g;
+      const __nv_bfloat16* row = q + (size_t)t * q_row_stride + (size_t)(head0 + hd) * D + 2 * c;
 #pragma unroll
-    for (int ks = 0; ks < MT; ++ks) {
-      qb[nh][ks][0] = hd < heads_here ? __ldcg(reinterpret_cast<const unsigned int*>(row + 16 * ks)) : 0u;
-      qb[nh][ks][1] = hd < heads_here ? __ldcg(reinterpret_cast<const unsigned int*>(row + 16 * ks + 8)) : 0u;
+      for (int ks = 0; ks < MT; ++ks) {
+        qb[nh][ks][0] = hd < heads_here ? __ldcg(reinterpret_cast<const unsigned int*>(row + 16 * ks)) : 0u;
+        qb[nh][ks][1] = hd < heads_here ? __ldcg(reinterpret_cast<const unsigned int*>(row + 16 * ks + 8)) : 0u;
+      }
+    }
+  } else {
+    // Units of 4 dims j0 .. j0 + 3 and their partners HALF further on: this CTA's query heads, then (in the
+    // split that owns the new position) the token's key and value of its kv head.
+    constexpr int UPH = HALF / 4;  // units per head
+    constexpr int ROUND = 8;       // slices in flight together
+    const int units = (heads_here + (owns_new ? 2 : 0)) * UPH;
+    const float* row = proj.slices + (size_t)t * proj.row_stride;
+    __nv_bfloat16* new_k_row = nullptr;  // the token's row of the page, for the CTA that writes it
+    __nv_bfloat16* new_v_row = nullptr;
+    if (owns_new && chunk == 0) {  // (one CTA per kv head writes the page; every head chunk needs the row)
+      const int page = page_of(pos);
+      if (page < 0 || page >= num_pages) {
+        if (threadIdx.x == 0 && error) atomicExch(error, 2);
+      } else {
+        const int within = page_shift >= 0 ? pos & (page_size - 1) : pos % page_size;
+        const size_t at = (((size_t)page * num_kv_heads + kv_head) * page_size + within) * D;
+        new_k_row = const_cast<__nv_bfloat16*>(k_cache) + at;
+        new_v_row = const_cast<__nv_bfloat16*>(v_cache) + at;
+      }
+    }
+    for (int unit = threadIdx.x; unit < units; unit += kMmaDecodeWarps * 32) {
+      const int hd = unit / UPH, j0 = (unit % UPH) * 4;
+      int column, slot;  // where the head starts in the projection's row, and its row of sh_q
+      __nv_bfloat16* page_row = nullptr;
+      if (hd < heads_here) { column = (head0 + hd) * D; slot = hd; }
+      else if (hd == heads_here) { column = (num_heads + kv_head) * D; slot = NH * 8; page_row = new_k_row; }
+      else { column = (num_heads + num_kv_heads + kv_head) * D; slot = NH * 8 + 1; page_row = new_v_row; }
+      const float* first = row + column + j0;
+      float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;  // slices in order, then the bias, as the separate kernel adds
+      for (int s0 = 0; s0 < proj.splits; s0 += ROUND) {
+        float4 da[ROUND], db[ROUND];
+#pragma unroll
+        for (int u = 0; u < ROUND; ++u) {
+          if (s0 + u < proj.splits) {
+            const float* slice = first + (size_t)(s0 + u) * proj.split_stride;
+            da[u] = load4_cg(slice);
+            db[u] = load4_cg(slice + HALF);
+          } else {
+            da[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            db[u] = da[u];
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < ROUND; ++u) {
+          a.x += da[u].x; a.y += da[u].y; a.z += da[u].z; a.w += da[u].w;
+          b.x += db[u].x; b.y += db[u].y; b.z += db[u].z; b.w += db[u].w;
+        }
+      }
+      if (proj.bias) {
+        const float4 ba = load4(proj.bias + column + j0), bb = load4(proj.bias + column + HALF + j0);
+        a.x += ba.x; a.y += ba.y; a.z += ba.z; a.w += ba.w;
+        b.x += bb.x; b.y += bb.y; b.z += bb.z; b.w += bb.w;
+      }
+      float4 lo = a, hi = b;
+      if (slot != NH * 8 + 1) {  // q and k are rotated, v is not
+        const float4 cs = *reinterpret_cast<const float4*>(&sh_trig[j0]), sn = *reinterpret_cast<const float4*>(&sh_trig[HALF + j0]);
+        lo = make_float4(a.x * cs.x - b.x * sn.x, a.y * cs.y - b.y * sn.y, a.z * cs.z - b.z * sn.z, a.w * cs.w - b.w * sn.w);
+        hi = make_float4(b.x * cs.x + a.x * sn.x, b.y * cs.y + a.y * sn.y, b.z * cs.z + a.z * sn.z, b.w * cs.w + a.w * sn.w);
+      }
+      uint2 lo2, hi2;
+      lo2.x = pack2(lo.x, lo.y); lo2.y = pack2(lo.z, lo.w);
+      hi2.x = pack2(hi.x, hi.y); hi2.y = pack2(hi.z, hi.w);
+      *reinterpret_cast<uint2*>(&sh_q[slot * QROW + j0]) = lo2;
+      *reinterpret_cast<uint2*>(&sh_q[slot * QROW + HALF + j0]) = hi2;
+      if (page_row) {
+        *reinterpret_cast<uint2*>(page_row + j0) = lo2;
+        *reinterpret_cast<uint2*>(page_row + HALF + j0) = hi2;
+      }
     }
   }
 #pragma unroll
   for (int u = 0; u < kStagedPerThread; ++u) sh_pages[threadIdx.x + u * kMmaDecodeWarps * 32] = staged[u];
   __syncthreads();
   staged_ready = true;
+  const int last_group = groups - 1;
+  const bool owner_warp = owns_new && groups > 0 && warp == last_group % kMmaDecodeWarps;
+  if (FUSED) {
+#pragma unroll
+    for (int nh = 0; nh < NH; ++nh) {
+      const int hd = nh * 8 + g;
+      const __nv_bfloat16* x = &sh_q[hd * QROW + 2 * c];
+#pragma unroll
+      for (int ks = 0; ks < MT; ++ks) {
+        qb[nh][ks][0] = hd < heads_here ? *reinterpret_cast<const uint32_t*>(x + 16 * ks) : 0u;
+        qb[nh][ks][1] = hd < heads_here ? *reinterpret_cast<const uint32_t*>(x + 16 * ks + 8) : 0u;
+      }
+    }
+  }
   // ldmatrix addressing: lane = 8 * matrix + row of the matrix.
   const int lm_mat = lane >> 3, lm_row = lane & 7;
   int stage = 0;
@@ -242,6 +369,20 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_row_strid
     __syncwarp();
     const uint32_t k_tile = my_ring + (uint32_t)stage * 2 * TILE_BYTES, v_tile = k_tile + TILE_BYTES;
     stage = (stage + 1) % STAGES;
+    if (FUSED && owner_warp && grp == last_group) {
+      // The copy brought whatever the page held in the token's own row: put the token's key and value there.
+      const int r = pos - base_key;
+#pragma unroll
+      for (int i = 0; i < D / 64; ++i) {
+        const int d = 2 * (lane + 32 * i);  // two dims to a lane and round
+        const uint32_t offset = (uint32_t)(r * ROW_BYTES + (((d >> 3) ^ (r & 7)) << 4) + (d & 7) * 2);
+        const uint32_t kk = *reinterpret_cast<const uint32_t*>(&sh_q[NH * 8 * QROW + d]);
+        const uint32_t vv = *reinterpret_cast<const uint32_t*>(&sh_q[(NH * 8 + 1) * QROW + d]);
+        asm volatile("st.shared.b32 [%0], %1;" ::"r"(k_tile + offset), "r"(kk) : "memory");
+        asm volatile("st.shared.b32 [%0], %1;" ::"r"(v_tile + offset), "r"(vv) : "memory");
+      }
+      __syncwarp();
+    }
 
     // ---- S^T = K Q^T: rows = keys g and g + 8 of the group, columns = heads 2c and 2c + 1 -------------
     float st[NH][4];
@@ -479,13 +620,12 @@ extern "C" int distie_attention_decode_mma_stages(int tokens, int blocks_per_tok
   return (2 * ctas > sm_count && ctas <= sm_count) ? 3 : 2;
 }
 
-// Same arguments and scratch layout as distie_attention_decode (bfloat16 only).
-extern "C" int distie_attention_decode_mma(const void* q, int q_row_stride, void* out, int out_row_stride,
-                                           float* scratch, const int* positions, const int* token_seq,
-                                           const int* seq_seat, const int* block_table, int table_width,
-                                           const void* k_cache, const void* v_cache, int tokens, int num_heads,
-                                           int num_kv_heads, int head_dim, int page_size, int num_pages, int window,
-                                           float scale, int num_splits, int* error, cudaStream_t stream) {
+// `proj` null: q is given, rotated, and the cache holds every key; else the kernel starts from the projection.
+static int launch_decode_mma(const ProjectionInput* proj, const void* q, int q_row_stride, void* out, int out_row_stride,
+                             float* scratch, const int* positions, const int* token_seq, const int* seq_seat,
+                             const int* block_table, int table_width, const void* k_cache, const void* v_cache,
+                             int tokens, int num_heads, int num_kv_heads, int head_dim, int page_size, int num_pages,
+                             int window, float scale, int num_splits, int* error, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (num_heads < 1 || num_kv_heads < 1 || num_heads % num_kv_heads != 0 || page_size < 1 || table_width < 1 ||
       num_splits < 1 || num_splits > 65535 || (num_splits > kMmaDecodeClusterSplits && scratch == nullptr) || (q_row_stride & 7) ||
@@ -520,9 +660,13 @@ extern "C" int distie_attention_decode_mma(const void* q, int q_row_stride, void
   static bool configured = false;
   if (!configured) {
 #define DISTIE_MMA_DECODE_SMEM(DV, SV, NV)                                                                        \
-  if ((err = cudaFuncSetAttribute(attention_decode_mma_kernel<DV, SV, NV, true>,                                    \
+  if ((err = cudaFuncSetAttribute(attention_decode_mma_kernel<DV, SV, NV, true, false>,                             \
                                   cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024)) != cudaSuccess ||       \
-      (err = cudaFuncSetAttribute(attention_decode_mma_kernel<DV, SV, NV, false>,                                   \
+      (err = cudaFuncSetAttribute(attention_decode_mma_kernel<DV, SV, NV, false, false>,                            \
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024)) != cudaSuccess ||       \
+      (err = cudaFuncSetAttribute(attention_decode_mma_kernel<DV, SV, NV, true, true>,                              \
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024)) != cudaSuccess ||       \
+      (err = cudaFuncSetAttribute(attention_decode_mma_kernel<DV, SV, NV, false, true>,                             \
                                   cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024)) != cudaSuccess)         \
     return (int)err
     DISTIE_MMA_DECODE_SMEM(64, 2, 1); DISTIE_MMA_DECODE_SMEM(64, 3, 1); DISTIE_MMA_DECODE_SMEM(128, 2, 1); DISTIE_MMA_DECODE_SMEM(128, 3, 1);
@@ -533,18 +677,22 @@ extern "C" int distie_attention_decode_mma(const void* q, int q_row_stride, void
   // Up to 8 splits (the portable cluster size) are merged inside the kernel, through the cluster's shared memory.
   const int cluster_merge = (num_splits > 1 && num_splits <= kMmaDecodeClusterSplits) ? 1 : 0;
   const dim3 cluster = cluster_merge ? dim3(1, 1, num_splits) : dim3(0, 0, 0);
+  const ProjectionInput projection = proj ? *proj : ProjectionInput();
 #define DISTIE_MMA_DECODE(DV, SV, NV)                                                                              \
-  if (page_shift >= 4) DISTIE_MMA_DECODE_PAGE(DV, SV, NV, true);                                                   \
-  else DISTIE_MMA_DECODE_PAGE(DV, SV, NV, false)
-#define DISTIE_MMA_DECODE_PAGE(DV, SV, NV, PV)                                                                     \
-  err = launch_dependent_cluster(8, cluster, attention_decode_mma_kernel<DV, SV, NV, PV>, grid, dim3(kMmaDecodeWarps * 32), \
-                         shared, stream, (const __nv_bfloat16*)q, q_row_stride, (__nv_bfloat16*)out, out_row_stride, \
+  if (page_shift >= 4) { DISTIE_MMA_DECODE_FUSED(DV, SV, NV, true); }                                               \
+  else { DISTIE_MMA_DECODE_FUSED(DV, SV, NV, false); }
+#define DISTIE_MMA_DECODE_FUSED(DV, SV, NV, PV)                                                                    \
+  if (proj) DISTIE_MMA_DECODE_PAGE(DV, SV, NV, PV, true);                                                           \
+  else DISTIE_MMA_DECODE_PAGE(DV, SV, NV, PV, false)
+#define DISTIE_MMA_DECODE_PAGE(DV, SV, NV, PV, FV)                                                                 \
+  err = launch_dependent_cluster(8, cluster, attention_decode_mma_kernel<DV, SV, NV, PV, FV>, grid, dim3(kMmaDecodeWarps * 32), \
+                         shared, stream, projection, (const __nv_bfloat16*)q, q_row_stride, (__nv_bfloat16*)out, out_row_stride, \
                          scratch_o, scratch_ml, positions, token_seq, seq_seat, block_table, table_width,          \
                          (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, num_heads, group, chunks,   \
                          num_kv_heads, page_size, page_shift, num_pages, window, scale_log2, cluster_merge, error)
 #define DISTIE_MMA_DECODE_BY_STAGES(DV, NV)   \
-  if (stages == 2) DISTIE_MMA_DECODE(DV, 2, NV); \
-  else DISTIE_MMA_DECODE(DV, 3, NV)
+  if (stages == 2) { DISTIE_MMA_DECODE(DV, 2, NV) } \
+  else { DISTIE_MMA_DECODE(DV, 3, NV) }
   if (head_dim == 64) {
     if (column_tiles == 1) { DISTIE_MMA_DECODE_BY_STAGES(64, 1); } else { DISTIE_MMA_DECODE_BY_STAGES(64, 2); }
   } else {
@@ -552,6 +700,7 @@ extern "C" int distie_attention_decode_mma(const void* q, int q_row_stride, void
   }
 #undef DISTIE_MMA_DECODE_BY_STAGES
 #undef DISTIE_MMA_DECODE_PAGE
+#undef DISTIE_MMA_DECODE_FUSED
 #undef DISTIE_MMA_DECODE
   if (err != cudaSuccess) return (int)err;
   if (num_splits > 1 && !cluster_merge) {
@@ -562,4 +711,44 @@ extern "C" int distie_attention_decode_mma(const void* q, int q_row_stride, void
     if (err != cudaSuccess) return (int)err;
   }
   return 0;
+}
+
+// Same arguments and scratch layout as distie_attention_decode (bfloat16 only).
+extern "C" int distie_attention_decode_mma(const void* q, int q_row_stride, void* out, int out_row_stride,
+                                           float* scratch, const int* positions, const int* token_seq,
+                                           const int* seq_seat, const int* block_table, int table_width,
+                                           const void* k_cache, const void* v_cache, int tokens, int num_heads,
+                                           int num_kv_heads, int head_dim, int page_size, int num_pages, int window,
+                                           float scale, int num_splits, int* error, cudaStream_t stream) {
+  return launch_decode_mma(nullptr, q, q_row_stride, out, out_row_stride, scratch, positions, token_seq, seq_seat,
+                           block_table, table_width, k_cache, v_cache, tokens, num_heads, num_kv_heads, head_dim,
+                           page_size, num_pages, window, scale, num_splits, error, stream);
+}
+
+// The same for a step of single tokens that starts from the q/k/v projection: `slices` [splits, tokens, row_stride]
+// float32 (q heads, k heads, v heads), `bias` [row_stride] or null, `inv_freq` [head_dim / 2] or null (no rotation; the
+// rotation is over the whole head, pairs (j, j + head_dim / 2)).  With `write_new` the token's key and value go into
+// their cache page and are used; without it the cache must hold them already.
+extern "C" int distie_attention_decode_mma_qkv(const float* slices, int splits, long long split_stride, int row_stride,
+                                               const float* bias, const float* inv_freq, float trig_factor,
+                                               int write_new, void* out, int out_row_stride, float* scratch,
+                                               const int* positions, const int* token_seq, const int* seq_seat,
+                                               const int* block_table, int table_width, void* k_cache, void* v_cache,
+                                               int tokens, int num_heads, int num_kv_heads, int head_dim, int page_size,
+                                               int num_pages, int window, float scale, int num_splits, int* error,
+                                               cudaStream_t stream) {
+  if (slices == nullptr || splits < 1 || row_stride < (num_heads + 2 * num_kv_heads) * head_dim) return DISTIE_ERR_ARG;
+  if ((row_stride & 3) || (split_stride & 3) || ((uintptr_t)slices & 15) || ((uintptr_t)bias & 15)) return DISTIE_ERR_UNSUPPORTED;
+  ProjectionInput proj;
+  proj.slices = slices;
+  proj.splits = splits;
+  proj.split_stride = split_stride;
+  proj.row_stride = row_stride;
+  proj.bias = bias;
+  proj.inv_freq = inv_freq;
+  proj.trig_factor = trig_factor;
+  proj.write_new = write_new;
+  return launch_decode_mma(&proj, nullptr, 8, out, out_row_stride, scratch, positions, token_seq, seq_seat, block_table,
+                           table_width, k_cache, v_cache, tokens, num_heads, num_kv_heads, head_dim, page_size,
+                           num_pages, window, scale, num_splits, error, stream);
 }

@@ -337,6 +337,48 @@ class DeviceKernels(KernelSet):
         by_length = max(1, max_kv_len // 256)
         return max(1, min(by_machine, by_length, 64))
 
+    def qkv_attention(self, x, weight, bias, step, kv, writes_cache, rotary, num_heads, num_kv_heads, head_dim,
+                      window, scale, out) -> None:
+        """A step of single tokens on the tensor-core kernels: the attention kernel starts from the
+        projection's float32 slices itself (bias, rotation, the token's key and value into the cache and into
+        its own tile), so the kernel between the projection and the attention is not launched."""
+        merged = (
+            step.num_decode_tokens == step.num_tokens and self.dtype == torch.bfloat16 and head_dim in _PREFILL_HEAD_DIMS
+            and self._skinny(x, weight) and weight.shape[0] == (num_heads + 2 * num_kv_heads) * head_dim
+            and (rotary is None or (rotary.rotary_dim == head_dim and not rotary.interleaved))
+            and (bias is None or bias.dtype == torch.float32) and kv.k.dtype == torch.bfloat16
+            and out.dtype == torch.bfloat16
+        )
+        if not merged:
+            return super().qkv_attention(x, weight, bias, step, kv, writes_cache, rotary, num_heads, num_kv_heads,
+                                         head_dim, window, scale, out)
+        slices = self.linear_split(x, weight)
+        window = int(window) if window else 0
+        tokens = step.num_tokens
+        splits = self.plan_splits(tokens, num_heads, num_kv_heads, step.max_kv_len)
+        if splits <= 2 * _CLUSTER_SPLITS:
+            splits = min(splits, _CLUSTER_SPLITS)  # merged inside the kernel, by a cluster of CTAs
+        scratch = None
+        if splits > _CLUSTER_SPLITS:
+            floats = function("distie_attention_decode_scratch_floats")(tokens, num_heads, head_dim, splits)
+            scratch = torch.empty(floats, dtype=torch.float32, device=x.device)
+        check(
+            function("distie_attention_decode_mma_qkv")(
+                slices.data_ptr(), slices.shape[0], slices.stride(0), slices.stride(1),
+                bias.data_ptr() if bias is not None else None,
+                rotary.inv_freq.data_ptr() if rotary is not None else None,
+                float(rotary.factor) if rotary is not None else 1.0, int(bool(writes_cache)),
+                out.data_ptr(), out.stride(0), scratch.data_ptr() if scratch is not None else None,
+                step.positions.data_ptr(), step.token_seq.data_ptr(), step.seq_seat.data_ptr(),
+                kv.block_table.data_ptr(), kv.block_table.shape[-1], kv.k.data_ptr(), kv.v.data_ptr(), tokens,
+                num_heads, num_kv_heads, head_dim, kv.page_size, kv.num_pages, window, float(scale), splits,
+                self.error_flag.data_ptr(), self._stream(),
+            ),
+            "attention_decode_mma_qkv",
+        )
+        self._ran("attention_decode_mma", 1 if splits <= _CLUSTER_SPLITS else 2)
+        self._ran("attention_decode_mma_qkv", 0)
+
     def attention(self, qkv, out, step, kv, num_heads, num_kv_heads, head_dim, window, scale) -> None:
         window = int(window) if window else 0
         n_dec = step.num_decode_tokens if head_dim in _DECODE_HEAD_DIMS else 0

@@ -121,6 +121,17 @@ class KernelSet(ABC):
         slices = self.linear_split(x, weight)
         self.rope_kv_write(slices, step, kv, rotary, num_heads, num_kv_heads, head_dim, bias=bias, q_out=q_out)
 
+    def qkv_attention(self, x, weight, bias, step: StepTensors, kv: KvSlot, writes_cache: bool,
+                      rotary: RotaryTable | None, num_heads: int, num_kv_heads: int, head_dim: int,
+                      window: int | None, scale: float, out) -> None:
+        """From the mixer's input to the attention's output: the q/k/v projection, bias, rotation, the new
+        keys and values into their pages (if ``writes_cache``) and attention over the pages into ``out``.
+        The default is the ops after one another; a set may merge them for some steps."""
+        q = torch.empty((x.shape[0], num_heads * head_dim), dtype=out.dtype, device=x.device)
+        self.qkv_rope_write(x, weight, bias, step, kv if writes_cache else None, rotary, num_heads, num_kv_heads,
+                            head_dim, q)
+        self.attention(q, out, step, kv, num_heads, num_kv_heads, head_dim, window, scale)
+
     @abstractmethod
     def attention(self, qkv, out, step: StepTensors, kv: KvSlot, num_heads: int, num_kv_heads: int,
                   head_dim: int, window: int | None, scale: float) -> None:

@@ -41,6 +41,9 @@ _SIGNATURES: dict[str, tuple[str, list]] = {
     ),
     "distie_attention_decode_mma_stages": ("bf16", [I, I, I, I]),
     "distie_attention_decode_mma": ("bf16", [P, I, P, I, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, F, I, P, P]),
+    "distie_attention_decode_mma_qkv": (
+        "bf16", [P, I, L, I, P, P, F, I, P, I, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, F, I, P, P]
+    ),
     "distie_gemm_tcgen05": ("bf16", [P, I, P, P, I, I, I, I, I, I, I, P, P]),
     "distie_gemm_tcgen05_qkv": ("bf16", [P, I, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, P, P]),
     "distie_gemm_tcgen05_skinny_splits": ("bf16", [I, I, I]),

@@ -103,22 +103,22 @@ class GqaAttention:
         if run.kv is None:
             raise RuntimeError("attention needs a cache slot")
         k = self.kernels
-        q = torch.empty((x.shape[0], self.num_heads * self.head_dim), dtype=x.dtype, device=x.device)
-        kv = run.kv if run.writes_cache else None
+        mixed = torch.empty((x.shape[0], self.num_heads * self.head_dim), dtype=x.dtype, device=x.device)
         table = self.position.rotary_table()
         if table is None and hasattr(self.position, "apply"):
             # An encoding of its own: the projection is finished here, the encoding changes q and k in
             # place, and the fused kernel only stores k and v and copies q out.
+            q = torch.empty_like(mixed)
             qkv = k.linear(x, self.qkv.weight, self.qkv.bias)
             self.position.apply(qkv, run.step, self.num_heads, self.num_kv_heads, self.head_dim)
-            k.rope_kv_write(qkv, run.step, kv, None, self.num_heads, self.num_kv_heads, self.head_dim, q_out=q)
+            k.rope_kv_write(qkv, run.step, run.kv if run.writes_cache else None, None, self.num_heads,
+                            self.num_kv_heads, self.head_dim, q_out=q)
+            k.attention(q, mixed, run.step, run.kv, self.num_heads, self.num_kv_heads, self.head_dim, self.window, self.scale)
         else:
-            # The projection, the bias, the rotation of q and k and the store of k and v in their pages
-            # as one op of the kernel set; q comes back in a buffer of its own.
-            k.qkv_rope_write(x, self.qkv.weight, self.qkv.bias, run.step, kv, table, self.num_heads,
-                             self.num_kv_heads, self.head_dim, q)
-        mixed = torch.empty_like(q)
-        k.attention(q, mixed, run.step, run.kv, self.num_heads, self.num_kv_heads, self.head_dim, self.window, self.scale)
+            # The projection, the bias, the rotation of q and k, the store of k and v in their pages and the
+            # attention over the pages as one op of the kernel set, which may merge kernels for some steps.
+            k.qkv_attention(x, self.qkv.weight, self.qkv.bias, run.step, run.kv, run.writes_cache, table,
+                            self.num_heads, self.num_kv_heads, self.head_dim, self.window, self.scale, mixed)
         if self.out.bias is not None:
             return self.out(mixed)
         return k.linear_split(mixed, self.out.weight)  # summed by the norm that follows

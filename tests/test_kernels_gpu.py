@@ -388,6 +388,53 @@ def test_decode_attention_at_every_split_count(kernel_sets, dtype, head_dim, hea
     close(out, want, dtype, f"decode attention in {splits} splits")
 
 
+@pytest.mark.parametrize(
+    "heads,kv_heads,head_dim,hidden,page,with_bias,with_table,factor",
+    [(12, 2, 128, 1536, 16, True, True, 1.0), (6, 1, 64, 200, 8, True, True, 1.25), (5, 5, 64, 72, 16, False, True, 1.0),
+     (40, 2, 128, 264, 32, True, False, 1.0), (4, 4, 128, 96, 4, True, True, 0.8)],
+)
+@pytest.mark.parametrize("splits", [1, 2, 4, 8, 13])
+def test_decode_attention_from_the_projection(kernel_sets, heads, kv_heads, head_dim, hidden, page, with_bias, with_table,
+                                              factor, splits, monkeypatch):
+    """A step of single tokens through the merged op (projection slices -> bias, rotation, the token's key and
+    value into the cache and into the attention itself) against the plain ops one after the other: the outputs,
+    the cache rows that were written, and that no other row was touched.  Positions at the start of a request,
+    at the first and last row of a page and of a group of 16 keys; with and without a write of the cache."""
+    from distie_b200.kernels.interface import KvSlot, RotaryTable
+
+    ks = kernel_sets[torch.bfloat16]
+    pasts = [699, 32, 1499, 0, 15, 16, 31, 255, 256]
+    step = step_of([1] * len(pasts), pasts, list(range(len(pasts))))
+    monkeypatch.setattr(ks, "plan_splits", lambda *args: splits)
+    n = (heads + 2 * kv_heads) * head_dim
+    x = torch.randn(step.num_tokens, hidden, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(n, hidden, device="cuda") / hidden**0.5).to(torch.bfloat16)
+    bias = torch.randn(n, device="cuda") if with_bias else None
+    inv_freq = (1.0 / (10000.0 ** (torch.arange(0, head_dim, 2, dtype=torch.float32) / head_dim))).cuda()
+    rotary = RotaryTable(inv_freq, head_dim, False, factor) if with_table else None
+    product = torch.nn.functional.linear(x.float(), w.float()).unsqueeze(0)
+    scale = head_dim**-0.5
+    for writes in (True, False):
+        kv_a = filled_cache_for(torch.bfloat16, kv_heads, head_dim, page, [p + 1 for p in pasts], seed=13)
+        kv_b = KvSlot(kv_a.k.clone(), kv_a.v.clone(), kv_a.block_table, kv_a.page_size, kv_a.num_pages)
+        before_k, before_v = kv_a.k.clone(), kv_a.v.clone()
+        out = torch.full((step.num_tokens, heads * head_dim), float("nan"), dtype=torch.bfloat16, device="cuda")
+        count = ks.kernel_counts.get("attention_decode_mma_qkv", 0)
+        ks.qkv_attention(x, w, bias, step, kv_a, writes, rotary, heads, kv_heads, head_dim, None, scale, out)
+        ks.check_errors()
+        assert ks.kernel_counts.get("attention_decode_mma_qkv", 0) == count + 1, "the merged kernel was meant to run"
+        q = torch.zeros_like(out)
+        ref.rope_kv_write(product, step, kv_b if writes else None, rotary, heads, kv_heads, head_dim, bias=bias, q_out=q)
+        want = ref.attention(q, step, kv_b, heads, kv_heads, head_dim, None, scale)
+        close(out, want, torch.bfloat16, f"merged decode attention, {splits} splits, writes {writes}")
+        close(kv_a.k, kv_b.k, torch.bfloat16, "cached keys")
+        close(kv_a.v, kv_b.v, torch.bfloat16, "cached values")
+        changed = (kv_a.k != before_k).any(-1) | (kv_a.v != before_v).any(-1)   # [pages, kv_heads, rows]
+        expected = (kv_b.k != before_k).any(-1) | (kv_b.v != before_v).any(-1)
+        assert not bool((changed & ~expected).any()), "a row other than the tokens' own was written"
+        assert bool(changed.any()) == writes
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("head_dim,page,far", [(128, 16, 3), (64, 16, 511), (32, 8, 256), (128, 16, 1008)])
 def test_attention_finds_one_far_key(kernel_sets, dtype, head_dim, page, far):
