@@ -856,13 +856,21 @@ static int launch_gemm_pair(const CUtensorMap& map_a, const CUtensorMap& map_b, 
   return err == cudaSuccess ? 0 : (int)err;
 }
 
-// Tile width (128, 192 or 256 columns).  Pairs of CTAs take 256: measured at the projection and feed-forward
-// shapes of 1.5B, 7B and 14B models with 512 to 2,048 rows, 256-wide tiles were the fastest or within 4 % of
-// it everywhere, while a count of waves alone picked 128 for [2048 x 7168 x 5120] and lost a third of the
-// time to operand traffic (a narrow tile re-reads A once per 128 columns).  A single CTA per tile (fewer than
-// 256 rows) takes the width whose waves of `slots` tiles cost least.
+// Tile width (128, 192 or 256 columns).  Pairs of CTAs take 256 as soon as the product is more than one wave of
+// tiles: measured at the projection and feed-forward shapes of 1.5B, 7B and 14B models with 512 to 2,048 rows,
+// 256-wide tiles were the fastest or within 4 % of it there, while a count of waves alone picked 128 for
+// [2048 x 7168 x 5120] and lost a third of the time to operand traffic (a narrow tile re-reads A once per 128
+// columns).  A product that is a single wave either way takes the narrowest tiles that still are one wave:
+// every pair then has less to do (2,048 x 1,536 x 1,536: 12.3 against 12.9 us with 192; 512 rows of it: 11.7
+// against 13.6 us with 128).  A single CTA per tile (fewer than 256 rows) takes the width whose waves of
+// `slots` tiles cost least.
 static int pick_tile_width(int M, int N, int tile_rows, int slots) {
-  if (tile_rows > kGemmBM) return 256;
+  if (tile_rows > kGemmBM) {
+    const int m_tiles = (M + tile_rows - 1) / tile_rows;
+    for (int width : {128, 192})  // (a few pairs fewer than there are: an SM left over in a GPC hosts no pair)
+      if ((long long)m_tiles * ((N + width - 1) / width) <= slots - 4) return width;
+    return 256;
+  }
   const int m_tiles = (M + tile_rows - 1) / tile_rows;
   int best = 256;
   long long best_cost = -1;
