@@ -81,6 +81,32 @@ __device__ __forceinline__ float exp2_approx(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// The softmax warps are bound by the number of instructions they issue (two warps to a scheduler, long chains of
+// dependent operations), so the loop over a block's scores uses the forms that do two things at once: the maximum
+// of three values, and float32 arithmetic on pairs of values in a 64-bit register (same rounding per value).
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t pair_of(float lo, float hi) {
+  uint64_t v;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "f"(lo), "f"(hi));
+  return v;
+}
+__device__ __forceinline__ void halves_of(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma_pairs(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add_pairs(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
 
 template <int D>
 __global__ void __launch_bounds__(kAttnThreads, 1)
@@ -293,7 +319,8 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       // The row's maximum over the group's keys: four running maxima keep the chain of dependent operations short.
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int i = 0; i < kAttnGroupKeys; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sv[i]));
+      for (int i = 0; i < kAttnGroupKeys; i += 2)
+        mx4[(i >> 1) & 3] = max3(mx4[(i >> 1) & 3], __uint_as_float(sv[i]), __uint_as_float(sv[i + 1]));
       const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       const float m_new = fmaxf(m_used, mx * scale_log2);
       const bool raise = m_new > m_used + kAttnRaise || (m_used == -INFINITY && m_new > -INFINITY);
@@ -321,18 +348,24 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       // first 32 of the group's 64 columns of this S buffer (the thread has its S in registers).  A
       // masked S is -inf and gives 0.
       const float shift = m_used == -INFINITY ? 0.f : m_used;
-      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+      uint64_t sum4[4] = {0ull, 0ull, 0ull, 0ull};  // four pairs of running sums
+      const uint64_t scale2 = pair_of(scale_log2, scale_log2), shift2 = pair_of(-shift, -shift);
       uint32_t packed[kAttnGroupKeys / 2];
 #pragma unroll
       for (int i = 0; i < kAttnGroupKeys; i += 2) {
-        const float p0 = exp2_approx(fmaf(__uint_as_float(sv[i]), scale_log2, -shift));
-        const float p1 = exp2_approx(fmaf(__uint_as_float(sv[i + 1]), scale_log2, -shift));
-        sum4[(i >> 1) & 3] += p0 + p1;
+        float x0, x1;
+        halves_of(fma_pairs(pair_of(__uint_as_float(sv[i]), __uint_as_float(sv[i + 1])), scale2, shift2), x0, x1);
+        const float p0 = exp2_approx(x0), p1 = exp2_approx(x1);
+        sum4[(i >> 1) & 3] = add_pairs(sum4[(i >> 1) & 3], pair_of(p0, p1));
         const __nv_bfloat162 pair = __floats2bfloat162_rn(p0, p1);
         packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&pair);
       }
       tmem_store_32(s_addr, packed);
-      l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      {
+        float even, odd;
+        halves_of(add_pairs(add_pairs(sum4[0], sum4[1]), add_pairs(sum4[2], sum4[3])), even, odd);
+        l += even + odd;
+      }
       asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       // Rows of V past the last key the tile needs: zero, so that P = 0 gives 0.  Each group clears the
       // rows of its own keys.
