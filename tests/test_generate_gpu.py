@@ -101,6 +101,54 @@ def test_long_decoding_bfloat16_and_float32(tiny_model):
             budget.check(got, want, "long decoding")
 
 
+@pytest.mark.parametrize("name", ["C", "D"])
+def test_the_merged_decode_attention_changes_no_logit(name, tmp_path_factory, monkeypatch):
+    """Steps of single tokens with the attention kernel that starts from the projection, against the same steps
+    with the projection, the rotation kernel and the attention one after the other: the sums, the rotation and
+    the rounding are the same operations in the same order, so the logits must agree bit for bit (and the
+    kernels that ran must differ)."""
+    from distie_b200.engine.engine import Engine
+    from distie_b200.kernels.device import DeviceKernels
+    from distie_b200.kernels.interface import KernelSet
+
+    folder, cfg, page, _ = folder_for(name, tmp_path_factory)
+    ids = helpers.random_ids(cfg["vocab_size"], 150, 41)
+    logits, counts = {}, {}
+    for merged in (True, False):
+        if not merged:
+            monkeypatch.setattr(DeviceKernels, "qkv_attention", KernelSet.qkv_attention)
+        engine = Engine.load(folder, dtype="bfloat16", num_blocks=64, page_size=page, max_seqs=2)
+        trace = engine.trace(ids[:70], len(ids) - 70 + 1, ids[70:] + [0])
+        logits[merged] = trace.logits
+        counts[merged] = dict(engine.model.kernels.kernel_counts)
+        assert engine.runner.graph_replays > 0
+    assert counts[True].get("attention_decode_mma_qkv", 0) > 0 and counts[False].get("attention_decode_mma_qkv", 0) == 0
+    assert counts[False].get("rope_kv_write_split", 0) > counts[True].get("rope_kv_write_split", 0)
+    assert torch.equal(logits[True], logits[False]), float((logits[True] - logits[False]).abs().max())
+
+
+@pytest.mark.parametrize("name", ["C", "D"])
+def test_the_merged_projection_epilogue_changes_no_logit(name, tmp_path_factory, monkeypatch):
+    """A prompt of 300 tokens with bias, rotation and the cache write in the q/k/v product's epilogue, against the
+    product's float32 result handed to the rotation kernel: the same operations on the same float32 sums."""
+    from distie_b200.engine.engine import Engine
+    from distie_b200.kernels.device import DeviceKernels
+    from distie_b200.kernels.interface import KernelSet
+
+    folder, cfg, page, _ = folder_for(name, tmp_path_factory)
+    ids = helpers.random_ids(cfg["vocab_size"], 300, 43)
+    logits, counts = {}, {}
+    for merged in (True, False):
+        if not merged:
+            monkeypatch.setattr(DeviceKernels, "qkv_rope_write", KernelSet.qkv_rope_write)
+        engine = Engine.load(folder, dtype="bfloat16", num_blocks=64, page_size=page, max_seqs=2)
+        trace = engine.trace(ids, 4, [1, 2, 3, 4])
+        logits[merged] = trace.logits
+        counts[merged] = dict(engine.model.kernels.kernel_counts)
+    assert counts[True].get("gemm_tcgen05_qkv", 0) > 0 and counts[False].get("gemm_tcgen05_qkv", 0) == 0
+    assert torch.equal(logits[True], logits[False]), float((logits[True] - logits[False]).abs().max())
+
+
 def test_preemption_and_chunked_prefill_on_gpu(tmp_path_factory):
     """tiny-B, prompts 1/5/17/40/63, portions of 11 beside decoding, a pool that forces preemption."""
     from distie_b200.engine.engine import Engine
