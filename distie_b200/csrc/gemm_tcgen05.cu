@@ -746,19 +746,21 @@ gemm_tcgen05_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
     const bool valid = ready && !sm.failed && k_blocks > 0;
     const int row = r0 + local_row;
     const float b = (EPI == SKINNY_EPI_STORE && bias && row < N) ? bias[row] : 0.f;
-    // Sixteen rows of x at a time: the accumulator never occupies more than sixteen registers.
-    for (int c0 = 0; c0 < BN && c0 < M; c0 += 16) {
+    // The whole accumulator of the row comes out of tensor memory at once (one wait, not one per sixteen
+    // columns: with 64 rows of x the waits were a microsecond at the end of every CTA); it is then handled
+    // sixteen rows of x at a time.
+    uint32_t whole[BN];
+    if (valid) {
+#pragma unroll
+      for (int c0 = 0; c0 < BN; c0 += 16) tmem_load_16(lane_base + c0, *reinterpret_cast<uint32_t(*)[16]>(&whole[c0]));
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+    }
+#pragma unroll
+    for (int c0 = 0; c0 < BN; c0 += 16) {
+      if (c0 >= M) break;
       float acc[16];
-      if (valid) {
-        uint32_t v[16];
-        tmem_load_16(lane_base + c0, v);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-        for (int j = 0; j < 16; ++j) acc[j] = __uint_as_float(v[j]);
-      } else {
-#pragma unroll
-        for (int j = 0; j < 16; ++j) acc[j] = 0.f;
-      }
+      for (int j = 0; j < 16; ++j) acc[j] = valid ? __uint_as_float(whole[c0 + j]) : 0.f;
       if (EPI == SKINNY_EPI_SWIGLU) {
 #pragma unroll
         for (int j = 0; j < 16; ++j) sm.exchange[local_row][j] = acc[j];
