@@ -112,10 +112,16 @@ __device__ __forceinline__ void store_accumulator(uint32_t lane_base, int row0, 
         store_row_bf16(v, (__nv_bfloat16*)out + (size_t)(row0 + lane) * ldo + col, inter - col, ((ldo | col) & 7) == 0);
     }
   } else {
-    for (int c0 = part * (BN / 2); c0 < (part + 1) * (BN / 2); c0 += 32) {
-      uint32_t acc[32];
-      tmem_load_32(lane_base + c0, acc);
-      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+    // The warp's whole part of the accumulator comes out of tensor memory behind one wait.
+    constexpr int CHUNKS = BN / 64;
+    uint32_t whole[CHUNKS][32];
+#pragma unroll
+    for (int i = 0; i < CHUNKS; ++i) tmem_load_32(lane_base + part * (BN / 2) + 32 * i, whole[i]);
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < CHUNKS; ++i) {
+      const int c0 = part * (BN / 2) + 32 * i;
+      uint32_t(&acc)[32] = whole[i];
       float v[32];
 #pragma unroll
       for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(acc[j]);
