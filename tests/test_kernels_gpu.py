@@ -399,7 +399,8 @@ def test_decode_attention_from_the_projection(kernel_sets, heads, kv_heads, head
     """A step of single tokens through the merged op (projection slices -> bias, rotation, the token's key and
     value into the cache and into the attention itself) against the plain ops one after the other: the outputs,
     the cache rows that were written, and that no other row was touched.  Positions at the start of a request,
-    at the first and last row of a page and of a group of 16 keys; with and without a write of the cache."""
+    at the first and last row of a page and of a group of 16 keys; with and without a write of the cache, and
+    with a window of 100 keys."""
     from distie_b200.kernels.interface import KvSlot, RotaryTable
 
     ks = kernel_sets[torch.bfloat16]
@@ -414,19 +415,19 @@ def test_decode_attention_from_the_projection(kernel_sets, heads, kv_heads, head
     rotary = RotaryTable(inv_freq, head_dim, False, factor) if with_table else None
     product = torch.nn.functional.linear(x.float(), w.float()).unsqueeze(0)
     scale = head_dim**-0.5
-    for writes in (True, False):
+    for writes, window in ((True, None), (False, None), (True, 100)):
         kv_a = filled_cache_for(torch.bfloat16, kv_heads, head_dim, page, [p + 1 for p in pasts], seed=13)
         kv_b = KvSlot(kv_a.k.clone(), kv_a.v.clone(), kv_a.block_table, kv_a.page_size, kv_a.num_pages)
         before_k, before_v = kv_a.k.clone(), kv_a.v.clone()
         out = torch.full((step.num_tokens, heads * head_dim), float("nan"), dtype=torch.bfloat16, device="cuda")
         count = ks.kernel_counts.get("attention_decode_mma_qkv", 0)
-        ks.qkv_attention(x, w, bias, step, kv_a, writes, rotary, heads, kv_heads, head_dim, None, scale, out)
+        ks.qkv_attention(x, w, bias, step, kv_a, writes, rotary, heads, kv_heads, head_dim, window, scale, out)
         ks.check_errors()
         assert ks.kernel_counts.get("attention_decode_mma_qkv", 0) == count + 1, "the merged kernel was meant to run"
         q = torch.zeros_like(out)
         ref.rope_kv_write(product, step, kv_b if writes else None, rotary, heads, kv_heads, head_dim, bias=bias, q_out=q)
-        want = ref.attention(q, step, kv_b, heads, kv_heads, head_dim, None, scale)
-        close(out, want, torch.bfloat16, f"merged decode attention, {splits} splits, writes {writes}")
+        want = ref.attention(q, step, kv_b, heads, kv_heads, head_dim, window, scale)
+        close(out, want, torch.bfloat16, f"merged decode attention, {splits} splits, writes {writes}, window {window}")
         close(kv_a.k, kv_b.k, torch.bfloat16, "cached keys")
         close(kv_a.v, kv_b.v, torch.bfloat16, "cached values")
         changed = (kv_a.k != before_k).any(-1) | (kv_a.v != before_v).any(-1)   # [pages, kv_heads, rows]
