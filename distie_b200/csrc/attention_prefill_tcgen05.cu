@@ -126,6 +126,12 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   volatile uint32_t* failed = &sm.failed;
 
+  if (threadIdx.x == 64) {
+    prefetch_tensor_map(&map_q);
+    prefetch_tensor_map(&map_k);
+    prefetch_tensor_map(&map_v);
+    prefetch_tensor_map(&map_out);
+  }
   if (threadIdx.x == 0) {
     mbar_init(&sm.q_full, 1);
     for (int s = 0; s < kAttnKStages; ++s) {

@@ -290,6 +290,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int k_blocks = (K + kGemmBK - 1) / kGemmBK;
 
+  if (threadIdx.x == 64) {
+    prefetch_tensor_map(&map_a);
+    prefetch_tensor_map(&map_b);
+  }
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&sm.full[s], 1);
@@ -463,6 +467,10 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   const uint32_t rank = cluster_cta_rank();       // 0: issues the MMAs
   const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
 
+  if (threadIdx.x == 64) {
+    prefetch_tensor_map(&map_a);
+    prefetch_tensor_map(&map_b);
+  }
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&sm.full[s], 1);
@@ -662,6 +670,10 @@ gemm_tcgen05_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
   const int r0 = EPI == SKINNY_EPI_SWIGLU ? tile * 64 : tile * kGemmBM;
 
   grid_dependency_release();
+  if (threadIdx.x == 32) {
+    prefetch_tensor_map(&map_w);
+    prefetch_tensor_map(&map_x);
+  }
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&sm.full[s], 1);
