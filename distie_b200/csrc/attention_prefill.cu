@@ -110,7 +110,9 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, 
 #pragma unroll
     for (int r = my_row0; r < kTileN; r += ROWS_PER_PASS) {
       const int key = kb + r;
-      bool ok = key <= p_last;
+      // (keys before every row's window are not looked up: a cache with a window may have given their page
+      // back; their rows are filled with zeros and masked)
+      bool ok = key <= p_last && key >= first_key;
       size_t at = 0;
       if (ok) {
         // page_shift >= 0: the page size is a power of two, so no division per row.

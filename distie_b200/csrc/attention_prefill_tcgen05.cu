@@ -183,13 +183,18 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   const int page_size = 1 << page_shift;
   const int* table = block_table + (size_t)seat * table_width;
   const int pages_per_block = kAttnKeys >> page_shift;  // at most 16
-  auto pages_of = [&](int j) {  // pages of block j that hold keys the tile needs
+  auto pages_of = [&](int j) {  // pages of block j up to the last one that holds keys the tile needs
     return min(pages_per_block, ((last_pos - (block_first + j) * kAttnKeys) >> page_shift) + 1);
   };
-  auto read_table = [&](int j) {  // this lane's page of block j, -1 beyond the block's pages
+  // Pages of the first block that lie wholly before the oldest key any row of the tile sees: a cache with a
+  // window may have given them back already, so they are neither looked up nor fetched (their rows of the
+  // tile are masked as keys and cleared as values).
+  const int skipped0 = (first_key - block_first * kAttnKeys) >> page_shift;
+  auto skipped = [&](int j) { return j == 0 ? skipped0 : 0; };
+  auto read_table = [&](int j) {  // this lane's page of block j, -1 outside the block's pages
     if (j >= blocks) return -1;
     const int column = (((block_first + j) * kAttnKeys) >> page_shift) + lane;
-    return (lane < pages_of(j) && column < table_width) ? __ldg(table + column) : -1;
+    return (lane >= skipped(j) && lane < pages_of(j) && column < table_width) ? __ldg(table + column) : -1;
   };
   const bool producer = warp == 0 || warp == kAttnVProducerWarp;
   int page_ahead = producer ? read_table(0) : -1;
@@ -212,16 +217,16 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       const int s = j % stages, use = j / stages;
       const int page = page_ahead;
       page_ahead = read_table(j + 1);
-      const int count = pages_of(j);
-      if (__any_sync(0xffffffffu, lane < count && (page < 0 || page >= num_pages))) {
+      const int count = pages_of(j), from = skipped(j);
+      if (__any_sync(0xffffffffu, lane >= from && lane < count && (page < 0 || page >= num_pages))) {
         if (lane == 0 && error) atomicExch(error, 4);
         ok = false;
         break;
       }
       if (!__all_sync(0xffffffffu, mbar_wait_unless(&empty[s], (use & 1) ^ 1, failed))) { ok = false; break; }
-      if (lane == 0) mbar_expect_tx(&full[s], (uint32_t)count * page_size * D * 2);
+      if (lane == 0) mbar_expect_tx(&full[s], (uint32_t)(count - from) * page_size * D * 2);
       __syncwarp();
-      if (lane < count) {
+      if (lane >= from && lane < count) {
         unsigned char* stage = (for_k ? sm.k[s] : sm.v[s]) + lane * page_size * 128;
         const int row = (page * num_kv_heads + kv_head) * page_size;
         for (int h = 0; h < HALVES; ++h) tma_load_2d(stage + h * kAttnHalf, map, &full[s], h * 64, row);
@@ -373,12 +378,13 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         l += even + odd;
       }
       asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-      // Rows of V past the last key the tile needs: zero, so that P = 0 gives 0.  Each group clears the
-      // rows of its own keys.
-      if (block_key0 + kAttnKeys - 1 > last_pos) {
+      // Rows of V past the last key the tile needs, and rows of pages that were not fetched because they lie
+      // before every row's window: zero, so that P = 0 gives 0.  Each group clears the rows of its own keys.
+      const int first_fetched = block_key0 + (skipped(j) << page_shift);
+      if (block_key0 + kAttnKeys - 1 > last_pos || first_fetched > block_key0) {
         if (!wait_all(&sm.v_full[vs], (j / kAttnVStages) & 1)) { ok = false; break; }
         const int row = g * kAttnGroupKeys + (r & (kAttnGroupKeys - 1));
-        if (r < kAttnGroupKeys && block_key0 + row > last_pos) {
+        if (r < kAttnGroupKeys && (block_key0 + row > last_pos || block_key0 + row < first_fetched)) {
 #pragma unroll
           for (int h = 0; h < HALVES; ++h) {
             uint4* dst = reinterpret_cast<uint4*>(sm.v[vs] + h * kAttnHalf + row * 128);

@@ -126,9 +126,12 @@ def test_trace_run_program(model, tmp_path):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("mode", ["whole", "tail", "mixed"])
-def test_run_order_is_data_on_the_gpu(mode, dtype):
+@pytest.mark.parametrize("name", ["B", "D"])
+def test_run_order_is_data_on_the_gpu(mode, dtype, name):
     """The toy arrangement (a layer twice, a layer reading another's keys and values, windows on some
-    layers): built from the same parts by a different list, replayed with the CUDA kernels."""
+    layers): built from the same parts by a different list, replayed with the CUDA kernels; with
+    configuration D in bfloat16 these are the tensor-core kernels, the merged ones included (a layer that
+    writes no keys and values of its own, a window)."""
     from distie_b200.config import EngineConfig
     from distie_b200.engine.engine import Engine, build_cache
     from distie_b200.engine.trace_replay import TraceSession
@@ -136,10 +139,10 @@ def test_run_order_is_data_on_the_gpu(mode, dtype):
     from distie_b200.models.decoder import DecoderModel, model_tensor_specs
     from distie_b200.weights import open_weights
 
-    cfg, page, weights = helpers.tiny("B")
+    cfg, page, weights = helpers.tiny(name)
     weights = helpers.bf16_rounded(weights)
     spec = helpers.toy_arrangement_spec(cfg)
-    requests = {f"r{i}": helpers.random_ids(cfg["vocab_size"], n, 60 + i) for i, n in enumerate([40, 67, 33, 150, 50, 36])}
+    requests = {f"r{i}": helpers.random_ids(cfg["vocab_size"], n, 60 + i) for i, n in enumerate([40, 67, 33, 200, 50, 36])}
     steps = MODES[mode](requests)
     kernels = make_kernels(torch.float32 if dtype == "float32" else torch.bfloat16, "cuda:0")
     config = EngineConfig(num_blocks=helpers.peak_tokens(steps) // page, page_size=page, max_seqs=8, dtype=dtype,
@@ -154,4 +157,7 @@ def test_run_order_is_data_on_the_gpu(mode, dtype):
         assert error <= helpers.FP32_TOL, f"{mode}: request {rid} position {at} off by {error:.2e} of the logit scale"
     else:
         helpers.Bf16Budget(requests, weights, cfg, expected, order=helpers.TOY_ORDER).check(got, expected, mode)
+        if name == "D" and mode == "tail":
+            ran = {kernel for kernel, count in kernels.kernel_counts.items() if count}
+            assert {"attention_decode_mma_qkv", "gemm_tcgen05_qkv", "attention_prefill_tcgen05"} <= ran, sorted(ran)
     assert cache.free_pages() == cache.total_pages() and cache.free_seats == cache.max_seats
