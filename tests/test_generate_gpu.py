@@ -21,7 +21,7 @@ def folder_for(name, tmp_path_factory, dtype="bfloat16"):
     return folder, cfg, page, {n: stored.tensor(n).float() for n in stored.keys()}
 
 
-@pytest.fixture(scope="module", params=["A", "B"])
+@pytest.fixture(scope="module", params=["A", "B", "D"])
 def tiny_model(request, tmp_path_factory):
     return folder_for(request.param, tmp_path_factory)
 
