@@ -164,7 +164,8 @@ def schedule_portions(requests: dict) -> list[dict]:
     return steps
 
 
-def schedule_mixed(requests: dict, seed: int = 0, live_max: int = 4, refeed: int = 0) -> list[dict]:
+def schedule_mixed(requests: dict, seed: int = 0, live_max: int = 4, refeed: int = 0,
+                   sizes: tuple = (2, 3, 5, 8, 13, 21, 40)) -> list[dict]:
     """Up to four live requests; portions of some beside single tokens of others; some sit a step out.
 
     With ``refeed`` that many requests are ended early, once each, somewhere past their middle (what a
@@ -194,7 +195,7 @@ def schedule_mixed(requests: dict, seed: int = 0, live_max: int = 4, refeed: int
             if at > 0 and rng.random() < 0.5:
                 size = 1
             else:
-                size = min(left, rng.choice((2, 3, 5, 8, 13, 21, 40)))
+                size = min(left, rng.choice(sizes))
             if left - size == 1 and size > 1:
                 size += 1
             entries.append({"id": rid, "tokens": ids[at : at + size], "want": list(range(size))})

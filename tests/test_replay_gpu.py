@@ -161,3 +161,35 @@ def test_run_order_is_data_on_the_gpu(mode, dtype, name):
             ran = {kernel for kernel, count in kernels.kernel_counts.items() if count}
             assert {"attention_decode_mma_qkv", "gemm_tcgen05_qkv", "attention_prefill_tcgen05"} <= ran, sorted(ran)
     assert cache.free_pages() == cache.total_pages() and cache.free_seats == cache.max_seats
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("seed", [1, 2, 3, 4])
+@pytest.mark.parametrize("name", ["C", "D"])
+def test_random_schedules_with_long_portions(name, seed, dtype, tmp_path_factory):
+    """Seeded random schedules whose portions reach 130 and 260 tokens, so that steps hold prompt portions on the
+    tensor-core product and attention kernels beside single tokens of other requests, with requests ended early
+    and fed again and so few pages that they are used again."""
+    from distie_b200.engine.trace_replay import TraceSession
+    from distie_b200.weights import ModelTensors, write_random_model
+
+    cfg, page, _ = helpers.tiny(name)
+    folder = str(tmp_path_factory.mktemp(f"fuzz{name}"))
+    write_random_model(folder, cfg, seed=helpers.TINY[name][2], std=helpers.STD[name], norm_noise=helpers.TINY[name][3], dtype="bfloat16")
+    stored = ModelTensors(folder)
+    weights = {n: stored.tensor(n).float() for n in stored.keys()}
+    lengths = [300, 70, 410, 33, 150, 260, 64]
+    requests = {f"r{i}": helpers.random_ids(cfg["vocab_size"], n, 500 + 10 * seed + i) for i, n in enumerate(lengths)}
+    steps = helpers.schedule_mixed(requests, seed=seed, refeed=2, sizes=(2, 5, 17, 40, 130, 260))
+    session = TraceSession.open(folder, dtype, helpers.peak_tokens(steps), page_size=page)
+    got = helpers.collect(steps, helpers.run_schedule(session, steps))
+    expected = helpers.expected_for(got, {rid: plain.forward_logits(ids, weights, cfg) for rid, ids in requests.items()})
+    if dtype == "float32":
+        error, rid, at = helpers.worst_error(got, expected)
+        assert error <= helpers.FP32_TOL, f"seed {seed}: request {rid} position {at} off by {error:.2e} of the logit scale"
+    else:
+        full = {rid: plain.forward_logits(ids, weights, cfg) for rid, ids in requests.items()}
+        helpers.Bf16Budget(requests, weights, cfg, full).check(got, expected, f"seed {seed}")
+        ran = {kernel for kernel, count in session.engine.runner.kernels.kernel_counts.items() if count}
+        assert {"attention_prefill_tcgen05", "gemm_tcgen05", "attention_decode_mma"} <= ran, sorted(ran)
+    cache = session.engine.cache
+    assert cache.free_pages() == cache.total_pages() and cache.free_seats == cache.max_seats
