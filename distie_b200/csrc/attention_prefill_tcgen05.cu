@@ -219,7 +219,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       page_ahead = read_table(j + 1);
       const int count = pages_of(j), from = skipped(j);
       if (__any_sync(0xffffffffu, lane >= from && lane < count && (page < 0 || page >= num_pages))) {
-        if (lane == 0 && error) atomicExch(error, 4);
+        if (lane == 0 && error) atomicExch(error, 5);
         ok = false;
         break;
       }

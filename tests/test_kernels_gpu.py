@@ -592,3 +592,34 @@ def test_position_beyond_the_block_table_sets_the_error_word(kernel_sets, dtype,
         ks.check_errors()
     ks.check_errors()  # the word was cleared
     assert torch.isfinite(out.float()).all()
+
+@pytest.mark.parametrize("tokens", [1, 140])
+def test_merged_ops_beyond_the_block_table_set_the_error_word(kernel_sets, tokens):
+    """The same for the ops that start from the projection: a position past the block table writes no key or value
+    anywhere, reads no page, and leaves the error word set (single tokens: the merged attention kernel; a
+    portion: the product with the cache write in its epilogue, then the attention)."""
+    from distie_b200.kernels.interface import KvSlot, RotaryTable
+    from distie_b200.kernels.library import KernelError
+
+    ks = kernel_sets[torch.bfloat16]
+    page, heads, kv_heads, head_dim, hidden = 16, 4, 2, 128, 256
+    kv = filled_cache_for(torch.bfloat16, kv_heads, head_dim, page, [200, 200])
+    before_k, before_v = kv.k.clone(), kv.v.clone()
+    width = kv.block_table.shape[1]
+    pasts = [200 - tokens, width * page + 5]
+    step = step_of([tokens, tokens], pasts, [0, 1])
+    n = (heads + 2 * kv_heads) * head_dim
+    x = torch.randn(step.num_tokens, hidden, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(n, hidden, device="cuda") / hidden**0.5).to(torch.bfloat16)
+    bias = torch.randn(n, device="cuda")
+    inv_freq = (1.0 / (10000.0 ** (torch.arange(0, head_dim, 2, dtype=torch.float32) / head_dim))).cuda()
+    out = torch.zeros(step.num_tokens, heads * head_dim, dtype=torch.bfloat16, device="cuda")
+    ks.qkv_attention(x, w, bias, step, kv, True, RotaryTable(inv_freq, head_dim), heads, kv_heads, head_dim, None, head_dim**-0.5, out)
+    with pytest.raises(KernelError, match="block table"):
+        ks.check_errors()
+    ks.check_errors()
+    assert torch.isfinite(out.float()).all()
+    # Only the first request's own slots changed.
+    changed = ((kv.k != before_k).any(-1) | (kv.v != before_v).any(-1)).nonzero()
+    own_pages = set(int(p) for p in kv.block_table[0].tolist() if p >= 0)
+    assert len(changed) > 0 and all(int(row[0]) in own_pages for row in changed)
