@@ -18,7 +18,7 @@ from __future__ import annotations
 import torch
 
 from . import library
-from .interface import KernelSet, KvSlot, RotaryTable, StepTensors
+from .interface import KernelSet, StepTensors
 from .library import KernelError, check, function
 
 _CODE = {torch.float32: 0, torch.bfloat16: 1}
