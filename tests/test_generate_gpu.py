@@ -167,6 +167,35 @@ def test_preemption_and_chunked_prefill_on_gpu(tmp_path_factory):
     assert engine.cache.free_pages() == engine.cache.total_pages()
 
 
+def test_preemption_and_portions_in_bfloat16_at_the_tensor_core_configuration(tmp_path_factory):
+    """Configuration D in bfloat16 through the scheduler: prompts of 3 to 300 tokens in portions of 150 beside
+    decoding requests, so few pages that requests are sent back and recomputed.  Every produced token must be the
+    plain arg-max of its position or a near tie of it (bfloat16 may turn a near tie), and a second run must give
+    the same tokens."""
+    from distie_b200.engine.engine import Engine
+
+    folder, cfg, page, weights = folder_for("D", tmp_path_factory)
+    engine = Engine.load(folder, dtype="bfloat16", num_blocks=16, page_size=page, max_seqs=5, token_budget=256,
+                         prefill_chunk=150, decode_graphs=True)
+    prompts = [helpers.random_ids(cfg["vocab_size"], n, 190 + n) for n in (3, 40, 300, 131, 64)]
+    results = engine.generate(prompts, max_new_tokens=64, ignore_eos=True)
+    assert sum(r.preemptions for r in results) >= 1, "the pool was meant to be too small"
+    for prompt, result in zip(prompts, results):
+        ids = prompt + result.token_ids[:-1]
+        full = plain.forward_logits(ids, weights, cfg)
+        budget = helpers.Bf16Budget({"x": ids}, weights, cfg, {"x": full})
+        rows = full[len(prompt) - 1 :]
+        slack = 3 * budget.max_error * plain.logit_scale(full)
+        for step, token in enumerate(result.token_ids):
+            short = float(rows[step].max() - rows[step][token])
+            assert short <= slack, f"prompt of {len(prompt)}: output {step} is {short:.3f} below the plain maximum (slack {slack:.3f})"
+    again = engine.generate(prompts, max_new_tokens=64, ignore_eos=True)
+    assert [r.token_ids for r in again] == [r.token_ids for r in results]
+    ran = {name for name, count in engine.model.kernels.kernel_counts.items() if count}
+    assert {"attention_decode_mma_qkv", "gemm_tcgen05_qkv", "attention_prefill_tcgen05"} <= ran, sorted(ran)
+    assert engine.cache.free_pages() == engine.cache.total_pages()
+
+
 def test_second_tiny_workload_against_the_sampling_oracle(tmp_path_factory):
     """The workload of the second tiny configuration with an oracle: prompts of 1/5/17/40/63 tokens in
     portions of 11 beside decoding requests, temperature 0.8 from seed 1, 24 tokens each, one forced
